@@ -1,0 +1,77 @@
+// Shared device helpers of the ccinfer_b200 kernels (sm_100a).
+//
+// Every kernel family is instantiated for two element types: float (the true
+// 32-bit path) and __nv_bfloat16 (the serving path).  Arithmetic is always
+// done in float; only loads and stores see the storage type.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define CCB_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes of the C interface
+enum { CCB_F32 = 0, CCB_BF16 = 1 };
+
+// bits of the device status word (set by kernels, never cleared by them)
+enum {
+  CCB_ST_BAD_TOKEN = 1,   // token id outside [0, vocab)
+  CCB_ST_BAD_SLOT = 2,    // cache slot outside the pool
+  CCB_ST_BAD_PAGE = 4,    // block-table entry outside the pool where a key was needed
+  CCB_ST_BAD_ROW = 8,     // row index outside the batch
+  CCB_ST_WAIT_TIMEOUT = 16  // a bounded mbarrier wait gave up
+};
+
+namespace ccb {
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of kThreads (a multiple of 32, at most 1024) in a fixed
+// order: lanes by butterfly, then the warps' partial sums one after another.
+// Every thread gets the result.  `red` holds at least 32 floats.
+template <int kThreads>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // red may still be read from an earlier call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) total += red[w];
+  return total;
+}
+
+__device__ __forceinline__ void set_status(int* status, int bit) {
+  if (status != nullptr) atomicOr(status, bit);
+}
+
+}  // namespace ccb
+
+// Host side: every launcher returns the CUDA error code of its launch (0 = ok)
+// or a negative number for an argument it refuses.
+#define CCB_REFUSE_SIZE (-2)
+#define CCB_REFUSE_DTYPE (-3)
+#define CCB_REFUSE_ARG (-4)
+
+static inline int ccb_launch_status() { return (int)cudaGetLastError(); }

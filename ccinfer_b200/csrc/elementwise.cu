@@ -1,0 +1,94 @@
+// Embedding gather and SiLU-multiply.
+//
+// embed:    h[t, :] = float(table[ids[t], :])          (7QiC/ccInfer: src/kernel/elementwise/elementwise.cu:67-78)
+// silu_mul: act[t, f] = silu(gu[t, f]) * gu[t, F + f]  (7QiC/ccInfer: src/kernel/mlp/silu_mul.cu:24-28)
+// The gate and up projections are one merged matrix product here, so the
+// kernel reads both halves of a [T, 2F] row.
+#include "common.cuh"
+
+using namespace ccb;
+
+template <typename T>
+__global__ void embed_gather_kernel(float* __restrict__ h, const T* __restrict__ table,
+                                    const int* __restrict__ ids, int D, int V, int* status) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* out = h + (size_t)t * D;
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) set_status(status, CCB_ST_BAD_TOKEN);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) out[d] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)id * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) out[d] = to_f32(row[d]);
+}
+
+CCB_API int ccb_embed_gather(float* h, const void* table, const int* ids, int T_, int D, int V,
+                             int dtype, int* status, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (D <= 0 || V <= 0) return CCB_REFUSE_SIZE;
+  const int threads = D >= 1024 ? 256 : 128;
+  if (dtype == CCB_F32)
+    embed_gather_kernel<float><<<T_, threads, 0, stream>>>(h, (const float*)table, ids, D, V, status);
+  else if (dtype == CCB_BF16)
+    embed_gather_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(h, (const __nv_bfloat16*)table, ids, D, V, status);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
+// accurate variant for the 32-bit path, fast exponential for the bf16 path
+template <typename T> __device__ __forceinline__ float silu(float g);
+template <> __device__ __forceinline__ float silu<float>(float g) { return g / (1.f + expf(-g)); }
+template <> __device__ __forceinline__ float silu<__nv_bfloat16>(float g) { return g / (1.f + __expf(-g)); }
+
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ act, const T* __restrict__ gu, int F, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / F;
+    const int f = (int)(i - t * F);
+    const T* row = gu + t * 2 * (size_t)F;
+    const float g = to_f32(row[f]);
+    const float u = to_f32(row[F + f]);
+    act[i] = from_f32<T>(silu<T>(g) * u);
+  }
+}
+
+// bf16, F even: two elements per thread
+__global__ void silu_mul_bf16x2_kernel(__nv_bfloat162* __restrict__ act, const __nv_bfloat162* __restrict__ gu,
+                                       int F2, size_t total2) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total2; i += stride) {
+    const size_t t = i / F2;
+    const int f = (int)(i - t * F2);
+    const __nv_bfloat162* row = gu + t * 2 * (size_t)F2;
+    const float2 g = __bfloat1622float2(row[f]);
+    const float2 u = __bfloat1622float2(row[F2 + f]);
+    act[i] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+  }
+}
+
+CCB_API int ccb_silu_mul(void* act, const void* gate_up, int T_, int F, int dtype, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (F <= 0) return CCB_REFUSE_SIZE;
+  const size_t total = (size_t)T_ * F;
+  const int threads = 256;
+  if (dtype == CCB_BF16 && (F % 2) == 0) {
+    const size_t total2 = total / 2;
+    const int blocks = (int)((total2 + threads - 1) / threads < 148 * 16 ? (total2 + threads - 1) / threads : 148 * 16);
+    silu_mul_bf16x2_kernel<<<blocks, threads, 0, stream>>>((__nv_bfloat162*)act, (const __nv_bfloat162*)gate_up,
+                                                            F / 2, total2);
+    return ccb_launch_status();
+  }
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == CCB_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)act, (const float*)gate_up, F, total);
+  else if (dtype == CCB_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)act, (const __nv_bfloat16*)gate_up, F, total);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}

@@ -1,0 +1,344 @@
+"""The engine core: model + cache + ONE step function.
+
+``Engine.step(entries)`` runs a batch of (request, its next tokens) — portions
+of prompts beside single decoded tokens, cut anywhere — as one batch from the
+cache and returns the logits at the wanted places.  It corresponds to
+7QiC/ccInfer's translate -> inference -> commit (src/worker/worker.cpp:330-539,
+src/worker/batch_translator.cpp:241-431, src/model/model_runner.h:25-247) with
+these differences: logits are computed only for the wanted rows and handed
+out (the reference computes all rows and keeps them inside the runner),
+sampling is a separate call, and nothing is allocated per step.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels
+from ..cache.manager import CacheManager, GroupSpec
+from ..config.registry import load_config
+from ..errors import InvalidArgument, KVBlockExhausted, RequestTooLong, Unsupported
+from ..weights.loader import open_weights, random_fetch
+from .plan import ModelPlan
+from .runtime import Runtime
+from .step import GroupStep, LayerCache, StepContext, StepLayout
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+@dataclasses.dataclass
+class StepEntry:
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()     # places among ``tokens`` whose logits are wanted
+
+
+@dataclasses.dataclass
+class EngineOptions:
+    dtype: object = "bfloat16"
+    device: str = "cuda:0"
+    page_size: int = 16              # tokens per cache page (the reference's constant, src/cache/block.h:9)
+    kv_tokens: Optional[int] = None  # tokens the cache pool of each group holds; default 1024 pages as the reference
+    max_requests: int = 64           # live requests = state slots (src/worker/worker.h:102)
+    max_tokens_per_step: int = 4096  # the reference's compute budget (src/scheduler/scheduler.cpp:25)
+    max_context: Optional[int] = None  # longest request; default min(model limit, pool)
+    use_graphs: bool = True
+
+
+class Engine:
+    def __init__(self, plan: ModelPlan, fetch, options: EngineOptions = None):
+        opt = options or EngineOptions()
+        self.options = opt
+        try:
+            self.dtype = _DTYPES[opt.dtype]
+        except KeyError:
+            raise Unsupported(f"dtype {opt.dtype!r}: bfloat16 or float32") from None
+        if opt.page_size <= 0:
+            raise InvalidArgument("page_size must be > 0")
+        plan.validate()
+        self.plan = plan
+        self.vocab_size = plan.vocab_size
+        self.rt = rt = Runtime(opt.device, self.dtype, opt.max_tokens_per_step, opt.max_requests)
+        for part in plan.parts():
+            part.bind(rt, fetch)
+
+        # ---- cache groups, storage and state ----
+        P = opt.page_size
+        kv_tokens = opt.kv_tokens if opt.kv_tokens is not None else 1024 * P
+        num_pages = max(1, -(-kv_tokens // P))
+        limit = num_pages * P
+        if plan.max_position is not None:
+            limit = min(limit, plan.max_position)
+        self.max_context = min(opt.max_context, limit) if opt.max_context else limit
+        group_keys: List[tuple] = []
+        self._entry_group: Dict[int, int] = {}
+        self._cache_k: Dict[int, torch.Tensor] = {}
+        self._cache_v: Dict[int, torch.Tensor] = {}
+        self._state: Dict[int, torch.Tensor] = {}
+        windows = []
+        for i, e in enumerate(plan.order):
+            mixer = plan.layers[e.layer].mixer
+            need = mixer.cache_need()
+            if e.cache_of is not None:
+                if need is None:
+                    raise InvalidArgument(f"order[{i}] reads a cache but its mixer keeps none")
+                if getattr(mixer, "own_kv", False):
+                    raise InvalidArgument(f"order[{i}] reads another entry's cache but its mixer writes keys")
+            elif need is not None:
+                if need.group_key not in group_keys:
+                    group_keys.append(need.group_key)
+                    windows.append(need.window)
+                self._entry_group[i] = group_keys.index(need.group_key)
+                shape = (num_pages, need.kv_heads, P, need.head_dim)
+                self._cache_k[i] = torch.zeros(shape, dtype=self.dtype, device=rt.device)
+                self._cache_v[i] = torch.zeros(shape, dtype=self.dtype, device=rt.device)
+            sn = mixer.state_need()
+            if sn is not None:
+                self._state[i] = torch.zeros((opt.max_requests,) + tuple(sn.shape), dtype=sn.dtype, device=rt.device)
+        for i, e in enumerate(plan.order):
+            if e.cache_of is not None:
+                if e.cache_of not in self._entry_group:
+                    raise InvalidArgument(f"order[{i}] reads the cache of entry {e.cache_of}, which keeps none")
+                self._entry_group[i] = self._entry_group[e.cache_of]
+        self.cache = CacheManager([GroupSpec(k, w, P, num_pages) for k, w in zip(group_keys, windows)],
+                                  opt.max_requests)
+        self.graph_safe = all(getattr(p, "graph_safe", True) for p in plan.parts())
+
+        # ---- the step arrays ----
+        stride = -(-self.max_context // P)
+        self.layout = lay = StepLayout(opt.max_tokens_per_step, opt.max_requests, [stride] * len(group_keys))
+        # two pinned staging buffers in turn: the host may fill one while the copy of the other is in flight
+        self._host_bufs = [torch.zeros(lay.size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._host_events = [None, None]
+        self._host_turn = 0
+        self._dev_buf = torch.zeros(lay.size, dtype=torch.int32, device=rt.device)
+        self.steps_run = 0
+        self.kernel_launch_estimate = 0
+
+    # ------------------------------------------------------------------------------------
+    @classmethod
+    def from_model_dir(cls, model_dir: str, options: EngineOptions = None) -> "Engine":
+        """The model class is chosen by config.json's architecture name."""
+        opt = options or EngineOptions()
+        arch, cfg = load_config(model_dir)
+        plan = arch.build_plan(cfg)
+        fetch = open_weights(model_dir, plan.tensor_specs(), opt.device, _DTYPES[opt.dtype],
+                             shared=plan.shared_tensor_names())
+        try:
+            eng = cls(plan, fetch, opt)
+        finally:
+            fetch.close()
+        eng.config = cfg
+        return eng
+
+    @classmethod
+    def from_random(cls, config, seed: int, std: float = 0.02, options: EngineOptions = None) -> "Engine":
+        """Random weights drawn on the device (nothing is written); for measurements on large shapes."""
+        from ..config.registry import architecture_of
+        opt = options or EngineOptions()
+        arch = architecture_of(config.to_json())
+        plan = arch.build_plan(config)
+        fetch = random_fetch(plan.tensor_specs(), seed, std, opt.device, _DTYPES[opt.dtype],
+                             shared=plan.shared_tensor_names())
+        eng = cls(plan, fetch, opt)
+        eng.config = config
+        return eng
+
+    # ------------------------------------------------------------------------------------
+    def open_request(self, req_id: Hashable) -> int:
+        """Gives the request a state slot (its state tensors are zeroed); returns the slot."""
+        rc = self.cache.open(req_id)
+        for st in self._state.values():
+            st[rc.slot].zero_()
+        return rc.slot
+
+    def close_request(self, req_id: Hashable) -> None:
+        """Gives back what the request holds: its pages in every group and its slot."""
+        self.cache.close(req_id)
+
+    def context_len(self, req_id: Hashable) -> int:
+        return self.cache.get(req_id).ctx_len
+
+    # ------------------------------------------------------------------------------------
+    def _validate(self, entries: List[StepEntry]) -> None:
+        if not entries:
+            raise InvalidArgument("a step needs at least one entry")
+        if len(entries) > self.options.max_requests:
+            raise InvalidArgument(f"{len(entries)} entries in a step, at most {self.options.max_requests}")
+        seen = set()
+        total = 0
+        for e in entries:
+            if e.req_id in seen:
+                raise InvalidArgument(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise InvalidArgument(f"request {e.req_id!r} brings no tokens")
+            total += n
+            rc = self.cache.get(e.req_id)
+            if rc.ctx_len + n > self.max_context:
+                raise RequestTooLong(f"request {e.req_id!r}: {rc.ctx_len} cached + {n} new tokens exceed the "
+                                     f"limit of {self.max_context}")
+            for w in e.want:
+                if not (0 <= w < n):
+                    raise InvalidArgument(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
+        if total > self.options.max_tokens_per_step:
+            raise InvalidArgument(f"{total} tokens in a step, at most {self.options.max_tokens_per_step}")
+
+    def _build(self, entries: List[StepEntry], pad_to: int = 0) -> StepContext:
+        """Fills the pinned buffer, copies it to the device and returns the views of the step."""
+        lay = self.layout
+        turn = self._host_turn
+        self._host_turn ^= 1
+        if self._host_events[turn] is not None:
+            self._host_events[turn].synchronize()  # its last copy has left the buffer
+        host_buf = self._host_bufs[turn]
+        host = host_buf.numpy()
+        B = len(entries)
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(counts, out=cu[1:])
+        T = int(cu[-1])
+        Bp = max(B, pad_to)
+        Tp = T + (Bp - B)
+        rcs = [self.cache.get(e.req_id) for e in entries]
+        pos0 = np.fromiter((rc.ctx_len for rc in rcs), dtype=np.int64, count=B)
+
+        tok = host[lay.o_token_ids:lay.o_token_ids + Tp]
+        posv = host[lay.o_positions:lay.o_positions + Tp]
+        eot = host[lay.o_entry_of_token:lay.o_entry_of_token + Tp]
+        for b, e in enumerate(entries):
+            tok[cu[b]:cu[b + 1]] = e.tokens
+        eot[:T] = np.repeat(np.arange(B, dtype=np.int32), counts)
+        posv[:T] = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1] - pos0, counts)
+        tok[T:Tp] = 0
+        posv[T:Tp] = 0
+        eot[T:Tp] = -1
+
+        rows = [int(cu[b]) + int(w) for b, e in enumerate(entries) for w in e.want]
+        R = len(rows)
+        lr = host[lay.o_logit_rows:lay.o_logit_rows + max(R, 1)]
+        if R:
+            lr[:R] = rows
+        hcu = host[lay.o_cu_q:lay.o_cu_q + Bp + 1]
+        hcu[:B + 1] = cu
+        hcu[B + 1:] = np.arange(T + 1, Tp + 1)
+        hp0 = host[lay.o_pos0:lay.o_pos0 + Bp]
+        hca = host[lay.o_ctx_after:lay.o_ctx_after + Bp]
+        hss = host[lay.o_state_slot:lay.o_state_slot + Bp]
+        hp0[:B] = pos0
+        hca[:B] = pos0 + counts
+        hss[:B] = [rc.slot for rc in rcs]
+        hp0[B:] = 0
+        hca[B:] = 0
+        hss[B:] = -1
+
+        step = StepContext()
+        step.n_tokens, step.n_entries, step.n_logit_rows = Tp, Bp, R
+        step.max_q_len = int(counts.max())
+        step.max_ctx = int((pos0 + counts).max())
+        dev = self._dev_buf
+
+        def dv(off, n):
+            return dev[off:off + n]
+
+        step.token_ids = dv(lay.o_token_ids, Tp)
+        step.positions = dv(lay.o_positions, Tp)
+        step.entry_of_token = dv(lay.o_entry_of_token, Tp)
+        step.logit_rows = dv(lay.o_logit_rows, max(R, 1))
+        step.cu_q = dv(lay.o_cu_q, Bp + 1)
+        step.pos0 = dv(lay.o_pos0, Bp)
+        step.ctx_after = dv(lay.o_ctx_after, Bp)
+        step.state_slot = dv(lay.o_state_slot, Bp)
+
+        for g, spec in enumerate(self.cache.groups):
+            P, stride = spec.page_size, lay.group_strides[g]
+            sm = host[lay.o_slot_map[g]:lay.o_slot_map[g] + Tp]
+            bt = host[lay.o_block_table[g]:lay.o_block_table[g] + Bp * stride].reshape(Bp, stride)
+            for b, rc in enumerate(rcs):
+                table = np.asarray(rc.tables[g], dtype=np.int32)
+                bt[b, :table.size] = table
+                p = np.arange(pos0[b], pos0[b] + counts[b])
+                sm[cu[b]:cu[b + 1]] = table[p // P] * P + p % P
+            sm[T:Tp] = -1
+            step.groups.append(GroupStep(
+                index=g, page_size=P, num_pages=spec.num_pages, window=spec.window,
+                slot_map=dv(lay.o_slot_map[g], Tp),
+                block_table=dv(lay.o_block_table[g], Bp * stride).view(Bp, stride),
+                host_slot_map=sm, host_block_table=bt))
+        step.host = _HostView(tok, posv, eot, lr[:R], hcu, hp0, hca, hss)
+        self._dev_buf.copy_(host_buf, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._host_events[turn] = ev
+        return step
+
+    def _forward(self, step: StepContext) -> Optional[torch.Tensor]:
+        plan = self.plan
+        stream = plan.embedding.forward(step)
+        for i, e in enumerate(plan.order):
+            block = plan.layers[e.layer]
+            cache = None
+            if i in self._entry_group:
+                src = i if e.cache_of is None else e.cache_of
+                cache = LayerCache(self._cache_k[src], self._cache_v[src], step.groups[self._entry_group[i]],
+                                   own=e.cache_of is None)
+            block.forward(stream, step, cache, self._state.get(i))
+        if step.n_logit_rows == 0:
+            return None
+        x = plan.final_norm.fold(stream, rows=step.logit_rows, n_rows=step.n_logit_rows)
+        return plan.head.forward(x)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the tokens given, as one batch, from the cache; returns float logits [wanted, vocab].
+
+        Rows are in the order of the entries and, within an entry, of its ``want``.
+        Either the whole step happens (every request's cached length grows by its
+        token count) or nothing does: if pages run out (KVBlockExhausted) or a
+        launch fails, the pages taken for the step are given back.
+        """
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self._validate(entries)
+        reserved = []
+        try:
+            for e in entries:
+                self.cache.reserve(e.req_id, len(e.tokens))
+                reserved.append(e.req_id)
+            step = self._build(entries)
+            logits = self._forward(step)
+        except BaseException:
+            for rid in reserved:
+                self.cache.rollback(rid)
+            raise
+        for e in entries:
+            self.cache.commit(e.req_id)
+        self.steps_run += 1
+        if logits is None:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.rt.device)
+        return logits
+
+    def check(self) -> None:
+        """Synchronises and raises DeviceFault if a kernel reported a bad index since the last check."""
+        self.rt.check_status()
+
+    def stats(self) -> dict:
+        s = self.cache.stats()
+        s["steps"] = self.steps_run
+        s["scratch_bytes"] = self.rt.scratch.bytes()
+        return s
+
+
+@dataclasses.dataclass
+class _HostView:
+    token_ids: np.ndarray
+    positions: np.ndarray
+    entry_of_token: np.ndarray
+    logit_rows: np.ndarray
+    cu_q: np.ndarray
+    pos0: np.ndarray
+    ctx_after: np.ndarray
+    state_slot: np.ndarray

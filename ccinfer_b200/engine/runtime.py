@@ -1,0 +1,73 @@
+"""What every part needs of the device: the compute type, scratch memory, the matrix product and the status word."""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+from .. import kernels
+from ..errors import DeviceFault, ExtensionMissing, Unsupported
+
+
+class ScratchPool:
+    """Named buffers that live as long as the engine and never move.
+
+    ``get(key, shape, dtype)`` returns the same storage for the same key, grown
+    only before the first step; parts ask for ``[max_tokens, width]`` once and
+    slice the rows of a step.  Layers of equal shape share a buffer by using the
+    same key, and fixed addresses let a decode step be replayed from a graph.
+    """
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        full_key = f"{key}:{dtype}"
+        buf = self._bufs.get(full_key)
+        if buf is None or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"scratch buffer '{key}' asked to grow after the pool was frozen "
+                                   f"({n} > {0 if buf is None else buf.numel()} elements)")
+            buf = torch.empty(n, dtype=dtype, device=self.device)
+            self._bufs[full_key] = buf
+        return buf[:n].view(shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+class Runtime:
+    def __init__(self, device, dtype: torch.dtype, max_tokens: int, max_entries: int):
+        if not torch.cuda.is_available():
+            raise ExtensionMissing("no CUDA device: the engine has no CPU path")
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise Unsupported(f"compute type {dtype} is not supported (float32 or bfloat16)")
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.max_tokens = int(max_tokens)
+        self.max_entries = int(max_entries)
+        torch.cuda.set_device(self.device)
+        kernels.lib()  # build / load now: fail loudly before anything else happens
+        self.scratch = ScratchPool(self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.cublas = kernels.CublasHandle(self.device) if dtype == torch.bfloat16 else None
+
+    def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """out[M, N] = x[M, K] @ w[N, K]^T; out may be float for bfloat16 operands (the logits)."""
+        if self.dtype == torch.float32:
+            kernels.gemm_f32(out, x, w)
+        else:
+            self.cublas.gemm_bf16(out, x, w)
+        return out
+
+    def check_status(self) -> None:
+        """Reads the status word (synchronises) and raises if a kernel reported a bad index."""
+        word = int(self.status.item())
+        if word:
+            self.status.zero_()
+            raise DeviceFault("a kernel reported " + kernels.status_message(word))

@@ -1,0 +1,95 @@
+"""The batch of one step as the device sees it.
+
+7QiC/ccInfer's translator builds seven int32 arrays per step and uploads each
+to a fresh allocation (src/worker/batch_translator.cpp:241-431).  Here all
+arrays of a step live at fixed offsets of ONE pinned host buffer and ONE device
+buffer of fixed size: a step is one host-to-device copy, and because nothing
+moves, a decode step can be replayed from a CUDA graph.
+
+  token_ids[T]       the tokens the step brings, entries one after another
+  positions[T]       absolute position of each token in its request
+  entry_of_token[T]  which entry (request) a token belongs to; -1 for padding
+  logit_rows[R]      token rows whose logits are wanted
+  cu_q[B+1]          first token row of each entry (exclusive prefix sum)
+  pos0[B]            position of the entry's first token (= tokens cached before)
+  ctx_after[B]       tokens cached after the step (= pos0 + count)
+  state_slot[B]      the request's state slot; -1 for padding
+  per cache group:   slot_map[T] (where each token's k/v go; -1 = nowhere) and
+                     block_table[B, stride] (logical page -> physical page, -1 = none)
+
+The reference finds a token's request by a linear scan of query_start_loc
+(src/kernel/attention/prefill_attn.cu:80-83); entry_of_token replaces that.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+
+@dataclasses.dataclass
+class GroupStep:
+    """A cache group's part of a step."""
+    index: int
+    page_size: int
+    num_pages: int
+    window: Optional[int]
+    slot_map: torch.Tensor       # int32 [T]
+    block_table: torch.Tensor    # int32 [B, stride] (a view with row stride = the full stride)
+    host_slot_map: np.ndarray
+    host_block_table: np.ndarray
+
+
+@dataclasses.dataclass
+class LayerCache:
+    """What a mixer gets of the cache: its key and value pages and its group's step arrays."""
+    k: torch.Tensor              # [pages, kv_heads, page_size, head_dim]
+    v: torch.Tensor
+    group: GroupStep
+    own: bool                    # False: the pages belong to another run entry; read only
+
+
+class StepContext:
+    """Views (device) and arrays (host) of the current step; see the module docstring."""
+
+    def __init__(self):
+        self.n_tokens = 0
+        self.n_entries = 0
+        self.n_logit_rows = 0
+        self.max_q_len = 0       # host facts for kernels that choose a launch shape
+        self.max_ctx = 0
+        self.token_ids = self.positions = self.entry_of_token = self.logit_rows = None
+        self.cu_q = self.pos0 = self.ctx_after = self.state_slot = None
+        self.groups: List[GroupStep] = []
+        self.host = None         # StepLayout.HostView of the same arrays
+
+
+class StepLayout:
+    """Fixed offsets of the step arrays inside one int32 buffer."""
+
+    def __init__(self, max_tokens: int, max_entries: int, group_strides: List[int]):
+        self.max_tokens, self.max_entries, self.group_strides = max_tokens, max_entries, list(group_strides)
+        off = 0
+
+        def region(n):
+            nonlocal off
+            start = off
+            off += (n + 3) // 4 * 4  # keep every region 16-byte aligned
+            return start
+
+        self.o_token_ids = region(max_tokens)
+        self.o_positions = region(max_tokens)
+        self.o_entry_of_token = region(max_tokens)
+        self.o_logit_rows = region(max_tokens)
+        self.o_cu_q = region(max_entries + 1)
+        self.o_pos0 = region(max_entries)
+        self.o_ctx_after = region(max_entries)
+        self.o_state_slot = region(max_entries)
+        self.o_slot_map = []
+        self.o_block_table = []
+        for stride in self.group_strides:
+            self.o_slot_map.append(region(max_tokens))
+            self.o_block_table.append(region(max_entries * stride))
+        self.size = off

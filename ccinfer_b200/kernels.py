@@ -1,0 +1,244 @@
+"""Python face of the CUDA kernels: one function per launcher of ``csrc``.
+
+The shared object is loaded with ctypes; tensors are passed as raw device
+pointers and every launch goes to torch's current CUDA stream, so the kernels
+take part in stream capture like any other work.  A launcher that refuses its
+arguments or whose launch fails raises; nothing falls back to another
+implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_size_t, c_void_p
+
+import torch
+
+from .csrc import build as _build
+from .errors import ExtensionMissing, InvalidArgument, Unsupported
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+ST_BAD_TOKEN, ST_BAD_SLOT, ST_BAD_PAGE, ST_BAD_ROW, ST_WAIT_TIMEOUT = 1, 2, 4, 8, 16
+STATUS_TEXT = {
+    ST_BAD_TOKEN: "a token id outside the vocabulary",
+    ST_BAD_SLOT: "a cache slot outside the pool",
+    ST_BAD_PAGE: "a block-table entry outside the pool where a key was needed",
+    ST_BAD_ROW: "a row index outside the batch",
+    ST_WAIT_TIMEOUT: "a bounded wait inside a kernel gave up",
+}
+
+_lock = threading.Lock()
+_libs = {}
+
+_SIGNATURES = {
+    "ccb_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ccb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ccb_residual_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                             c_int, c_void_p, c_void_p],
+    "ccb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "ccb_qk_norm_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_void_p],
+    "ccb_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                    c_void_p, c_void_p],
+    "ccb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_cublas_create": [ctypes.POINTER(c_void_p)],
+    "ccb_cublas_destroy": [c_void_p],
+    "ccb_cublas_set_workspace": [c_void_p, c_void_p, c_size_t],
+    "ccb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p],
+    "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+}
+
+
+def lib(group: str = "core"):
+    """The loaded shared object of a kernel group (built at the first call)."""
+    with _lock:
+        if group in _libs:
+            return _libs[group]
+        path = _build.library_path(group)
+        try:
+            handle = ctypes.CDLL(path)
+        except OSError as e:
+            raise ExtensionMissing(f"cannot load {path}: {e}") from e
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(handle, name, None)
+            if fn is not None:
+                fn.argtypes = argtypes
+                fn.restype = c_int
+        _libs[group] = handle
+        return handle
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -2:
+        raise Unsupported(f"{what}: a size outside what the kernel takes")
+    if code == -3:
+        raise Unsupported(f"{what}: element type not supported")
+    if code == -4:
+        raise InvalidArgument(f"{what}: a required argument is missing")
+    if code >= 1000:
+        raise RuntimeError(f"{what}: cuBLAS status {code - 1000}")
+    raise RuntimeError(f"{what}: CUDA error {code}")
+
+
+def _p(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise Unsupported(f"element type {t.dtype} is not supported by the kernels") from None
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise InvalidArgument("kernels take contiguous CUDA tensors")
+
+
+def status_message(word: int) -> str:
+    return "; ".join(text for bit, text in STATUS_TEXT.items() if word & bit) or "no fault"
+
+
+# ---------------------------------------------------------------------------------------------
+def embed_gather(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status=None) -> None:
+    """h[t, :] = float(table[ids[t], :]); h is the float residual stream [T, D]."""
+    _cuda(h, table, ids, status)
+    T, D = h.shape
+    assert h.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == D and ids.numel() >= T
+    _check(lib().ccb_embed_gather(_p(h), _p(table), _p(ids), T, D, table.shape[0], _dt(table), _p(status),
+                                  _stream()), "embed_gather")
+
+
+def silu_mul(act: torch.Tensor, gate_up: torch.Tensor) -> None:
+    """act[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+    _cuda(act, gate_up)
+    T, F = act.shape
+    assert gate_up.shape == (T, 2 * F) and act.dtype == gate_up.dtype
+    _check(lib().ccb_silu_mul(_p(act), _p(gate_up), T, F, _dt(act), _stream()), "silu_mul")
+
+
+def residual_rmsnorm(y, h, delta, w, eps: float, row_idx=None, n_rows=None, status=None) -> None:
+    """y = RMSNorm(h + delta) * w, and h <- h + delta when no rows are picked.
+
+    h float [T, D]; delta (optional) and y in the storage type; w float [D].
+    With ``row_idx`` (int32 [R]) only those rows of h are normed, into y [R, D].
+    """
+    _cuda(y, h, delta, w, row_idx, status)
+    D = h.shape[1]
+    rows = y.shape[0] if n_rows is None else n_rows
+    assert h.dtype == torch.float32 and w.dtype == torch.float32 and w.numel() == D and y.shape[1] == D
+    assert delta is None or (delta.dtype == y.dtype and delta.shape[1] == D)
+    _check(lib().ccb_residual_rmsnorm(_p(y), _p(h), _p(delta), _p(w), _p(row_idx), rows, h.shape[0], D,
+                                      float(eps), _dt(y), _p(status), _stream()), "residual_rmsnorm")
+
+
+def rmsnorm(y, x, w, eps: float) -> None:
+    """Plain RMSNorm over the last axis of a contiguous tensor; w float."""
+    _cuda(y, x, w)
+    D = x.shape[-1]
+    assert w.dtype == torch.float32 and w.numel() == D and y.dtype == x.dtype and y.shape == x.shape
+    _check(lib().ccb_rmsnorm(_p(y), _p(x), _p(w), x.numel() // D, D, float(eps), _dt(x), _stream()), "rmsnorm")
+
+
+def qk_norm_rope_kv_write(qkv, q_out, k_cache, v_cache, positions, slot_map, inv_freq, q_w, k_w, eps,
+                          nq: int, nkv: int, hd: int, page_size: int, status=None) -> None:
+    """Head norms, rotation and cache write in one pass over qkv [T, (nq + 2 nkv) hd].
+
+    q goes to q_out [T, nq, hd]; k and v go to their caches [pages, nkv, page, hd]
+    at slot_map[t] (a negative slot skips the write).  inv_freq, q_w, k_w may
+    be None to leave that step out; nkv = 0 handles q alone.
+    """
+    _cuda(qkv, q_out, k_cache, v_cache, positions, slot_map, inv_freq, q_w, k_w, status)
+    T = q_out.shape[0]
+    assert qkv.shape[0] >= T and qkv.shape[1] >= (nq + 2 * nkv) * hd and qkv.dtype == q_out.dtype
+    num_slots = 0
+    if nkv > 0:
+        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+        assert k_cache.shape[1:] == (nkv, page_size, hd) and v_cache.shape == k_cache.shape
+        num_slots = k_cache.shape[0] * page_size
+    _check(lib().ccb_qk_norm_rope_kv_write(_p(qkv), qkv.stride(0), _p(q_out), _p(k_cache), _p(v_cache),
+                                           _p(positions), _p(slot_map), _p(inv_freq), _p(q_w), _p(k_w),
+                                           float(eps), T, nq, nkv, hd, page_size, num_slots, _dt(qkv),
+                                           _p(status), _stream()), "qk_norm_rope_kv_write")
+
+
+def paged_attention_generic(q, k_cache, v_cache, out, positions, entry_of_token, block_table, n_entries: int,
+                            window: int, scale: float, status=None) -> None:
+    """Causal attention of q [T, nq, hd] over paged caches [pages, nkv, page, hd].
+
+    Token t belongs to request row entry_of_token[t] of block_table [B, stride]
+    and sits at absolute position positions[t]; window <= 0 means all keys.
+    """
+    _cuda(q, k_cache, v_cache, out, positions, entry_of_token, block_table, status)
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    assert hd2 == hd and out.shape == q.shape and q.dtype == k_cache.dtype == v_cache.dtype == out.dtype
+    _check(lib().ccb_paged_attention_generic(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(positions),
+                                             _p(entry_of_token), _p(block_table), block_table.stride(0),
+                                             n_entries, T, nq, nkv, hd, page_size, num_pages, int(window),
+                                             float(scale), _dt(q), _p(status), _stream()),
+           "paged_attention_generic")
+
+
+def gemm_f32(c, a, w) -> None:
+    """c[M, N] = a[M, K] @ w[N, K]^T in true 32-bit arithmetic (row strides may exceed the widths)."""
+    assert c.dtype == a.dtype == w.dtype == torch.float32 and c.is_cuda and a.is_cuda and w.is_cuda
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    _check(lib().ccb_gemm_f32(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _stream()),
+           "gemm_f32")
+
+
+class CublasHandle:
+    """One cuBLAS handle with a caller-owned workspace (no allocation inside a step)."""
+
+    def __init__(self, device, workspace_bytes: int = 64 << 20):
+        self._h = c_void_p()
+        with torch.cuda.device(device):
+            _check(lib().ccb_cublas_create(ctypes.byref(self._h)), "cublas_create")
+            self.workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=device)
+            _check(lib().ccb_cublas_set_workspace(self._h, self.workspace.data_ptr(), workspace_bytes),
+                   "cublas_set_workspace")
+
+    def gemm_bf16(self, c, a, w) -> None:
+        """c[M, N] (bfloat16 or float) = a[M, K] @ w[N, K]^T, bfloat16 operands, float accumulation."""
+        assert a.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT
+        M, K = a.shape
+        N = w.shape[0]
+        assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+        _check(lib().ccb_gemm_bf16(self._h, _p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0),
+                                   _dt(c), _stream()), "gemm_bf16")
+
+    def close(self):
+        if self._h:
+            lib().ccb_cublas_destroy(self._h)
+            self._h = c_void_p()
+
+
+def sample_rows(logits, tokens, temperature=None, seed=None, out_index=None) -> None:
+    """tokens[r] = greedy or temperature draw of logits[r, :] (float), per-row parameters.
+
+    temperature float [R] (<= 0 greedy), seed uint32-valued int32/int64 [R] taken
+    as 32 bits, out_index int32 [R].  temperature None = greedy for all rows.
+    """
+    _cuda(tokens, temperature, seed, out_index)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and tokens.dtype == torch.int32
+    assert temperature is None or (temperature.dtype == torch.float32 and seed.dtype == torch.int32
+                                   and out_index.dtype == torch.int32)
+    _check(lib().ccb_sample_rows(_p(logits), logits.stride(0), _p(tokens), _p(temperature), _p(seed),
+                                 _p(out_index), R, V, _stream()), "sample_rows")

@@ -1,0 +1,94 @@
+"""Grouped-query attention over a paged cache.
+
+  [q|k|v] = x W_qkv^T (no bias); optional per-head RMSNorm of q and k over the
+  head axis, before the rotation; rotate-half position encoding of q and k; k
+  (rotated) and v go to the cache; q head h reads kv head h / (nq / nkv);
+  s = q.k / sqrt(hd), causal (optionally windowed) softmax, o = P v; a = o W_o^T
+  (7QiC/ccInfer: src/model/qwen3/qwen3_model.cpp:158-298).
+
+The three projections are one merged matrix (rows q, then k, then v), as the
+reference merges them at load (src/model/qwen3/qwen3_weights.cpp:16-43).  A
+layer that reads another layer's cache (``own_kv=False``) has only the q and
+o projections.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from ..errors import Unsupported
+from .base import CacheNeed, Mixer, PositionEncoding, TensorSpec
+
+
+class GroupedQueryAttention(Mixer):
+    def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position: PositionEncoding, names: dict, qk_norm_eps: Optional[float] = None,
+                 window: Optional[int] = None, own_kv: bool = True, scale: Optional[float] = None):
+        """``names``: tensor names under the keys q, k, v, o and (with qk_norm_eps) q_norm, k_norm."""
+        if num_heads % num_kv_heads:
+            raise Unsupported(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
+        if head_dim % 16 or head_dim > 256:
+            raise Unsupported(f"head size {head_dim}: the attention kernels take multiples of 16 up to 256")
+        if window is not None and window <= 0:
+            raise Unsupported("a window must be > 0")
+        self.hidden, self.nq, self.nkv, self.hd = int(hidden), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.position, self.names = position, dict(names)
+        self.qk_norm_eps, self.window, self.own_kv = qk_norm_eps, window, own_kv
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.q_width, self.kv_width = self.nq * self.hd, self.nkv * self.hd
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+        self.rt = None
+
+    # -- what it wants ---------------------------------------------------------
+    def tensor_specs(self):
+        n, D = self.names, self.hidden
+        specs = [TensorSpec(n["q"], (self.q_width, D)), TensorSpec(n["o"], (D, self.q_width))]
+        if self.own_kv:
+            specs += [TensorSpec(n["k"], (self.kv_width, D)), TensorSpec(n["v"], (self.kv_width, D))]
+        if self.qk_norm_eps is not None:
+            specs.append(TensorSpec(n["q_norm"], (self.hd,), role="vector", init="one_plus_normal"))
+            if self.own_kv:
+                specs.append(TensorSpec(n["k_norm"], (self.hd,), role="vector", init="one_plus_normal"))
+        return specs
+
+    def cache_need(self):
+        return CacheNeed(kv_heads=self.nkv, head_dim=self.hd, window=self.window)
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+        n = self.names
+        if self.own_kv:
+            self.w_qkv = torch.cat([fetch(n["q"]), fetch(n["k"]), fetch(n["v"])], dim=0).contiguous()
+        else:
+            self.w_qkv = fetch(n["q"])
+        self.w_o = fetch(n["o"])
+        if self.qk_norm_eps is not None:
+            self.q_norm_w = fetch(n["q_norm"])
+            self.k_norm_w = fetch(n["k_norm"]) if self.own_kv else None
+        self.position.bind(rt, fetch)
+
+    # -- a step ----------------------------------------------------------------
+    def forward(self, x, step, cache, state):
+        rt = self.rt
+        T = x.shape[0]
+        nkv_w = self.nkv if self.own_kv else 0
+        width = self.q_width + 2 * nkv_w * self.hd
+        qkv = rt.scratch.get("attn_qkv", (rt.max_tokens, width), rt.dtype)[:T]
+        rt.linear(qkv, x, self.w_qkv)
+        q = rt.scratch.get("attn_q", (rt.max_tokens, self.nq, self.hd), rt.dtype)[:T]
+        g = cache.group
+        kernels.qk_norm_rope_kv_write(
+            qkv, q, cache.k if self.own_kv else None, cache.v if self.own_kv else None, step.positions,
+            g.slot_map if self.own_kv else None, self.position.rotary_table(), self.q_norm_w, self.k_norm_w,
+            self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, self.nq, nkv_w, self.hd, g.page_size,
+            status=rt.status)
+        o = rt.scratch.get("attn_o", (rt.max_tokens, self.nq, self.hd), rt.dtype)[:T]
+        kernels.paged_attention_generic(q, cache.k, cache.v, o, step.positions, step.entry_of_token,
+                                        g.block_table, step.n_entries, self.window or 0, self.scale,
+                                        status=rt.status)
+        out = rt.scratch.get("attn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
+        rt.linear(out, o.view(T, self.q_width), self.w_o)
+        return out

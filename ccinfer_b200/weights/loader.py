@@ -1,0 +1,159 @@
+"""Weights by tensor name: checking, loading to the device, and the random-weights mode.
+
+As in 7QiC/ccInfer the model folder holds one ``model.safetensors``
+(src/worker/worker.cpp:256) and tensors are asked for by their HF names with
+an expected shape (src/model/loader.h:87-155).  Unlike the reference, which
+stops at the first missing tensor and never looks at the others, the whole
+file is compared with the model's wants first and ONE error lists every
+missing tensor, every unexpected one and every wrong shape.
+
+Types on the device: matrices in the compute type (bfloat16 for serving, float
+for the 32-bit path); per-channel vectors (norm weights) always in float, which
+holds a bfloat16 value exactly and leaves a tensor stored in 32 bits as it is;
+integer tables as int32.  A matrix stored in float is rounded to nearest-even
+when the compute type is bfloat16.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+from typing import Callable, Dict, List
+
+import torch
+
+from ..errors import ModelLoadFailed
+from ..parts.base import TensorSpec
+from .safetensors_io import SafetensorsFile, write_safetensors
+
+WEIGHTS_FILE = "model.safetensors"
+
+
+def check_tensors(specs: List[TensorSpec], entries: Dict[str, tuple], where: str) -> None:
+    """Raises ModelLoadFailed naming all missing, unexpected and mis-shaped tensors, or returns."""
+    wanted = {s.name: s for s in specs}
+    missing = sorted(n for n in wanted if n not in entries)
+    unexpected = sorted(n for n in entries if n not in wanted)
+    wrong = []
+    for n, s in wanted.items():
+        if n in entries and tuple(entries[n][1]) != tuple(s.shape):
+            wrong.append(f"{n}: file has {list(entries[n][1])}, model wants {list(s.shape)}")
+    bad_type = []
+    for n, s in wanted.items():
+        if n in entries:
+            integer = entries[n][0] in ("I32", "I64")
+            if integer != (s.role == "table"):
+                bad_type.append(f"{n}: stored as {entries[n][0]}, model wants "
+                                f"{'an integer table' if s.role == 'table' else 'floating point'}")
+    if not (missing or unexpected or wrong or bad_type):
+        return
+    lines = [f"{where} does not match the model:"]
+    if missing:
+        lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
+    if unexpected:
+        lines.append(f"  unexpected tensors ({len(unexpected)}): " + ", ".join(unexpected))
+    if wrong:
+        lines.append(f"  wrong shapes ({len(wrong)}): " + "; ".join(sorted(wrong)))
+    if bad_type:
+        lines.append(f"  wrong storage types ({len(bad_type)}): " + "; ".join(sorted(bad_type)))
+    raise ModelLoadFailed("\n".join(lines))
+
+
+def device_dtype(spec: TensorSpec, compute_dtype: torch.dtype) -> torch.dtype:
+    if spec.role == "vector":
+        return torch.float32
+    if spec.role == "table":
+        return torch.int32
+    return compute_dtype
+
+
+def open_weights(model_dir: str, specs: List[TensorSpec], device, compute_dtype,
+                 shared=()) -> Callable[[str], torch.Tensor]:
+    """Checks the folder's file against ``specs`` and returns ``fetch(name) -> device tensor``.
+
+    Names in ``shared`` (wanted by more than one part, like a tied head) are
+    copied once and handed out again; every other call makes a fresh copy that
+    the asking part owns."""
+    path = os.path.join(model_dir, WEIGHTS_FILE)
+    if not os.path.isfile(path):
+        raise ModelLoadFailed(f"{path} does not exist (the model folder holds config.json and {WEIGHTS_FILE})")
+    f = SafetensorsFile(path)
+    check_tensors(specs, f.entries, path)
+    by_name = {s.name: s for s in specs}
+    cache: Dict[str, torch.Tensor] = {}
+
+    def fetch(name: str) -> torch.Tensor:
+        if name in cache:
+            return cache[name]
+        spec = by_name[name]
+        t = f.tensor(name).to(device=device, dtype=device_dtype(spec, compute_dtype)).contiguous()
+        if name in shared:
+            cache[name] = t
+        return t
+
+    fetch.close = f.close  # type: ignore[attr-defined]
+    return fetch
+
+
+# ---------------------------------------------------------------------------------------------
+# random weights
+# ---------------------------------------------------------------------------------------------
+def _tensor_seed(seed: int, name: str) -> int:
+    d = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+    return int.from_bytes(d[:8], "little") & ((1 << 63) - 1)
+
+
+def random_tensor(spec: TensorSpec, seed: int, std: float, device="cpu") -> torch.Tensor:
+    """Float values of one tensor: N(0, std), or 1 + N(0, std) for norm weights.
+
+    The stream depends on (seed, tensor name) only, so a tensor's values do not
+    change with the order or the number of the others.
+    """
+    g = torch.Generator(device=device)
+    g.manual_seed(_tensor_seed(seed, spec.name))
+    if spec.role == "table":
+        raise ModelLoadFailed(f"no random rule for the integer table '{spec.name}'")
+    t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * std
+    if spec.init == "one_plus_normal":
+        t += 1.0
+    return t
+
+
+def write_random_model(model_dir: str, config, seed: int, std: float = 0.02, store_dtype: str = None) -> str:
+    """Writes ``config.json`` and ``model.safetensors`` for a typed configuration and a seed.
+
+    Values are drawn in float and stored in ``store_dtype`` ("bfloat16" or
+    "float32"; default: the configuration's torch_dtype).
+    """
+    from ..config.registry import architecture_of
+    cj = config.to_json()
+    arch = architecture_of(cj)
+    store_dtype = store_dtype or cj.get("torch_dtype", "bfloat16")
+    tdt = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}[store_dtype]
+    cj["torch_dtype"] = store_dtype
+    plan = arch.build_plan(config)
+    os.makedirs(model_dir, exist_ok=True)
+    tensors = {s.name: random_tensor(s, seed, std).to(tdt) for s in plan.tensor_specs()}
+    write_safetensors(os.path.join(model_dir, WEIGHTS_FILE), tensors,
+                      metadata={"format": "pt", "weights_seed": seed, "weights_std": std})
+    with open(os.path.join(model_dir, "config.json"), "w") as f:
+        json.dump(cj, f, indent=1)
+    return model_dir
+
+
+def random_fetch(specs: List[TensorSpec], seed: int, std: float, device, compute_dtype, shared=()):
+    """``fetch`` that draws every tensor on the device (no file; for measurements on large shapes)."""
+    by_name = {s.name: s for s in specs}
+    cache: Dict[str, torch.Tensor] = {}
+
+    def fetch(name: str) -> torch.Tensor:
+        if name in cache:
+            return cache[name]
+        spec = by_name[name]
+        t = random_tensor(spec, seed, std, device=device).to(device_dtype(spec, compute_dtype))
+        if name in shared:
+            cache[name] = t
+        return t
+
+    fetch.close = lambda: None  # type: ignore[attr-defined]
+    return fetch

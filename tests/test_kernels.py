@@ -1,0 +1,292 @@
+"""Each kernel alone against the plain function of the same op, at sizes other than the engine tests'."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# error relative to the largest reference value
+TOL = {"float32": 3e-6, "bfloat16": 1.2e-2}
+
+
+def _k():
+    from ccinfer_b200 import kernels
+    return kernels
+
+
+def _rel(got, ref):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert torch.isfinite(got).all()
+    return float((got - ref).abs().max() / ref.abs().max().clamp_min(1e-9))
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(shape, generator=g) * scale).to(dtype)
+    return x.cuda(), x.double()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,D,V", [(1, 80, 11), (37, 1000, 301), (5, 4096, 64)])
+def test_embed_gather(dtype, T, D, V):
+    table, ref = _rand((V, D), DT[dtype], 1)
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
+    h = torch.empty((T, D), dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _k().embed_gather(h, table, ids.cuda(), status)
+    assert torch.equal(h.cpu().double(), plain.embed(ref, ids.tolist()))
+    assert int(status.item()) == 0
+    bad = ids.clone()
+    bad[0] = V
+    _k().embed_gather(h, table, bad.cuda(), status)
+    assert int(status.item()) == _k().ST_BAD_TOKEN
+    assert float(h[0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,D,eps", [(3, 80, 1e-6), (17, 1000, 1e-5), (2, 5120, 3e-6)])
+def test_residual_rmsnorm(dtype, T, D, eps):
+    k = _k()
+    h0, h_ref = _rand((T, D), torch.float32, 3, 2.0)
+    delta, d_ref = _rand((T, D), DT[dtype], 4)
+    w, w_ref = _rand((D,), torch.float32, 5)
+    w_ref = w_ref + 1
+    w = (w + 1).contiguous()
+    # fused with the residual sum
+    h = h0.clone()
+    y = torch.empty((T, D), dtype=DT[dtype], device="cuda")
+    k.residual_rmsnorm(y, h, delta, w, eps)
+    ref_h = h_ref + d_ref
+    assert _rel(h, ref_h) <= 3e-7
+    assert _rel(y, plain.rms_norm(ref_h, w_ref, eps)) <= TOL[dtype]
+    # without a delta, h untouched
+    h = h0.clone()
+    k.residual_rmsnorm(y, h, None, w, eps)
+    assert torch.equal(h, h0)
+    assert _rel(y, plain.rms_norm(h_ref, w_ref, eps)) <= TOL[dtype]
+    # picked rows: h untouched, delta added on the fly
+    rows = torch.tensor([T - 1, 0, T - 1], dtype=torch.int32, device="cuda")
+    h = h0.clone()
+    yr = torch.empty((3, D), dtype=DT[dtype], device="cuda")
+    k.residual_rmsnorm(yr, h, delta, w, eps, row_idx=rows)
+    assert torch.equal(h, h0)
+    assert _rel(yr, plain.rms_norm(ref_h, w_ref, eps)[[T - 1, 0, T - 1]]) <= TOL[dtype]
+    # plain norm of a typed tensor
+    x, x_ref = _rand((T, 3, D), DT[dtype], 6)
+    y3 = torch.empty_like(x)
+    k.rmsnorm(y3, x, w, eps)
+    assert _rel(y3, plain.rms_norm(x_ref, w_ref, eps)) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,F", [(1, 7), (9, 208), (3, 12288)])
+def test_silu_mul(dtype, T, F):
+    gu, ref = _rand((T, 2 * F), DT[dtype], 7, 3.0)
+    act = torch.empty((T, F), dtype=DT[dtype], device="cuda")
+    _k().silu_mul(act, gu)
+    g, u = ref[:, :F], ref[:, F:]
+    assert _rel(act, g / (1 + torch.exp(-g)) * u) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 17, 33), (5, 301, 80), (33, 130, 257), (70, 64, 12), (130, 500, 96)])
+def test_gemm_f32(M, N, K):
+    a, a_ref = _rand((M, K), torch.float32, 8)
+    w, w_ref = _rand((N, K), torch.float32, 9)
+    c = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    _k().gemm_f32(c, a, w)
+    assert _rel(c, a_ref @ w_ref.T) <= 2e-6
+    # a row's result does not depend on the other rows of the batch
+    c1 = torch.empty((1, N), dtype=torch.float32, device="cuda")
+    _k().gemm_f32(c1, a[M - 1:M].contiguous(), w)
+    assert torch.equal(c1[0], c[M - 1])
+
+
+@pytest.mark.parametrize("out", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 24, 40), (7, 304, 80), (64, 1000, 256), (200, 96, 512)])
+def test_gemm_bf16(out, M, N, K):
+    k = _k()
+    handle = k.CublasHandle(torch.device("cuda:0"))
+    a, a_ref = _rand((M, K), torch.bfloat16, 10)
+    w, w_ref = _rand((N, K), torch.bfloat16, 11)
+    c = torch.empty((M, N), dtype=DT[out], device="cuda")
+    handle.gemm_bf16(c, a, w)
+    assert _rel(c, a_ref @ w_ref.T) <= (1e-5 if out == "float32" else 8e-3)
+    handle.close()
+
+
+def _paged_case(dtype, lens_ctx, lens_new, nq, nkv, hd, P, seed, window=None, peak=None):
+    """Random keys in a shuffled page pool; returns inputs of the attention kernel and the plain result.
+
+    ``peak`` = (entry, key position): that key and the entry's last query are scaled so that this one
+    score stands out, which shows whether a far key or a key on a page's edge is really read."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens_ctx)
+    total_pages = sum(-(-(c + n) // P) for c, n in zip(lens_ctx, lens_new)) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    stride = max(-(-(c + n) // P) for c, n in zip(lens_ctx, lens_new)) + 1
+    k_cache = torch.zeros((total_pages, nkv, P, hd))
+    v_cache = torch.zeros((total_pages, nkv, P, hd))
+    # stale data everywhere: what is not a visible key must not matter
+    k_cache.normal_(generator=g).mul_(5)
+    v_cache.normal_(generator=g).mul_(5)
+    bt = torch.full((B, stride), -1, dtype=torch.int32)
+    qs, pos, eot, refs = [], [], [], []
+    for b, (c, n) in enumerate(zip(lens_ctx, lens_new)):
+        L = c + n
+        k = torch.randn((L, nkv, hd), generator=g)
+        v = torch.randn((L, nkv, hd), generator=g)
+        q = torch.randn((L, nq, hd), generator=g)
+        if peak is not None and peak[0] == b:
+            k[peak[1]] *= 6.0
+            q[L - 1] = k[peak[1]].repeat_interleave(nq // nkv, dim=0) * 1.0
+        k, v, q = (t.to(DT[dtype]).float() for t in (k, v, q))
+        for lp in range(-(-L // P)):
+            page = perm.pop()
+            bt[b, lp] = page
+            lo, hi = lp * P, min(L, lp * P + P)
+            k_cache[page, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            v_cache[page, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+        ref = plain.causal_attention(q.double(), k.double(), v.double(), window)
+        refs.append(ref[c:])
+        qs.append(q[c:])
+        pos += list(range(c, L))
+        eot += [b] * n
+    dev = lambda t, dt=None: (t.to(dt) if dt else t).cuda().contiguous()
+    return (dev(torch.cat(qs), DT[dtype]), dev(k_cache, DT[dtype]), dev(v_cache, DT[dtype]),
+            dev(torch.tensor(pos, dtype=torch.int32)), dev(torch.tensor(eot, dtype=torch.int32)), dev(bt),
+            torch.cat(refs))
+
+
+ATTN_CASES = [
+    # ctx, new, nq, nkv, hd, page, window
+    ([0], [1], 2, 1, 16, 4, None),
+    ([0, 5, 31], [9, 1, 2], 6, 3, 48, 8, None),
+    ([100, 0, 63], [1, 70, 1], 8, 2, 64, 16, None),
+    ([0, 40, 129], [33, 3, 1], 4, 4, 80, 16, 24),
+    ([300], [1], 16, 2, 128, 16, None),
+    ([17, 250], [40, 1], 5, 1, 256, 32, 100),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_paged_attention_generic(dtype, case):
+    ctx, new, nq, nkv, hd, P, window = case
+    q, kc, vc, pos, eot, bt, ref = _paged_case(dtype, ctx, new, nq, nkv, hd, P, seed=hd + len(ctx), window=window)
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _k().paged_attention_generic(q, kc, vc, out, pos, eot, bt, len(ctx), window or 0, 1 / math.sqrt(hd), status)
+    assert int(status.item()) == 0
+    assert _rel(out, ref) <= (1e-5 if dtype == "float32" else 1.5e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far_key", [0, 15, 16, 255, 256, 257, 511])
+def test_attention_reads_far_key(dtype, far_key):
+    """One key among hundreds carries the whole output: its value must come through."""
+    nq, nkv, hd, P = 4, 2, 64, 16
+    L = 600
+    q, kc, vc, pos, eot, bt, ref = _paged_case(dtype, [L - 1], [1], nq, nkv, hd, P, seed=far_key,
+                                               peak=(0, far_key))
+    out = torch.empty_like(q)
+    _k().paged_attention_generic(q, kc, vc, out, pos, eot, bt, 1, 0, 1 / math.sqrt(hd))
+    assert _rel(out, ref) <= (1e-5 if dtype == "float32" else 1.5e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("edge", [-1, 0, 1])
+def test_attention_window_edge(dtype, edge):
+    """The strongest key sits just outside, on, and just inside the window's edge."""
+    nq, nkv, hd, P, W = 2, 1, 32, 8, 40
+    L = 200
+    key = (L - 1) - W + 1 + edge  # edge -1: the first key that is no longer seen
+    q, kc, vc, pos, eot, bt, ref = _paged_case(dtype, [L - 1], [1], nq, nkv, hd, P, seed=7, window=W,
+                                               peak=(0, key))
+    out = torch.empty_like(q)
+    _k().paged_attention_generic(q, kc, vc, out, pos, eot, bt, 1, W, 1 / math.sqrt(hd))
+    assert _rel(out, ref) <= (1e-5 if dtype == "float32" else 1.5e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,hd,P,theta", [(4, 2, 16, 4, 1e4), (6, 3, 48, 8, 5e4), (8, 2, 128, 16, 1e6),
+                                                 (3, 1, 256, 16, 1e6)])
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, hd, P, theta):
+    k = _k()
+    T, eps = 11, 1e-6
+    pages = 9
+    qkv, ref = _rand((T, (nq + 2 * nkv) * hd), DT[dtype], 12)
+    qw, qw_ref = _rand((hd,), torch.float32, 13)
+    kw, kw_ref = _rand((hd,), torch.float32, 14)
+    qw, kw, qw_ref, kw_ref = qw + 1, kw + 1, qw_ref + 1, kw_ref + 1
+    positions = torch.tensor([0, 1, 2, 3, 900, 901, 17, 4000, 5, 6, 7], dtype=torch.int32)
+    slots = torch.randperm(pages * P, generator=torch.Generator().manual_seed(15))[:T].to(torch.int32)
+    slots[3] = -1  # a padded row: nothing is cached for it
+    inv_freq = plain.rope_inv_freq(hd, theta)
+    q_out = torch.empty((T, nq, hd), dtype=DT[dtype], device="cuda")
+    kc = torch.zeros((pages, nkv, P, hd), dtype=DT[dtype], device="cuda")
+    vc = torch.zeros_like(kc)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.qk_norm_rope_kv_write(qkv, q_out, kc, vc, positions.cuda(), slots.cuda(), inv_freq.cuda(), qw, kw, eps,
+                            nq, nkv, hd, P, status)
+    assert int(status.item()) == 0
+    q_ref = ref[:, :nq * hd].view(T, nq, hd)
+    k_ref = ref[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd)
+    v_ref = ref[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    q_ref = plain.apply_rope(plain.rms_norm(q_ref, qw_ref, eps), positions, inv_freq)
+    k_ref = plain.apply_rope(plain.rms_norm(k_ref, kw_ref, eps), positions, inv_freq)
+    tol = 2e-6 if dtype == "float32" else 1.2e-2
+    assert _rel(q_out, q_ref) <= tol
+    kc_h, vc_h = kc.cpu().double(), vc.cpu().double()
+    written = torch.zeros(pages * P, dtype=torch.bool)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        written[s] = True
+        assert float((kc_h[s // P, :, s % P] - k_ref[t]).abs().max()) <= tol * float(k_ref.abs().max())
+        assert float((vc_h[s // P, :, s % P] - v_ref[t]).abs().max()) == 0.0  # v is copied as it is
+    untouched = ~written
+    assert float(kc_h.transpose(1, 2).reshape(pages * P, -1)[untouched].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("V", [11, 500, 151936])
+def test_sampling(V):
+    k = _k()
+    R = 5
+    g = torch.Generator().manual_seed(16)
+    logits = torch.randn((R, V), generator=g)
+    logits[1, V // 2] = logits[1].max() + 1  # a clear winner
+    logits[2, 3] = logits[2, V - 1] = logits[2].max() + 2  # a tie: the lowest id wins
+    tokens = torch.zeros(R, dtype=torch.int32, device="cuda")
+    k.sample_rows(logits.cuda(), tokens)
+    want = [plain.greedy(logits[r]) for r in range(R)]
+    assert tokens.tolist() == want and want[2] == 3
+    temps = torch.tensor([0.0, 0.8, 1.5, 0.3, 1.0])
+    seeds = torch.tensor([7, 7, 42, 123456789, -5], dtype=torch.int32)
+    idx = torch.tensor([0, 3, 1, 250, 9], dtype=torch.int32)
+    k.sample_rows(logits.cuda(), tokens, temps.cuda(), seeds.cuda(), idx.cuda())
+    want = [plain.sample_temperature(logits[r], float(temps[r]), int(seeds[r]) & 0xFFFFFFFF, int(idx[r]))
+            for r in range(R)]
+    assert tokens.tolist() == want
+
+
+def test_sampling_distribution():
+    """Temperature draws follow softmax(logits / T): chi-square over a 12-symbol vocabulary."""
+    k = _k()
+    V, n, T = 12, 20000, 0.7
+    logits = torch.linspace(-1.5, 1.5, V)
+    p = torch.softmax(logits.double() / T, dim=0).numpy()
+    rows = logits[None, :].expand(n, V).contiguous().cuda()
+    tokens = torch.zeros(n, dtype=torch.int32, device="cuda")
+    temps = torch.full((n,), T, device="cuda")
+    seeds = torch.full((n,), 99, dtype=torch.int32, device="cuda")
+    idx = torch.arange(n, dtype=torch.int32, device="cuda")
+    k.sample_rows(rows, tokens, temps, seeds, idx)
+    counts = np.bincount(tokens.cpu().numpy(), minlength=V)
+    chi2 = float(((counts - n * p) ** 2 / (n * p)).sum())
+    assert chi2 < 40.0, chi2  # 11 degrees of freedom: 40 is far in the tail (p < 1e-4)
