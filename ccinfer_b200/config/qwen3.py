@@ -170,7 +170,6 @@ class Qwen3Config:
             "rope_scaling": None,
             "use_sliding_window": self.use_sliding_window,
             "sliding_window": self.sliding_window,
-            "max_window_layers": self.max_window_layers
-            if self.max_window_layers is not None else self.num_hidden_layers,
+            "max_window_layers": self.max_window_layers,
         }
         return j

@@ -116,8 +116,11 @@ class Engine:
         self._host_events = [None, None]
         self._host_turn = 0
         self._dev_buf = torch.zeros(lay.size, dtype=torch.int32, device=rt.device)
+        n_rows = max(opt.max_requests, 1)
+        self._sample_tokens = torch.zeros(opt.max_tokens_per_step, dtype=torch.int32, device=rt.device)
+        self._sample_host = torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32).pin_memory()
+        self._sample_dev = torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32, device=rt.device)
         self.steps_run = 0
-        self.kernel_launch_estimate = 0
 
     # ------------------------------------------------------------------------------------
     @classmethod
@@ -320,6 +323,31 @@ class Engine:
         if logits is None:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.rt.device)
         return logits
+
+    def sample(self, logits: torch.Tensor, params: Sequence, out_index: Sequence[int]) -> List[int]:
+        """One token per logits row: greedy where temperature <= 0, else a temperature draw.
+
+        ``params[r]`` has ``temperature`` and ``seed``; ``out_index[r]`` is how many tokens the
+        row's request has produced so far.  A draw depends on (seed, out_index) only, not on the
+        batch.  Returns host integers (this waits for the step).
+        """
+        R = logits.shape[0]
+        if R == 0:
+            return []
+        if len(params) != R or len(out_index) != R:
+            raise InvalidArgument("one parameter set and one output index per logits row")
+        tokens = self._sample_tokens[:R]
+        if all(p.temperature <= 0 for p in params):
+            kernels.sample_rows(logits, tokens)
+        else:
+            hp = self._sample_host
+            hp[0, :R] = torch.tensor([float(p.temperature) for p in params], dtype=torch.float32).view(torch.int32)
+            hp[1, :R] = torch.tensor([int(p.seed) & 0xFFFFFFFF for p in params], dtype=torch.int64).to(torch.int32)
+            hp[2, :R] = torch.tensor(list(out_index), dtype=torch.int32)
+            self._sample_dev.copy_(hp, non_blocking=True)
+            d = self._sample_dev
+            kernels.sample_rows(logits, tokens, d[0, :R].view(torch.float32), d[1, :R], d[2, :R])
+        return tokens.tolist()
 
     def check(self) -> None:
         """Synchronises and raises DeviceFault if a kernel reported a bad index since the last check."""

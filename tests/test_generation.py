@@ -1,0 +1,138 @@
+"""Generation through the entry points against the plain implementation: Python, command line, trace replay."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def model_a(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("genA"))
+    cfg, w, page = helpers.make_model_dir(d, "A")
+    return d, cfg, w, page
+
+
+@pytest.fixture(scope="module")
+def model_b(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("genB"))
+    cfg, w, page = helpers.make_model_dir(d, "B", store="float32")
+    return d, cfg, w, page
+
+
+def _prompts(cfg, lengths, seed):
+    rng = np.random.RandomState(seed)
+    return [rng.randint(0, cfg["vocab_size"], size=n).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_tiny_a(model_a, dtype):
+    """Three requests, prompts of 5, 11 and 17 tokens, 8 greedy tokens each, pages of 4."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, page = model_a
+    prompts = _prompts(cfg, [5, 11, 17], 0)
+    llm = LLM(d, dtype=dtype, page_size=page, kv_tokens=128, max_requests=4, max_tokens_per_step=64)
+    got = llm.generate(prompts, SamplingParams(max_tokens=8))
+    want = [plain.generate(cfg, w, p, 8) for p in prompts]
+    assert got == want
+    assert all(p.used_pages == 0 for p in llm.engine.cache.pools)
+
+
+def test_temperature_generation_tiny_b_in_portions(model_b):
+    """Four requests, prompts of 1, 9, 33 and 64 tokens in portions of 7 beside running decodes,
+    12 tokens each at temperature 0.8 with seed 7, pages of 8."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, page = model_b
+    prompts = _prompts(cfg, [1, 9, 33, 64], 1)
+    llm = LLM(d, dtype="float32", page_size=page, kv_tokens=512, prefill_chunk_size=7, max_requests=4,
+              max_tokens_per_step=64)
+    got = llm.generate(prompts, SamplingParams(max_tokens=12, temperature=0.8, seed=7))
+    want = [plain.generate(cfg, w, p, 12, temperature=0.8, seed=7) for p in prompts]
+    assert got == want
+    assert got != [plain.generate(cfg, w, p, 12) for p in prompts]  # it is not greedy in disguise
+
+
+def test_pages_run_out_during_generation(model_b):
+    """So few pages that a request is preempted and computed again: the tokens are those of a calm run."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, page = model_b
+    prompts = _prompts(cfg, [20, 26, 17], 2)
+    sp = [SamplingParams(max_tokens=24, temperature=0.6, seed=5), SamplingParams(max_tokens=20),
+          SamplingParams(max_tokens=28, temperature=1.1, seed=9)]
+    llm = LLM(d, dtype="float32", page_size=page, kv_tokens=13 * page, prefill_chunk_size=16, max_requests=4,
+              max_tokens_per_step=64)
+    got = llm.generate(prompts, sp)
+    assert llm.scheduler.preemptions > 0
+    want = [plain.generate(cfg, w, p, s.max_tokens, s.temperature, s.seed) for p, s in zip(prompts, sp)]
+    assert got == want
+    llm.engine.cache.check_consistency()
+
+
+def test_long_decoding_and_first_tokens(model_b):
+    """A one-token prompt decoded far, every position compared; and the first tokens of a sequence."""
+    from ccinfer_b200.engine.engine import Engine, EngineOptions
+    d, cfg, w, page = model_b
+    toks = _prompts(cfg, [230], 3)[0]
+    ref = helpers.plain_logits(cfg, w, toks)
+    for dtype, tol in (("float32", 2e-5), ("bfloat16", 3e-2)):
+        eng = Engine.from_model_dir(d, EngineOptions(dtype=dtype, page_size=page, kv_tokens=256, max_requests=2,
+                                                     max_tokens_per_step=32))
+        steps = [{"entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": []} for t in toks]
+        rows = helpers.replay(eng, steps)
+        helpers.compare(rows, {"x": ref}, tol, f"long decoding {dtype}")
+        first = {k: v for k, v in rows.items() if k[1] < 4}
+        helpers.compare(first, {"x": ref}, tol, f"first tokens {dtype}")
+
+
+def test_command_line(model_a):
+    d, cfg, w, page = model_a
+    prompt = _prompts(cfg, [9], 4)[0]
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "ccinfer"), "--model-path", d, "--dtype", "float32",
+           "--prefill-chunk-size", "4", "--page-size", str(page), "--kv-tokens", "64", "--max-tokens", "5",
+           "--prompt-ids", ",".join(map(str, prompt)), "--stats"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["token_ids"] == plain.generate(cfg, w, prompt, 5)
+    bad = subprocess.run(cmd[:2] + ["--model-path", "/nonexistent", "--prompt-ids", "1"], capture_output=True,
+                         text=True, timeout=300)
+    assert bad.returncode == 2 and "ModelLoadFailed" in bad.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_b, dtype, tmp_path):
+    """bin/trace_run as a user calls it: a mixed trace over a small pool, files compared with the plain logits."""
+    d, cfg, w, page = model_b
+    reqs = {f"q{i}": p for i, p in enumerate(_prompts(cfg, [40, 3, 75, 64, 18], 5))}
+    steps = helpers.trace_mixed(reqs, max_live=4, seed=2)
+    pool = helpers.max_live_tokens(steps)
+    out_dir = tmp_path / "out"
+    lines = "".join(json.dumps({"step": i, **st}) + "\n" for i, st in enumerate(steps))
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out",
+                        str(out_dir), "--max-tokens", str(pool)], input=lines, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.split() == [x for i in range(len(steps)) for x in ("done", str(i))]
+    ref = {rid: helpers.plain_logits(cfg, w, toks) for rid, toks in reqs.items()}
+    V = cfg["vocab_size"]
+    rows, seen = {}, {rid: 0 for rid in reqs}
+    for i, st in enumerate(steps):
+        n_want = sum(len(e["want"]) for e in st["entries"])
+        arr = np.fromfile(out_dir / f"{i}.f32", dtype="<f4").reshape(n_want, V)
+        r_ = 0
+        for e in st["entries"]:
+            for wnt in e["want"]:
+                rows[(e["id"], seen[e["id"]] + wnt)] = arr[r_]
+                r_ += 1
+            seen[e["id"]] += len(e["tokens"])
+    assert len(rows) == sum(len(t) for t in reqs.values())
+    helpers.compare(rows, ref, 2e-5 if dtype == "float32" else 3e-2, f"trace_run {dtype}")

@@ -1,0 +1,209 @@
+"""The scheduler's decisions (no GPU), driven with a fake engine that has a real cache manager.
+
+The cases follow 7QiC/ccInfer's tests/unit/test_scheduler.cpp: decodes batched, decode before prefill in a
+mixed step (:296-329), round robin, 512-token portions (:387-441), the cap on started requests (:443-496),
+replay without sampling (:498-548); and add what the reference does not decide: mixed sampling parameters in
+one step, and what happens when pages run out.
+"""
+import hashlib
+
+import pytest
+
+from ccinfer_b200.cache.manager import CacheManager, GroupSpec
+from ccinfer_b200.engine.scheduler import Scheduler
+from ccinfer_b200.errors import InvalidArgument, KVBlockExhausted, RequestTooLong, Unsupported
+from ccinfer_b200.sampling import SamplingParams
+
+
+class FakeEngine:
+    """Logits of a position are a hash of all tokens up to it; a draw depends on (hash, seed, out_index)."""
+
+    def __init__(self, pages=64, page=4, slots=8, max_context=None, window=None):
+        groups = [GroupSpec(("all",), None, page, pages)]
+        if window:
+            groups.append(GroupSpec(("window", window), window, page, pages))
+        self.cache = CacheManager(groups, slots)
+        self.max_context = max_context or pages * page
+        self.history = {}
+        self.steps = []
+
+    def open_request(self, rid):
+        self.cache.open(rid)
+        self.history[rid] = []
+
+    def close_request(self, rid):
+        self.cache.close(rid)
+        del self.history[rid]
+
+    def step(self, entries):
+        self.steps.append([(e.req_id, list(e.tokens), list(e.want)) for e in entries])
+        reserved = []
+        try:
+            for e in entries:
+                self.cache.reserve(e.req_id, len(e.tokens))
+                reserved.append(e.req_id)
+        except KVBlockExhausted:
+            for rid in reserved:
+                self.cache.rollback(rid)
+            raise
+        rows = []
+        for e in entries:
+            self.cache.commit(e.req_id)
+            h = self.history[e.req_id]
+            for i, t in enumerate(e.tokens):
+                h.append(t)
+                if i in e.want:
+                    rows.append(hashlib.sha256(repr(h).encode()).hexdigest())
+        self.cache.check_consistency()
+        return _Rows(rows)
+
+    def sample(self, logits, params, out_index):
+        out = []
+        for row, p, i in zip(logits.rows, params, out_index):
+            key = row if p.temperature <= 0 else f"{row}:{p.seed}:{i}:{p.temperature}"
+            out.append(int(hashlib.sha256(key.encode()).hexdigest(), 16) % 1000)
+        return out
+
+
+class _Rows:
+    def __init__(self, rows):
+        self.rows = rows
+        self.shape = (len(rows), 1000)
+
+
+def _prompt(n, base=0):
+    return [(base + 7 * i) % 997 for i in range(n)]
+
+
+def test_decodes_are_batched_and_come_first():
+    eng = FakeEngine()
+    s = Scheduler(eng, prefill_chunk_size=8)
+    s.submit("a", _prompt(5), SamplingParams(max_tokens=4))
+    s.submit("b", _prompt(6, 100), SamplingParams(max_tokens=4))
+    s.step()  # both prompts whole
+    assert [(rid, len(t)) for rid, t, _ in eng.steps[-1]] == [("a", 5), ("b", 6)]
+    s.submit("c", _prompt(20, 200), SamplingParams(max_tokens=2))
+    s.step()
+    kinds = [(rid, len(t), w) for rid, t, w in eng.steps[-1]]
+    assert kinds == [("a", 1, [0]), ("b", 1, [0]), ("c", 8, [])]  # decodes first, then a portion without logits
+    s.step()
+    s.step()
+    assert eng.steps[-1][-1] == ("c", _prompt(20, 200)[16:], [3])  # the last portion wants its last position
+
+
+def test_portions_and_token_budget():
+    eng = FakeEngine(pages=1024, page=16)
+    s = Scheduler(eng, prefill_chunk_size=512, max_tokens_per_step=600)
+    s.submit("a", _prompt(1100), SamplingParams(max_tokens=1))
+    s.submit("b", _prompt(300, 5), SamplingParams(max_tokens=1))
+    s.step()
+    assert [(rid, len(t)) for rid, t, _ in eng.steps[-1]] == [("a", 512), ("b", 88)]  # 600 in all
+    s.step()
+    assert [(rid, len(t)) for rid, t, _ in eng.steps[-1]] == [("a", 512), ("b", 88)]
+    whole = Scheduler(FakeEngine(pages=1024, page=16), prefill_chunk_size=0)
+    whole.submit("a", _prompt(1100), SamplingParams(max_tokens=1))
+    whole.step()
+    assert len(whole.engine.steps[-1][0][1]) == 1100  # 0 = whole prompts
+
+
+def test_round_robin_when_the_budget_is_short():
+    eng = FakeEngine(pages=256, page=16)
+    s = Scheduler(eng, prefill_chunk_size=16, max_tokens_per_step=16)
+    for i in range(3):
+        s.submit(f"r{i}", _prompt(40, i), SamplingParams(max_tokens=1))
+    ran = []
+    for _ in range(6):
+        s.step()
+        ran.append(eng.steps[-1][0][0])
+    assert ran == ["r0", "r1", "r2", "r0", "r1", "r2"]
+
+
+def test_cap_on_started_requests():
+    eng = FakeEngine(pages=512, page=4, slots=8)
+    s = Scheduler(eng, prefill_chunk_size=4, max_running=2)
+    for i in range(4):
+        s.submit(f"r{i}", _prompt(10, i), SamplingParams(max_tokens=3))
+    s.step()
+    assert [rid for rid, _, _ in eng.steps[-1]] == ["r0", "r1"]  # two started; the others wait their turn
+    out = s.run()
+    assert sorted(out) == ["r0", "r1", "r2", "r3"] and all(len(v) == 3 for v in out.values())
+
+
+def test_max_tokens_context_limit_eos_and_cancel():
+    eng = FakeEngine(pages=8, page=4, max_context=12)
+    s = Scheduler(eng)
+    s.submit("zero", _prompt(3), SamplingParams(max_tokens=0))
+    s.submit("long", _prompt(10), SamplingParams(max_tokens=50))
+    ev = s.step()
+    assert ev[0].req_id == "zero" and ev[0].finished and ev[0].token is None
+    events = list(ev)
+    while s.has_work():
+        events += s.step()
+    toks = [e.token for e in events if e.req_id == "long" and e.token is not None]
+    assert len(toks) == 3  # contexts 10, 11 and 12 gave a token each; a 13th position does not exist
+    assert events[-1].finished and events[-1].reason == "max_context"
+    assert eng.cache.stats()["groups"][0]["pages_used"] == 0
+    with pytest.raises(RequestTooLong):
+        s.submit("huge", _prompt(13))
+    with pytest.raises(InvalidArgument):
+        s.submit("empty", [])
+    with pytest.raises(InvalidArgument):
+        s.submit("neg", [1, -2])
+    with pytest.raises(Unsupported):
+        s.submit("topk", _prompt(3), SamplingParams(top_k=5))
+    s.submit("x", _prompt(4), SamplingParams(max_tokens=30))
+    s.step()
+    with pytest.raises(InvalidArgument):
+        s.submit("x", _prompt(4))
+    assert s.cancel("x") and not s.cancel("x") and not s.has_work()
+    assert eng.cache.stats()["slots_free"] == 8
+    # eos
+    eng2 = FakeEngine()
+    probe = Scheduler(eng2)
+    probe.submit("p", _prompt(6), SamplingParams(max_tokens=5))
+    full = probe.run()["p"]
+    s2 = Scheduler(FakeEngine(), eos_token_id=full[2])
+    s2.submit("p", _prompt(6), SamplingParams(max_tokens=5))
+    assert s2.run()["p"] == full[:3]
+
+
+def test_greedy_and_temperature_share_a_step():
+    eng = FakeEngine()
+    s = Scheduler(eng)
+    s.submit("g", _prompt(5), SamplingParams(max_tokens=3))
+    s.submit("t", _prompt(5), SamplingParams(max_tokens=3, temperature=0.8, seed=7))
+    out = s.run()
+    assert all(len(step) == 2 for step in eng.steps)  # never skipped for differing parameters
+    assert out["g"] != out["t"]
+
+
+@pytest.mark.parametrize("window", [None, 6])
+def test_pages_run_out_preempts_the_youngest_and_tokens_do_not_change(window):
+    reqs = {"a": (_prompt(9, 1), 14), "b": (_prompt(11, 2), 12), "c": (_prompt(7, 3), 16)}
+
+    def run(pages):
+        eng = FakeEngine(pages=pages, page=4, window=window)
+        s = Scheduler(eng, prefill_chunk_size=8)
+        for rid, (p, n) in reqs.items():
+            s.submit(rid, p, SamplingParams(max_tokens=n, temperature=0.5, seed=3))
+        out = s.run()
+        assert all(p.used_pages == 0 for p in eng.cache.pools)
+        return out, s.preemptions, eng
+
+    calm, n0, _ = run(pages=64)
+    tight, n1, eng = run(pages=9)  # all three do not fit at their final lengths (6 + 6 + 6 pages)
+    assert n0 == 0 and n1 > 0
+    assert tight == calm
+    # the oldest request was never computed again: its tokens entered the cache exactly once
+    fed = [t for step in eng.steps for rid, toks, _ in step if rid == "a" for t in toks]
+    assert len(fed) == len(reqs["a"][0]) + reqs["a"][1] - 1
+    # a replayed prompt's last portion asks for no logits when a token is already known
+    assert any(rid != "a" and len(toks) > 1 and not want for step in eng.steps for rid, toks, want in step)
+
+
+def test_a_request_that_cannot_fit_alone_fails_loudly():
+    eng = FakeEngine(pages=3, page=4, max_context=1000)
+    s = Scheduler(eng)
+    s.submit("a", _prompt(10), SamplingParams(max_tokens=20))
+    with pytest.raises(KVBlockExhausted):
+        s.run()
