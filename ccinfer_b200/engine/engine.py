@@ -121,6 +121,8 @@ class Engine:
         self._sample_host = torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32).pin_memory()
         self._sample_dev = torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32, device=rt.device)
         self.steps_run = 0
+        self.graph_replays = 0
+        self._graphs: Dict[int, tuple] = {}
 
     # ------------------------------------------------------------------------------------
     @classmethod
@@ -222,7 +224,10 @@ class Engine:
         posv[T:Tp] = 0
         eot[T:Tp] = -1
 
-        rows = [int(cu[b]) + int(w) for b, e in enumerate(entries) for w in e.want]
+        if pad_to:  # a decode step padded to a graph's size: one row per entry, the padding's rows are ignored
+            rows = list(range(Bp))
+        else:
+            rows = [int(cu[b]) + int(w) for b, e in enumerate(entries) for w in e.want]
         R = len(rows)
         lr = host[lay.o_logit_rows:lay.o_logit_rows + max(R, 1)]
         if R:
@@ -296,6 +301,40 @@ class Engine:
         x = plan.final_norm.fold(stream, rows=step.logit_rows, n_rows=step.n_logit_rows)
         return plan.head.forward(x)
 
+    # -- decode steps replayed from CUDA graphs ------------------------------------------------
+    def _graph_bucket(self, entries: List[StepEntry]) -> int:
+        """Size of the graph a step can be replayed from: 0 unless every entry is one token wanting its logits."""
+        if not (self.options.use_graphs and self.graph_safe):
+            return 0
+        for e in entries:
+            if len(e.tokens) != 1 or list(e.want) != [0]:
+                return 0
+        b = 1
+        while b < len(entries):
+            b *= 2
+        return b if b <= self.options.max_requests else 0
+
+    def _replay_decode(self, entries: List[StepEntry], bucket: int) -> torch.Tensor:
+        """A decode step of up to ``bucket`` requests: the step arrays are copied, the kernels replayed.
+
+        The launch sequence of a decode step depends on the number of rows only, and every buffer it
+        touches has a fixed address, so it is captured once per size (rows beyond the live requests
+        are padding: they cache nothing and attend to nothing)."""
+        step = self._build(entries, pad_to=bucket)
+        if bucket not in self._graphs:
+            self._forward(step)  # once eagerly: every scratch buffer exists before the capture
+            graph = torch.cuda.CUDAGraph()
+            own0, lib0 = kernels.counters.own, kernels.counters.library
+            with torch.cuda.graph(graph):
+                out = self._forward(step)
+            self._graphs[bucket] = (graph, out, kernels.counters.own - own0, kernels.counters.library - lib0)
+        graph, out, n_own, n_lib = self._graphs[bucket]
+        graph.replay()
+        kernels.counters.own += n_own      # a replay launches what the capture recorded
+        kernels.counters.library += n_lib
+        self.graph_replays += 1
+        return out[:len(entries)]
+
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the tokens given, as one batch, from the cache; returns float logits [wanted, vocab].
 
@@ -311,8 +350,12 @@ class Engine:
             for e in entries:
                 self.cache.reserve(e.req_id, len(e.tokens))
                 reserved.append(e.req_id)
-            step = self._build(entries)
-            logits = self._forward(step)
+            bucket = self._graph_bucket(entries)
+            if bucket:
+                logits = self._replay_decode(entries, bucket)
+            else:
+                step = self._build(entries)
+                logits = self._forward(step)
         except BaseException:
             for rid in reserved:
                 self.cache.rollback(rid)

@@ -77,8 +77,21 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+class _Counters:
+    """Launches since import: ``own`` = kernels of this package, ``library`` = cuBLAS products."""
+    own = 0
+    library = 0
+
+
+counters = _Counters()
+
+
 def _check(code: int, what: str) -> None:
     if code == 0:
+        if what == "gemm_bf16":
+            counters.library += 1
+        elif not what.startswith("cublas"):
+            counters.own += 1
         return
     if code == -2:
         raise Unsupported(f"{what}: a size outside what the kernel takes")
