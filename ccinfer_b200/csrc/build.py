@@ -33,6 +33,8 @@ GROUPS = {
         "norm.cu",
         "rope_kv.cu",
         "attention_generic.cu",
+        "attention_split.cu",
+        "attention_decode_mma.cu",
         "gemm_f32.cu",
         "gemm_cublas.cu",
         "sampling.cu",

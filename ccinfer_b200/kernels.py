@@ -44,6 +44,12 @@ _SIGNATURES = {
     "ccb_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                     c_void_p, c_void_p],
+    "ccb_attention_split": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                            c_int, c_void_p, c_void_p],
+    "ccb_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_float, c_int, c_void_p, c_void_p],
     "ccb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_cublas_create": [ctypes.POINTER(c_void_p)],
     "ccb_cublas_destroy": [c_void_p],
@@ -204,6 +210,75 @@ def paged_attention_generic(q, k_cache, v_cache, out, positions, entry_of_token,
                                              n_entries, T, nq, nkv, hd, page_size, num_pages, int(window),
                                              float(scale), _dt(q), _p(status), _stream()),
            "paged_attention_generic")
+
+
+SPLIT_TARGET_BLOCKS = 2 * 148   # blocks the split kernel aims for: two per SM
+SPLIT_MAX = 32
+
+
+def attention_split_heads_per_block(nq: int, nkv: int, hd: int) -> int:
+    g = nq // nkv
+    return 4 if (g >= 4 and hd <= 128) else (2 if g >= 2 else 1)
+
+
+def attention_split_plan(n_rows: int, nq: int, nkv: int, hd: int, heads_per_block: int = 0):
+    """(num_splits, scratch floats for the accumulators, scratch floats for max and sum).
+
+    The number of splits depends on the number of token rows only, so a step of a given size always
+    launches the same grid (and its results do not depend on the lengths in the batch)."""
+    gt = heads_per_block or attention_split_heads_per_block(nq, nkv, hd)
+    per_split = n_rows * nkv * -(-(nq // nkv) // gt)
+    splits = max(1, min(SPLIT_MAX, SPLIT_TARGET_BLOCKS // max(1, per_split)))
+    return splits, SPLIT_TARGET_BLOCKS * gt * hd, SPLIT_TARGET_BLOCKS * gt * 2
+
+
+def attention_split(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
+                    n_entries: int, row0: int, n_rows: int, window: int, scale: float, num_splits: int,
+                    status=None) -> None:
+    """Attention of the token rows row0 .. row0 + n_rows - 1, each a single query with its own position
+    and request; the key range is cut into ``num_splits`` pieces merged afterwards (scratch from
+    ``attention_split_plan``; unused with one split)."""
+    _cuda(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status)
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    assert hd2 == hd and out.shape == q.shape and q.dtype == k_cache.dtype == v_cache.dtype == out.dtype
+    assert 0 <= row0 and row0 + n_rows <= T
+    if num_splits > 1:
+        assert part_acc.dtype == part_ml.dtype == torch.float32
+        assert part_acc.numel() >= n_rows * nq * num_splits * hd and part_ml.numel() >= n_rows * nq * num_splits * 2
+    _check(lib().ccb_attention_split(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml),
+                                     _p(positions), _p(entry_of_token), _p(block_table), block_table.stride(0),
+                                     n_entries, row0, n_rows, nq, nkv, hd, page_size, num_pages, int(window),
+                                     float(scale), num_splits, _dt(q), _p(status), _stream()), "attention_split")
+    if num_splits > 1:
+        counters.own += 1  # the merge kernel
+
+
+DECODE_MMA_HEAD_SIZES = (64, 128)
+DECODE_MMA_HEADS_PER_BLOCK = 16
+
+
+def attention_decode_mma(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
+                         n_entries: int, row0: int, n_rows: int, window: int, scale: float, num_splits: int,
+                         status=None) -> None:
+    """As attention_split, on tensor cores: bfloat16, head size 64 or 128, a block per (row, kv head, split)
+    serving the whole group of q heads."""
+    _cuda(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status)
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    assert hd2 == hd and out.shape == q.shape
+    assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16
+    assert 0 <= row0 and row0 + n_rows <= T
+    if num_splits > 1:
+        assert part_acc.dtype == part_ml.dtype == torch.float32
+        assert part_acc.numel() >= n_rows * nq * num_splits * hd and part_ml.numel() >= n_rows * nq * num_splits * 2
+    _check(lib().ccb_attention_decode_mma(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml),
+                                          _p(positions), _p(entry_of_token), _p(block_table),
+                                          block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
+                                          num_pages, int(window), float(scale), num_splits, _p(status),
+                                          _stream()), "attention_decode_mma")
+    if num_splits > 1:
+        counters.own += 1  # the merge kernel
 
 
 def gemm_f32(c, a, w) -> None:

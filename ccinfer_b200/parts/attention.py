@@ -70,6 +70,18 @@ class GroupedQueryAttention(Mixer):
             self.k_norm_w = fetch(n["k_norm"]) if self.own_kv else None
         self.position.bind(rt, fetch)
 
+    def _attend(self, q, o, cache, step, T):
+        """Every token row is a single query over its request's pages (split kernel)."""
+        rt, g = self.rt, cache.group
+        mma = rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
+        per_block = kernels.DECODE_MMA_HEADS_PER_BLOCK if mma else 0
+        splits, n_acc, n_ml = kernels.attention_split_plan(T, self.nq, self.nkv, self.hd, per_block)
+        part_acc = rt.scratch.get("attn_part_acc", (n_acc,), torch.float32)
+        part_ml = rt.scratch.get("attn_part_ml", (n_ml,), torch.float32)
+        fn = kernels.attention_decode_mma if mma else kernels.attention_split
+        fn(q, cache.k, cache.v, o, part_acc, part_ml, step.positions, step.entry_of_token, g.block_table,
+           step.n_entries, 0, T, self.window or 0, self.scale, splits, status=rt.status)
+
     # -- a step ----------------------------------------------------------------
     def forward(self, x, step, cache, state):
         rt = self.rt
@@ -86,9 +98,7 @@ class GroupedQueryAttention(Mixer):
             self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, self.nq, nkv_w, self.hd, g.page_size,
             status=rt.status)
         o = rt.scratch.get("attn_o", (rt.max_tokens, self.nq, self.hd), rt.dtype)[:T]
-        kernels.paged_attention_generic(q, cache.k, cache.v, o, step.positions, step.entry_of_token,
-                                        g.block_table, step.n_entries, self.window or 0, self.scale,
-                                        status=rt.status)
+        self._attend(q, o, cache, step, T)
         out = rt.scratch.get("attn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
         rt.linear(out, o.view(T, self.q_width), self.w_o)
         return out

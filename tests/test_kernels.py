@@ -185,6 +185,124 @@ def test_paged_attention_generic(dtype, case):
     assert _rel(out, ref) <= (1e-5 if dtype == "float32" else 1.5e-2)
 
 
+def _run_split(q, kc, vc, pos, eot, bt, n_entries, window, hd, splits, row0=0, n_rows=None, fn=None):
+    k = _k()
+    fn = fn or k.attention_split
+    T, nq, _ = q.shape
+    n_rows = T - row0 if n_rows is None else n_rows
+    out = torch.zeros_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    part_acc = torch.empty(max(1, n_rows * nq * splits * hd), dtype=torch.float32, device="cuda")
+    part_ml = torch.empty(max(1, n_rows * nq * splits * 2), dtype=torch.float32, device="cuda")
+    fn(q, kc, vc, out, part_acc, part_ml, pos, eot, bt, n_entries, row0, n_rows, window or 0,
+       1 / math.sqrt(hd), splits, status)
+    assert int(status.item()) == 0
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("splits", [1, 3, 32])
+@pytest.mark.parametrize("case", ATTN_CASES + [([700, 33], [1, 1], 32, 8, 128, 16, None),
+                                                ([90], [2], 12, 2, 96, 8, 50), ([64], [1], 7, 7, 32, 16, None)])
+def test_attention_split(dtype, case, splits):
+    ctx, new, nq, nkv, hd, P, window = case
+    q, kc, vc, pos, eot, bt, ref = _paged_case(dtype, ctx, new, nq, nkv, hd, P, seed=hd + len(ctx), window=window)
+    out = _run_split(q, kc, vc, pos, eot, bt, len(ctx), window, hd, splits)
+    assert _rel(out, ref) <= (1e-5 if dtype == "float32" else 1.5e-2)
+    if q.shape[0] > 2:  # a range of rows only: the others stay untouched
+        part = _run_split(q, kc, vc, pos, eot, bt, len(ctx), window, hd, splits, row0=1, n_rows=q.shape[0] - 2)
+        assert torch.equal(part[1:-1], out[1:-1]) and float(part[0].abs().max()) == 0 == float(part[-1].abs().max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far_key", [0, 15, 16, 255, 256, 257, 511])
+def test_attention_split_reads_far_key(dtype, far_key):
+    nq, nkv, hd, P = 8, 2, 128, 16
+    L = 600
+    q, kc, vc, pos, eot, bt, ref = _paged_case(dtype, [L - 1], [1], nq, nkv, hd, P, seed=far_key,
+                                               peak=(0, far_key))
+    for splits in (1, 5):
+        out = _run_split(q, kc, vc, pos, eot, bt, 1, None, hd, splits)
+        assert _rel(out, ref) <= (1e-5 if dtype == "float32" else 1.5e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("edge", [-1, 0, 1])
+def test_attention_split_window_edge(dtype, edge):
+    nq, nkv, hd, P, W = 2, 1, 32, 8, 40
+    L = 200
+    key = (L - 1) - W + 1 + edge
+    q, kc, vc, pos, eot, bt, ref = _paged_case(dtype, [L - 1], [1], nq, nkv, hd, P, seed=7, window=W,
+                                               peak=(0, key))
+    for splits in (1, 4):
+        out = _run_split(q, kc, vc, pos, eot, bt, 1, W, hd, splits)
+        assert _rel(out, ref) <= (1e-5 if dtype == "float32" else 1.5e-2)
+
+
+MMA_CASES = [
+    # ctx, new, nq, nkv, hd, page, window
+    ([0], [1], 4, 1, 64, 16, None),
+    ([700, 33, 64, 63], [1, 1, 1, 1], 32, 8, 128, 16, None),
+    ([100, 0, 63], [1, 70, 1], 8, 2, 64, 8, None),
+    ([300, 129], [5, 1], 12, 2, 128, 4, 100),
+    ([511], [1], 40, 2, 128, 32, None),       # groups of 20 q heads: two head chunks per kv head
+    ([90], [2], 3, 3, 64, 16, 50),
+]
+
+
+@pytest.mark.parametrize("splits", [1, 3, 32])
+@pytest.mark.parametrize("case", MMA_CASES)
+def test_attention_decode_mma(case, splits):
+    ctx, new, nq, nkv, hd, P, window = case
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", ctx, new, nq, nkv, hd, P, seed=hd + len(ctx),
+                                               window=window)
+    out = _run_split(q, kc, vc, pos, eot, bt, len(ctx), window, hd, splits, fn=_k().attention_decode_mma)
+    assert _rel(out, ref) <= 1.5e-2
+    if q.shape[0] > 2:
+        part = _run_split(q, kc, vc, pos, eot, bt, len(ctx), window, hd, splits, row0=1, n_rows=q.shape[0] - 2,
+                          fn=_k().attention_decode_mma)
+        assert torch.equal(part[1:-1], out[1:-1]) and float(part[0].abs().max()) == 0 == float(part[-1].abs().max())
+
+
+@pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 257, 511, 598])
+def test_attention_decode_mma_reads_far_key(far_key):
+    nq, nkv, hd, P = 8, 2, 128, 16
+    L = 600
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [L - 1], [1], nq, nkv, hd, P, seed=far_key,
+                                               peak=(0, far_key))
+    for splits in (1, 5):
+        out = _run_split(q, kc, vc, pos, eot, bt, 1, None, hd, splits, fn=_k().attention_decode_mma)
+        assert _rel(out, ref) <= 1.5e-2
+
+
+@pytest.mark.parametrize("edge", [-1, 0, 1])
+def test_attention_decode_mma_window_edge(edge):
+    nq, nkv, hd, P, W = 4, 1, 64, 8, 40
+    L = 200
+    key = (L - 1) - W + 1 + edge
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [L - 1], [1], nq, nkv, hd, P, seed=7, window=W,
+                                               peak=(0, key))
+    for splits in (1, 4):
+        out = _run_split(q, kc, vc, pos, eot, bt, 1, W, hd, splits, fn=_k().attention_decode_mma)
+        assert _rel(out, ref) <= 1.5e-2
+
+
+def test_attention_decode_mma_refuses_other_head_sizes():
+    from ccinfer_b200.errors import Unsupported
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [10], [1], 2, 1, 48, 16, seed=1)
+    with pytest.raises(Unsupported):
+        _run_split(q, kc, vc, pos, eot, bt, 1, None, 48, 1, fn=_k().attention_decode_mma)
+
+
+def test_attention_split_padding_rows():
+    """Rows that belong to no request (padding of a replayed decode step) come out as zeros."""
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [40, 9], [1, 1], 4, 2, 64, 16, seed=3)
+    eot2 = eot.clone()
+    eot2[1] = -1
+    out = _run_split(q, kc, vc, pos, eot2, bt, 2, None, 64, 4)
+    assert float(out[1].abs().max()) == 0.0 and _rel(out[:1], ref[:1]) <= 1.5e-2
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("far_key", [0, 15, 16, 255, 256, 257, 511])
 def test_attention_reads_far_key(dtype, far_key):
