@@ -37,6 +37,7 @@ GROUPS = {
         "attention_decode_mma.cu",
         "gemm_f32.cu",
         "gemm_cublas.cu",
+        "gemm_skinny.cu",
         "sampling.cu",
     ],
 }

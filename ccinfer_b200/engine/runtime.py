@@ -61,6 +61,8 @@ class Runtime:
         """out[M, N] = x[M, K] @ w[N, K]^T; out may be float for bfloat16 operands (the logits)."""
         if self.dtype == torch.float32:
             kernels.gemm_f32(out, x, w)
+        elif kernels.gemm_skinny_fits(x.shape[0], x.shape[1], x, w):
+            kernels.gemm_skinny_bf16(out, x, w)   # a few tokens: stream the weights with our own kernel
         else:
             self.cublas.gemm_bf16(out, x, w)
         return out

@@ -56,6 +56,8 @@ _SIGNATURES = {
     "ccb_cublas_set_workspace": [c_void_p, c_void_p, c_size_t],
     "ccb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                       c_void_p],
+    "ccb_gemm_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p],
     "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -289,6 +291,25 @@ def gemm_f32(c, a, w) -> None:
     assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
     _check(lib().ccb_gemm_f32(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _stream()),
            "gemm_f32")
+
+
+SKINNY_MAX_ROWS = 16
+
+
+def gemm_skinny_fits(M: int, K: int, a, w) -> bool:
+    """Whether the few-rows product takes this shape (else the library product does)."""
+    return (M <= SKINNY_MAX_ROWS and K % 32 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny_bf16(c, a, w) -> None:
+    """c[M, N] (bfloat16 or float) = a[M, K] @ w[N, K]^T for M <= 32, K a multiple of 32 (own kernel)."""
+    assert a.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT and c.is_cuda and a.is_cuda and w.is_cuda
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    _check(lib().ccb_gemm_skinny_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0),
+                                      _dt(c), _stream()), "gemm_skinny_bf16")
 
 
 class CublasHandle:

@@ -119,6 +119,40 @@ def test_gemm_bf16(out, M, N, K):
     handle.close()
 
 
+@pytest.mark.parametrize("out", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 24, 64), (3, 301, 96), (8, 1000, 4096), (9, 500, 160), (16, 40, 12288),
+                                   (17, 130, 256), (32, 6144, 512)])
+def test_gemm_skinny(out, M, N, K):
+    k = _k()
+    a, a_ref = _rand((M, K), torch.bfloat16, 20)
+    w, w_ref = _rand((N, K), torch.bfloat16, 21)
+    c = torch.full((M, N), float("nan"), dtype=DT[out], device="cuda")
+    k.gemm_skinny_bf16(c, a, w)
+    assert _rel(c, a_ref @ w_ref.T) <= (2e-5 if out == "float32" else 8e-3)
+    # a row's result does not depend on the other rows of the batch
+    c1 = torch.empty((1, N), dtype=DT[out], device="cuda")
+    k.gemm_skinny_bf16(c1, a[M - 1:M].contiguous(), w)
+    assert torch.equal(c1[0], c[M - 1])
+    # rows of a wider buffer (row stride > K) as the engine passes them
+    wide = torch.zeros((M, K + 64), dtype=torch.bfloat16, device="cuda")
+    wide[:, :K] = a
+    c2 = torch.empty_like(c)
+    k.gemm_skinny_bf16(c2, wide[:, :K], w)
+    assert torch.equal(c2, c)
+
+
+def test_gemm_skinny_refuses():
+    from ccinfer_b200.errors import Unsupported
+    k = _k()
+    for M, K in ((33, 64), (4, 80)):
+        a = torch.zeros((M, K), dtype=torch.bfloat16, device="cuda")
+        w = torch.zeros((16, K), dtype=torch.bfloat16, device="cuda")
+        c = torch.zeros((M, 16), dtype=torch.bfloat16, device="cuda")
+        assert not k.gemm_skinny_fits(M, K, a, w)
+        with pytest.raises(Unsupported):
+            k.gemm_skinny_bf16(c, a, w)
+
+
 def _paged_case(dtype, lens_ctx, lens_new, nq, nkv, hd, P, seed, window=None, peak=None):
     """Random keys in a shuffled page pool; returns inputs of the attention kernel and the plain result.
 
