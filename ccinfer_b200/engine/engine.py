@@ -203,6 +203,11 @@ class Engine:
             self._host_events[turn].synchronize()  # its last copy has left the buffer
         host_buf = self._host_bufs[turn]
         host = host_buf.numpy()
+        # single-token entries (decoding requests) first: kernels treat the two kinds of rows differently
+        order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
+        place = {i: k for k, i in enumerate(order)}
+        given = entries
+        entries = [given[i] for i in order]
         B = len(entries)
         counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
         cu = np.zeros(B + 1, dtype=np.int64)
@@ -227,7 +232,7 @@ class Engine:
         if pad_to:  # a decode step padded to a graph's size: one row per entry, the padding's rows are ignored
             rows = list(range(Bp))
         else:
-            rows = [int(cu[b]) + int(w) for b, e in enumerate(entries) for w in e.want]
+            rows = [int(cu[place[i]]) + int(w) for i, e in enumerate(given) for w in e.want]
         R = len(rows)
         lr = host[lay.o_logit_rows:lay.o_logit_rows + max(R, 1)]
         if R:
@@ -247,6 +252,8 @@ class Engine:
 
         step = StepContext()
         step.n_tokens, step.n_entries, step.n_logit_rows = Tp, Bp, R
+        n_single = int((counts == 1).sum())
+        step.n_single = n_single + (Bp - B) if n_single == B else n_single   # padding rows are single rows too
         step.max_q_len = int(counts.max())
         step.max_ctx = int((pos0 + counts).max())
         dev = self._dev_buf

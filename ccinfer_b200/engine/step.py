@@ -6,7 +6,7 @@ arrays of a step live at fixed offsets of ONE pinned host buffer and ONE device
 buffer of fixed size: a step is one host-to-device copy, and because nothing
 moves, a decode step can be replayed from a CUDA graph.
 
-  token_ids[T]       the tokens the step brings, entries one after another
+  token_ids[T]       the tokens the step brings, entries one after another (single-token entries first)
   positions[T]       absolute position of each token in its request
   entry_of_token[T]  which entry (request) a token belongs to; -1 for padding
   logit_rows[R]      token rows whose logits are wanted
@@ -58,6 +58,7 @@ class StepContext:
         self.n_tokens = 0
         self.n_entries = 0
         self.n_logit_rows = 0
+        self.n_single = 0        # the first n_single entries (and token rows) bring one token each
         self.max_q_len = 0       # host facts for kernels that choose a launch shape
         self.max_ctx = 0
         self.token_ids = self.positions = self.entry_of_token = self.logit_rows = None

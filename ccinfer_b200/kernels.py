@@ -50,6 +50,9 @@ _SIGNATURES = {
     "ccb_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_int, c_void_p, c_void_p],
+    "ccb_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                  c_void_p],
     "ccb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_cublas_create": [ctypes.POINTER(c_void_p)],
     "ccb_cublas_destroy": [c_void_p],
@@ -281,6 +284,23 @@ def attention_decode_mma(q, k_cache, v_cache, out, part_acc, part_ml, positions,
                                           _stream()), "attention_decode_mma")
     if num_splits > 1:
         counters.own += 1  # the merge kernel
+
+
+def attention_prefill_mma(q, k_cache, v_cache, out, cu_q, pos0, block_table, entry0: int, n_entries: int,
+                          max_new: int, window: int, scale: float, status=None) -> None:
+    """Causal attention of the new tokens of the step's requests entry0 .. entry0 + n_entries - 1 over their
+    pages, on tensor cores (bfloat16, head size 64 or 128).  cu_q [B + 1] gives each request's first token
+    row, pos0 [B] the position of that token; max_new is the most new tokens any of them has."""
+    _cuda(q, k_cache, v_cache, out, cu_q, pos0, block_table, status)
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    assert hd2 == hd and out.shape == q.shape
+    assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16
+    assert entry0 >= 0 and entry0 + n_entries <= block_table.shape[0] and cu_q.numel() >= entry0 + n_entries + 1
+    _check(lib().ccb_attention_prefill_mma(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(cu_q), _p(pos0),
+                                           _p(block_table), block_table.stride(0), entry0, n_entries, max_new,
+                                           nq, nkv, hd, page_size, num_pages, int(window), float(scale),
+                                           _p(status), _stream()), "attention_prefill_mma")
 
 
 def gemm_f32(c, a, w) -> None:

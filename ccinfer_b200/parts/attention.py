@@ -71,16 +71,27 @@ class GroupedQueryAttention(Mixer):
         self.position.bind(rt, fetch)
 
     def _attend(self, q, o, cache, step, T):
-        """Every token row is a single query over its request's pages (split kernel)."""
+        """Attention of every token row of the step over its request's pages.
+
+        A step lists its single-token requests first.  On the tensor-core path (bfloat16, head size 64 or
+        128) those rows go to the decode kernel (key range split over blocks) and the portions of prompts to
+        the prefill kernel (64 query tokens a block); otherwise every row is a single query of the split
+        kernel, which takes all sizes and both types."""
         rt, g = self.rt, cache.group
         mma = rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
-        per_block = kernels.DECODE_MMA_HEADS_PER_BLOCK if mma else 0
-        splits, n_acc, n_ml = kernels.attention_split_plan(T, self.nq, self.nkv, self.hd, per_block)
-        part_acc = rt.scratch.get("attn_part_acc", (n_acc,), torch.float32)
-        part_ml = rt.scratch.get("attn_part_ml", (n_ml,), torch.float32)
-        fn = kernels.attention_decode_mma if mma else kernels.attention_split
-        fn(q, cache.k, cache.v, o, part_acc, part_ml, step.positions, step.entry_of_token, g.block_table,
-           step.n_entries, 0, T, self.window or 0, self.scale, splits, status=rt.status)
+        n_rows = step.n_single if mma else T
+        if n_rows > 0:
+            per_block = kernels.DECODE_MMA_HEADS_PER_BLOCK if mma else 0
+            splits, n_acc, n_ml = kernels.attention_split_plan(n_rows, self.nq, self.nkv, self.hd, per_block)
+            part_acc = rt.scratch.get("attn_part_acc", (n_acc,), torch.float32)
+            part_ml = rt.scratch.get("attn_part_ml", (n_ml,), torch.float32)
+            fn = kernels.attention_decode_mma if mma else kernels.attention_split
+            fn(q, cache.k, cache.v, o, part_acc, part_ml, step.positions, step.entry_of_token, g.block_table,
+               step.n_entries, 0, n_rows, self.window or 0, self.scale, splits, status=rt.status)
+        if mma and step.n_entries > step.n_single:
+            kernels.attention_prefill_mma(q, cache.k, cache.v, o, step.cu_q, step.pos0, g.block_table,
+                                          step.n_single, step.n_entries - step.n_single, step.max_q_len,
+                                          self.window or 0, self.scale, status=rt.status)
 
     # -- a step ----------------------------------------------------------------
     def forward(self, x, step, cache, state):

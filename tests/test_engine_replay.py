@@ -15,8 +15,9 @@ pytestmark = pytest.mark.gpu
 
 # relative to the largest logit of the request
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
-CONFIGS = ["A", "B", "C"]
-LENGTHS = {"A": [5, 11, 17, 64, 120], "B": [1, 9, 33, 64, 150, 97], "C": [3, 40, 77, 130, 96, 51]}
+CONFIGS = ["A", "B", "C", "D", "E"]
+LENGTHS = {"A": [5, 11, 17, 64, 120], "B": [1, 9, 33, 64, 150, 97], "C": [3, 40, 77, 130, 96, 51],
+           "D": [2, 70, 200, 129, 64, 333], "E": [1, 65, 150, 300, 128]}
 
 
 def _requests(cfg, lengths, seed=5):

@@ -31,10 +31,31 @@ TINY_C = {
 }
 C_SEED, C_STD, C_PAGE = 2, 0.04, 16
 
+# head size 64: the tensor-core attention kernels of the bfloat16 path; layer 1 reads a window of 40 keys
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 128,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 192,
+    "vocab_size": 333, "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 1024, "torch_dtype": "float32",
+    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1,
+}
+D_SEED, D_STD, D_PAGE = 3, 0.03, 16
+
+# head size 128, one kv head for 8 q heads, pages of 32
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 96,
+    "num_attention_heads": 8, "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 128,
+    "vocab_size": 260, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "max_position_embeddings": 1024, "torch_dtype": "float32",
+}
+E_SEED, E_STD, E_PAGE = 4, 0.03, 32
+
 ALL = {
     "A": (TINY_A, A_SEED, A_STD, A_PAGE),
     "B": (TINY_B, B_SEED, B_STD, B_PAGE),
     "C": (TINY_C, C_SEED, C_STD, C_PAGE),
+    "D": (TINY_D, D_SEED, D_STD, D_PAGE),
+    "E": (TINY_E, E_SEED, E_STD, E_PAGE),
 }
 
 
