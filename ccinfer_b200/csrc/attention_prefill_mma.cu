@@ -54,6 +54,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   const int rows_here = min(kQTile, n_new - q_first);
   const int p_first = p0 + q_first, p_last = p_first + rows_here - 1;
   const int* bt = block_table + (size_t)b * bt_stride;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
   // Q tile -> shared memory (rows beyond the request's tokens are zero)
 #pragma unroll
@@ -70,29 +71,36 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   const int first_tile = j_lo / kKTile, last_tile = p_last / kKTile;
   const int n_tiles = last_tile - first_tile + 1;
 
+  // Two threads share a key row: one page lookup and one address per thread and tile, then 16-byte copies of
+  // alternating chunks, so that a pair of lanes always asks for one whole 32-byte sector.
+  static_assert(kPThreads == 2 * kKTile, "two threads per key row");
+  const int ld_row = tid >> 1, ld_half = tid & 1;
   auto issue = [&](int tile, int stage) {
     __nv_bfloat16* ks_ = k_s + stage * TILE_ELEMS;
     __nv_bfloat16* vs_ = v_s + stage * TILE_ELEMS;
-#pragma unroll
-    for (int i = 0; i < kKTile * CH / kPThreads; ++i) {
-      const int idx = tid + kPThreads * i;
-      const int row = idx / CH, c = idx - row * CH;
-      const int j = tile * kKTile + row;
-      bool valid = j >= j_lo && j <= p_last;
-      size_t src = 0;
-      if (valid) {
-        const int lp = j / page_size;
-        const int page = lp < bt_stride ? bt[lp] : -1;
-        if (page < 0 || page >= num_pages) {
-          set_status(status, CCB_ST_BAD_PAGE);
-          valid = false;
-        } else {
-          src = (((size_t)page * nkv + kvh) * page_size + (j - lp * page_size)) * HD + c * 8;
-        }
+    const int j = tile * kKTile + ld_row;
+    bool valid = j >= j_lo && j <= p_last;
+    size_t src = 0;
+    if (valid) {
+      const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+      const int page = lp < bt_stride ? bt[lp] : -1;
+      if (page < 0 || page >= num_pages) {
+        set_status(status, CCB_ST_BAD_PAGE);
+        valid = false;
+      } else {
+        src = (((size_t)page * nkv + kvh) * page_size + (j - lp * page_size)) * HD;
       }
-      const int dst = swz<HD>(row, c);
-      cp_async16(smem_u32(ks_ + dst), k_cache + src, valid);
-      cp_async16(smem_u32(vs_ + dst), v_cache + src, valid);
+    }
+    const __nv_bfloat16* ksrc = k_cache + src;
+    const __nv_bfloat16* vsrc = v_cache + src;
+    const uint32_t kdst = smem_u32(ks_ + ld_row * HD), vdst = smem_u32(vs_ + ld_row * HD);
+    const int sw = ld_row & 7;
+#pragma unroll
+    for (int i = 0; i < CH / 2; ++i) {
+      const int c = 2 * i + ld_half;
+      const uint32_t off = (uint32_t)((c ^ sw) << 4);
+      cp_async16(kdst + off, ksrc + c * 8, valid);
+      cp_async16(vdst + off, vsrc + c * 8, valid);
     }
   };
 
