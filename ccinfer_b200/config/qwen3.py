@@ -60,6 +60,7 @@ class Qwen3Config:
     use_sliding_window: bool = False
     sliding_window: Optional[int] = None
     max_window_layers: Optional[int] = None
+    layer_types: Optional[tuple] = None   # per layer "full_attention" / "sliding_attention", if the file has it
 
     # -- derived -----------------------------------------------------------
     @property
@@ -78,8 +79,12 @@ class Qwen3Config:
         """Keys a layer's queries see besides causality: None = all of them.
 
         With ``use_sliding_window`` the layers from ``max_window_layers`` on
-        see the last ``sliding_window`` keys (their own included).
+        see the last ``sliding_window`` keys (their own included).  A
+        ``layer_types`` list, where the file has one, says it layer by layer
+        and wins over that rule.
         """
+        if self.layer_types is not None:
+            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else None
         if not self.use_sliding_window or self.sliding_window is None:
             return None
         first = self.num_hidden_layers if self.max_window_layers is None else self.max_window_layers
@@ -143,11 +148,20 @@ class Qwen3Config:
                 raise ModelConfigInvalid("config.json: 'max_window_layers' must be >= 0")
         if use_sw and sw is None:
             raise ModelConfigInvalid("config.json: use_sliding_window is true but sliding_window is null")
+        lt = j.get("layer_types")
+        if lt is not None:
+            if (not isinstance(lt, list) or len(lt) != layers
+                    or any(t not in ("full_attention", "sliding_attention") for t in lt)):
+                raise ModelConfigInvalid("config.json: 'layer_types' must list full_attention or "
+                                         "sliding_attention for each of the layers")
+            if "sliding_attention" in lt and sw is None:
+                raise ModelConfigInvalid("config.json: layer_types has sliding_attention but sliding_window is null")
+            lt = tuple(lt)
         return cls(architecture=arch, vocab_size=vocab, hidden_size=hidden, num_hidden_layers=layers,
                    num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
                    intermediate_size=inter, max_position_embeddings=max_pos, rope_theta=theta,
                    rms_norm_eps=eps, tie_word_embeddings=tie, torch_dtype=dtype,
-                   use_sliding_window=use_sw, sliding_window=sw, max_window_layers=mwl)
+                   use_sliding_window=use_sw, sliding_window=sw, max_window_layers=mwl, layer_types=lt)
 
     def to_json(self) -> dict:
         j = {
@@ -172,4 +186,6 @@ class Qwen3Config:
             "sliding_window": self.sliding_window,
             "max_window_layers": self.max_window_layers,
         }
+        if self.layer_types is not None:
+            j["layer_types"] = list(self.layer_types)
         return j

@@ -174,6 +174,8 @@ def layer_window(cfg: dict, layer: int):
     ``max_window_layers`` use ``sliding_window`` keys, the others all keys.
     (The reference reads none of these keys: src/model/config.h:55-133.)
     """
+    if cfg.get("layer_types") is not None:  # a per-layer list, where the file has one, wins
+        return int(cfg["sliding_window"]) if cfg["layer_types"][layer] == "sliding_attention" else None
     if not cfg.get("use_sliding_window", False) or cfg.get("sliding_window") is None:
         return None
     if layer >= cfg.get("max_window_layers", cfg["num_hidden_layers"]):

@@ -26,6 +26,22 @@ def test_parse_tiny_configs():
     assert [c.layer_window(l) for l in range(4)] == [None, 24, 24, 24]
 
 
+def test_layer_types_win_over_the_window_rule():
+    j = dict(tiny_configs.TINY_C, layer_types=["sliding_attention", "full_attention", "full_attention",
+                                                "sliding_attention"])
+    c = Qwen3Config.from_json(j)
+    assert [c.layer_window(l) for l in range(4)] == [24, None, None, 24]
+    assert Qwen3Config.from_json(c.to_json()) == c
+    with pytest.raises(ModelConfigInvalid):
+        Qwen3Config.from_json(dict(j, layer_types=["full_attention"]))
+    with pytest.raises(ModelConfigInvalid):
+        Qwen3Config.from_json(dict(j, sliding_window=None, use_sliding_window=False))
+    # the keys as a stock checkpoint has them: a window size is named but not in use
+    stock = dict(tiny_configs.TINY_A, use_sliding_window=False, sliding_window=4096, max_window_layers=2,
+                 layer_types=["full_attention", "full_attention"], attention_dropout=0.0, bos_token_id=1)
+    assert all(Qwen3Config.from_json(stock).layer_window(l) is None for l in range(2))
+
+
 def test_defaults_follow_the_reference():
     j = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 64, "num_attention_heads": 4,
          "num_hidden_layers": 1, "intermediate_size": 8, "vocab_size": 10}
