@@ -1,0 +1,289 @@
+"""Each part alone against its plain function, the order of layers as data, and a toy architecture whose
+mixer keeps state of its own, registered, built and stepped without a change to the package's files."""
+import dataclasses
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+def _rel(got, ref):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert torch.isfinite(got).all()
+    return float((got - ref).abs().max() / ref.abs().max().clamp_min(1e-9))
+
+
+def _weights(specs, seed, std=0.1):
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for s in specs:
+        w = torch.randn(s.shape, generator=g) * std
+        if s.init == "one_plus_normal":
+            w = w + 1
+        out[s.name] = w.to(torch.bfloat16).float()  # the same values in both compute types
+    return out
+
+
+def _fetch(weights, specs, dtype):
+    by = {s.name: s for s in specs}
+
+    def fetch(name):
+        return weights[name].to("cuda", dtype=torch.float32 if by[name].role == "vector" else dtype).contiguous()
+    return fetch
+
+
+def _engine(plan, weights, dtype, page=8, tokens=256):
+    from ccinfer_b200.engine.engine import Engine, EngineOptions
+    return Engine(plan, _fetch(weights, plan.tensor_specs(), DT[dtype]),
+                  EngineOptions(dtype=dtype, page_size=page, kv_tokens=tokens, max_requests=4,
+                                max_tokens_per_step=tokens, use_graphs=False))
+
+
+def _qwen_plan(hidden=48, heads=4, kv=2, hd=16, inter=72, vocab=97, layers=1, window=None, eps=1e-5, theta=1e4):
+    from ccinfer_b200.config import Qwen3Config
+    from ccinfer_b200.architectures.qwen3 import build_plan
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": layers, "hidden_size": hidden,
+           "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd, "intermediate_size": inter,
+           "vocab_size": vocab, "rope_theta": theta, "rms_norm_eps": eps, "max_position_embeddings": 512}
+    if window:
+        cfg.update(use_sliding_window=True, sliding_window=window, max_window_layers=0)
+    return cfg, build_plan(Qwen3Config.from_json(cfg))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_parts_alone(dtype):
+    """Norm, position encoding, feed-forward, embedding, head, mixer and block, each called by itself."""
+    from ccinfer_b200.engine.engine import StepEntry
+    from ccinfer_b200.parts import Residual
+    cfg, plan = _qwen_plan(window=20)
+    w = _weights(plan.tensor_specs(), 1)
+    eng = _engine(plan, w, dtype)
+    T = 45
+    toks = list(range(3, 3 + T))
+    eng.open_request("a")
+    eng.cache.reserve("a", T)
+    step = eng._build([StepEntry("a", toks, [0, T - 1])])
+    block = plan.layers[0]
+    g = torch.Generator().manual_seed(2)
+    x_ref = torch.randn(T, 48, generator=g).to(DT[dtype]).double()
+    x = x_ref.to("cuda", DT[dtype])
+    p = "model.layers.0."
+    wd = {k: v.double() for k, v in w.items()}
+    # embedding
+    stream = plan.embedding.forward(step)
+    assert torch.equal(stream.h.cpu().double(), plain.embed(wd["model.embed_tokens.weight"], toks))
+    # norm: plain apply, fold of a pending delta, fold on picked rows
+    assert _rel(block.norm1.apply(x), plain.rms_norm(x_ref, wd[p + "input_layernorm.weight"], 1e-5)) <= TOL[dtype]
+    h0 = stream.h.clone()
+    stream.pending = x
+    y = block.norm1.fold(stream)
+    assert stream.pending is None and _rel(stream.h, h0.cpu().double() + x_ref) <= 1e-6
+    assert _rel(y, plain.rms_norm(h0.cpu().double() + x_ref, wd[p + "input_layernorm.weight"], 1e-5)) <= TOL[dtype]
+    rows = plan.final_norm.fold(stream, rows=step.logit_rows, n_rows=2)
+    ref_rows = plain.rms_norm(stream.h.cpu().double(), wd["model.norm.weight"], 1e-5)[[0, T - 1]]
+    assert _rel(rows, ref_rows) <= TOL[dtype]
+    # head
+    assert _rel(plan.head.forward(rows), rows.cpu().double() @ wd["lm_head.weight"].T) <= TOL[dtype]
+    # position encoding by itself
+    xq = x.view(T, 3, 16).contiguous()
+    rot = block.mixer.position.apply(xq, step.positions)
+    assert _rel(rot, plain.apply_rope(x_ref.view(T, 3, 16), torch.arange(T), plain.rope_inv_freq(16, 1e4))) <= TOL[dtype]
+    # feed-forward
+    ff = block.ffn.forward(x, step)
+    assert _rel(ff, plain.swiglu(x_ref, wd[p + "mlp.gate_proj.weight"], wd[p + "mlp.up_proj.weight"],
+                                 wd[p + "mlp.down_proj.weight"])) <= TOL[dtype]
+    # mixer (windowed attention over the paged cache)
+    from ccinfer_b200.engine.step import LayerCache
+    cache = LayerCache(eng._cache_k[0], eng._cache_v[0], step.groups[0], True)
+    att = block.mixer.forward(x, step, cache, None)
+    ref_att = plain.attention_block(x_ref, wd, p + "self_attn.", cfg, torch.arange(T), window=20)
+    assert _rel(att, ref_att) <= TOL[dtype]
+    # the block: h += Attn(norm1(h)); pending = MLP(norm2(h))
+    s2 = Residual(h0.clone())
+    block.forward(s2, step, cache, None)
+    hh = h0.cpu().double()
+    hh = hh + plain.attention_block(plain.rms_norm(hh, wd[p + "input_layernorm.weight"], 1e-5), wd,
+                                    p + "self_attn.", cfg, torch.arange(T), window=20)
+    assert _rel(s2.h, hh) <= TOL[dtype]
+    mlp = plain.swiglu(plain.rms_norm(hh, wd[p + "post_attention_layernorm.weight"], 1e-5),
+                       wd[p + "mlp.gate_proj.weight"], wd[p + "mlp.up_proj.weight"], wd[p + "mlp.down_proj.weight"])
+    assert _rel(s2.pending, mlp) <= TOL[dtype] * 2
+    eng.cache.rollback("a")
+    eng.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_order_of_layers_is_data(dtype):
+    """A layer named twice (two caches) and a layer that reads another run's cache, against plain parts."""
+    from ccinfer_b200.engine.engine import StepEntry
+    from ccinfer_b200.engine.plan import ModelPlan, RunEntry
+    from ccinfer_b200.parts import (GroupedQueryAttention, OutputHead, PreNormBlock, RMSNorm, RotaryHalf, SwiGLU,
+                                    TokenEmbedding)
+    D, nq, nkv, hd, F, V, eps, theta = 32, 4, 2, 16, 40, 61, 1e-6, 1e4
+
+    def block(name, own_kv):
+        n = {k: f"{name}.attn.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+        return PreNormBlock(
+            RMSNorm(D, eps, f"{name}.n1"),
+            GroupedQueryAttention(D, nq, nkv, hd, RotaryHalf(hd, theta), n, qk_norm_eps=eps, own_kv=own_kv),
+            RMSNorm(D, eps, f"{name}.n2"),
+            SwiGLU(D, F, {k: f"{name}.ffn.{k}" for k in ("gate", "up", "down")}))
+
+    plan = ModelPlan(TokenEmbedding(V, D, "emb"), [block("L0", True), block("L1", False)],
+                     [RunEntry(0), RunEntry(1, cache_of=0), RunEntry(0)], RMSNorm(D, eps, "nf"),
+                     OutputHead(D, V, "emb"), V, 256)
+    assert plan.shared_tensor_names() == {"emb"}
+    w = _weights(plan.tensor_specs(), 3, std=0.15)
+    assert "L1.attn.k" not in w and "L1.attn.k_norm" not in w  # the borrowing layer has no k/v projections
+    eng = _engine(plan, w, dtype)
+    toks = [5, 9, 60, 1, 33, 7, 7, 12, 50, 2, 18, 41, 3]
+    eng.open_request("r")
+    got = torch.cat([eng.step([StepEntry("r", toks[:6], list(range(6)))]),
+                     eng.step([StepEntry("r", toks[6:8], [0, 1])]),
+                     eng.step([StepEntry("r", toks[8:], list(range(5)))])]).cpu()
+    eng.check()
+    assert len(eng._cache_k) == 2  # runs 0 and 2 own a cache, run 1 borrows
+
+    wd = {k: v.double() for k, v in w.items()}
+    T = len(toks)
+    pos = torch.arange(T)
+    inv = plain.rope_inv_freq(hd, theta)
+
+    def qkv(x, name, with_kv=True):
+        q = plain.apply_rope(plain.rms_norm((x @ wd[f"{name}.attn.q"].T).view(T, nq, hd), wd[f"{name}.attn.q_norm"], eps), pos, inv)
+        if not with_kv:
+            return q, None, None
+        k = plain.apply_rope(plain.rms_norm((x @ wd[f"{name}.attn.k"].T).view(T, nkv, hd), wd[f"{name}.attn.k_norm"], eps), pos, inv)
+        return q, k, (x @ wd[f"{name}.attn.v"].T).view(T, nkv, hd)
+
+    def ffn(h, name):
+        x = plain.rms_norm(h, wd[f"{name}.n2"], eps)
+        return h + plain.swiglu(x, wd[f"{name}.ffn.gate"], wd[f"{name}.ffn.up"], wd[f"{name}.ffn.down"])
+
+    h = plain.embed(wd["emb"], toks)
+    q, k0, v0 = qkv(plain.rms_norm(h, wd["L0.n1"], eps), "L0")
+    h = ffn(h + plain.causal_attention(q, k0, v0).reshape(T, -1) @ wd["L0.attn.o"].T, "L0")
+    q, _, _ = qkv(plain.rms_norm(h, wd["L1.n1"], eps), "L1", with_kv=False)
+    h = ffn(h + plain.causal_attention(q, k0, v0).reshape(T, -1) @ wd["L1.attn.o"].T, "L1")  # run 0's keys
+    q, k2, v2 = qkv(plain.rms_norm(h, wd["L0.n1"], eps), "L0")
+    h = ffn(h + plain.causal_attention(q, k2, v2).reshape(T, -1) @ wd["L0.attn.o"].T, "L0")
+    ref = plain.rms_norm(h, wd["nf"], eps) @ wd["emb"].T
+    assert _rel(got, ref) <= TOL[dtype]
+
+
+# ---------------------------------------------------------------------------------------------
+# a toy architecture, defined here: its mixer keeps a running sum per request in a state slot
+# ---------------------------------------------------------------------------------------------
+@dataclasses.dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    eps: float
+
+    @classmethod
+    def from_json(cls, j):
+        return cls(j["vocab_size"], j["hidden_size"], j["intermediate_size"], j["eps"])
+
+    def to_json(self):
+        return {"architectures": ["ToyRunningMeanLM"], "torch_dtype": "float32", **dataclasses.asdict(self)}
+
+
+def _toy_parts():
+    from ccinfer_b200.parts.base import Mixer, StateNeed, TensorSpec
+
+    class RunningMean(Mixer):
+        """y_t = W mean(x_0 .. x_t): the sum and the count live in the request's state slot."""
+        graph_safe = False  # it reads the step's host arrays
+
+        def __init__(self, dim, name):
+            self.dim, self.name = dim, name
+
+        def tensor_specs(self):
+            return [TensorSpec(self.name, (self.dim, self.dim))]
+
+        def state_need(self):
+            return StateNeed((self.dim + 1,), torch.float32)
+
+        def bind(self, rt, fetch):
+            self.w = fetch(self.name)
+
+        def forward(self, x, step, cache, state):
+            out = torch.empty_like(x)
+            cu, slots = step.host.cu_q, step.host.state_slot
+            for b in range(step.n_entries):
+                if slots[b] < 0:
+                    continue
+                st = state[int(slots[b])]
+                xs = x[int(cu[b]):int(cu[b + 1])].float()
+                sums = st[:self.dim] + torch.cumsum(xs, 0)
+                counts = st[self.dim] + torch.arange(1, xs.shape[0] + 1, device=x.device)
+                out[int(cu[b]):int(cu[b + 1])] = ((sums / counts[:, None]) @ self.w.float().T).to(x.dtype)
+                st[:self.dim] = sums[-1]
+                st[self.dim] = counts[-1]
+            return out
+
+    return RunningMean
+
+
+def _toy_plan(cfg: ToyConfig):
+    from ccinfer_b200.engine.plan import ModelPlan, RunEntry
+    from ccinfer_b200.parts import OutputHead, PreNormBlock, RMSNorm, SwiGLU, TokenEmbedding
+    RunningMean = _toy_parts()
+    D = cfg.hidden_size
+    blocks = [PreNormBlock(RMSNorm(D, cfg.eps, f"b{i}.n1"), RunningMean(D, f"b{i}.mix"), RMSNorm(D, cfg.eps, f"b{i}.n2"),
+                           SwiGLU(D, cfg.intermediate_size, {k: f"b{i}.{k}" for k in ("gate", "up", "down")}))
+              for i in range(2)]
+    return ModelPlan(TokenEmbedding(cfg.vocab_size, D, "emb"), blocks, [RunEntry(0), RunEntry(1)],
+                     RMSNorm(D, cfg.eps, "nf"), OutputHead(D, cfg.vocab_size, "head"), cfg.vocab_size, None)
+
+
+def _toy_plain(w, cfg, toks):
+    w = {k: v.double() for k, v in w.items()}
+    h = plain.embed(w["emb"], toks)
+    n = torch.arange(1, len(toks) + 1, dtype=torch.float64)[:, None]
+    for i in range(2):
+        x = plain.rms_norm(h, w[f"b{i}.n1"], cfg.eps)
+        h = h + (torch.cumsum(x, 0) / n) @ w[f"b{i}.mix"].T
+        h = h + plain.swiglu(plain.rms_norm(h, w[f"b{i}.n2"], cfg.eps), w[f"b{i}.gate"], w[f"b{i}.up"], w[f"b{i}.down"])
+    return plain.rms_norm(h, w["nf"], cfg.eps) @ w["head"].T
+
+
+def test_toy_mixer_with_state_of_its_own(tmp_path):
+    from ccinfer_b200.config import register_architecture
+    from ccinfer_b200.engine.engine import Engine, EngineOptions, StepEntry
+    from ccinfer_b200.weights import SafetensorsFile, write_random_model
+    register_architecture("ToyRunningMeanLM", ToyConfig.from_json, _toy_plan, replace=True)
+    cfg = ToyConfig(vocab_size=53, hidden_size=24, intermediate_size=40, eps=1e-6)
+    d = write_random_model(str(tmp_path / "toy"), cfg, seed=9, std=0.3, store_dtype="float32")
+    f = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    w = {n: f.tensor(n).clone() for n in f.entries}
+    eng = Engine.from_model_dir(d, EngineOptions(dtype="float32", max_requests=2, max_tokens_per_step=64))
+    assert not eng.graph_safe and len(eng.cache.groups) == 0 and len(eng._state) == 2
+    rng = np.random.RandomState(0)
+    a, b, c = (rng.randint(0, 53, size=n).tolist() for n in (19, 7, 11))
+    eng.open_request("a")
+    eng.open_request("b")
+    rows = {"a": [], "b": [], "c": []}
+    rows["a"].append(eng.step([StepEntry("a", a[:5], range(5))]))
+    out = eng.step([StepEntry("b", b[:3], range(3)), StepEntry("a", a[5:6], [0])])   # a portion beside a single token
+    rows["b"].append(out[:3]); rows["a"].append(out[3:])
+    out = eng.step([StepEntry("a", a[6:17], range(11)), StepEntry("b", b[3:], range(4))])
+    rows["a"].append(out[:11]); rows["b"].append(out[11:])
+    eng.close_request("b")
+    eng.open_request("c")  # takes b's slot: its state starts from zero again
+    assert eng.cache.get("c").slot != eng.cache.get("a").slot
+    out = eng.step([StepEntry("c", c, range(11)), StepEntry("a", a[17:], range(2))])
+    rows["c"].append(out[:11]); rows["a"].append(out[11:])
+    for rid, toks in (("a", a), ("b", b), ("c", c)):
+        assert _rel(torch.cat(rows[rid]), _toy_plain(w, cfg, toks)) <= 2e-5, rid
