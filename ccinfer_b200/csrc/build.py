@@ -39,6 +39,7 @@ GROUPS = {
         "gemm_f32.cu",
         "gemm_cublas.cu",
         "gemm_skinny.cu",
+        "gemm_tcgen05.cu",
         "sampling.cu",
     ],
 }

@@ -61,6 +61,8 @@ _SIGNATURES = {
                       c_void_p],
     "ccb_gemm_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
+    "ccb_gemm_tc_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                         c_void_p, c_void_p, c_void_p, c_void_p],
     "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -330,6 +332,43 @@ def gemm_skinny_bf16(c, a, w) -> None:
     assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
     _check(lib().ccb_gemm_skinny_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0),
                                       _dt(c), _stream()), "gemm_skinny_bf16")
+
+
+TC_SWAP_MAX_ROWS = 64     # up to here the weights are the 128-row side of the tensor-core tile
+TC_TARGET_BLOCKS = 148    # one block per SM
+
+
+def gemm_tc_fits(K: int, a, w) -> bool:
+    return (K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc_splits(M: int, N: int, K: int) -> int:
+    """How many slices of K run as separate blocks (decode shapes only): enough blocks for every SM."""
+    if M > TC_SWAP_MAX_ROWS:
+        return 1
+    tiles = -(-N // 128)
+    kb = -(-K // 64)
+    s = max(1, min(-(-TC_TARGET_BLOCKS // tiles), kb // 4, 16))
+    while s > 1 and (s - 1) * (-(-kb // s)) >= kb:   # every slice must hold a k block
+        s -= 1
+    return s
+
+
+def gemm_tc_bf16(c, a, w, splits: int = 1, partial=None, counters=None, status=None) -> None:
+    """c[M, N] (bfloat16 or float) = a[M, K] @ w[N, K]^T on tcgen05 tensor cores with TMA loads.
+
+    M <= 64 streams the weights as the 128-row operand and may cut K into ``splits`` slices
+    (``partial``: float scratch of splits * M * N, ``counters``: int32 zeros, one per 128 features)."""
+    assert a.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT and c.is_cuda and a.is_cuda and w.is_cuda
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    if splits > 1:
+        assert partial.dtype == torch.float32 and partial.numel() >= splits * M * N
+        assert counters.dtype == torch.int32 and counters.numel() >= -(-N // 128)
+    _check(lib().ccb_gemm_tc_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _dt(c),
+                                  splits, _p(partial), _p(counters), _p(status), _stream()), "gemm_tc_bf16")
 
 
 class CublasHandle:

@@ -141,6 +141,41 @@ def test_gemm_skinny(out, M, N, K):
     assert torch.equal(c2, c)
 
 
+@pytest.mark.parametrize("out", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (200, 520, 192), (65, 96, 4096), (300, 301 * 8, 96),
+                                   (2048, 1024, 1024)])
+def test_gemm_tc_normal(out, M, N, K):
+    k = _k()
+    a, a_ref = _rand((M, K), torch.bfloat16, 30)
+    w, w_ref = _rand((N, K), torch.bfloat16, 31)
+    c = torch.full((M, N), float("nan"), dtype=DT[out], device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.gemm_tc_bf16(c, a, w, status=status)
+    assert int(status.item()) == 0
+    assert _rel(c, a_ref @ w_ref.T) <= (2e-5 if out == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("out", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K,splits", [(1, 128, 64, 1), (8, 256, 512, 1), (8, 384, 4096, 4), (16, 130, 192, 3),
+                                          (17, 1000, 256, 2), (33, 520, 12288, 5), (64, 6144, 4096, 3),
+                                          (5, 301 * 8, 96, 1)])
+def test_gemm_tc_swapped(out, M, N, K, splits):
+    k = _k()
+    a, a_ref = _rand((M, K), torch.bfloat16, 32)
+    w, w_ref = _rand((N, K), torch.bfloat16, 33)
+    c = torch.full((M, N), float("nan"), dtype=DT[out], device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    partial = torch.empty(splits * M * N, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(-(-N // 128), dtype=torch.int32, device="cuda")
+    for _ in range(2):  # the counters are left at zero for the next launch
+        c.fill_(float("nan"))
+        k.gemm_tc_bf16(c, a, w, splits, partial, counters, status)
+        assert int(status.item()) == 0
+        assert _rel(c, a_ref @ w_ref.T) <= (2e-5 if out == "float32" else 8e-3)
+    assert int(counters.abs().sum().item()) == 0
+    assert k.gemm_tc_splits(M, N, K) >= 1
+
+
 def test_gemm_skinny_refuses():
     from ccinfer_b200.errors import Unsupported
     k = _k()
