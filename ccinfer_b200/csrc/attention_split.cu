@@ -366,3 +366,66 @@ CCB_API int ccb_attention_split(const void* q, const void* k_cache, const void* 
                                   window, scale, num_splits, status, stream);
   return CCB_REFUSE_DTYPE;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for callers that cannot allocate (declared in attention_split_noalloc.h).
+// ---------------------------------------------------------------------------------------------
+#include "attention_split_noalloc.h"
+#include <mutex>
+
+namespace {
+
+// Scratch of the split partials, part of the library image itself: every GPU that loads the library holds
+// these CCB_NOALLOC_SCRATCH_FLOATS * 4 bytes until the process exits.
+static __device__ __align__(256) float g_noalloc_scratch[CCB_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};  // device address of the array on each device, found at set-up
+std::mutex g_noalloc_mu;
+
+// In host code `g_noalloc_scratch` is only a handle of the symbol, not an address a kernel may use; the
+// device address is asked for once per device, with that device current.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return CCB_REFUSE_ARG;
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return CCB_REFUSE_ARG;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+CCB_API int ccb_attention_split_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        const int* positions, const int* entry_of_token, const int* block_table,
+                                        int bt_stride, int n_entries, int row0, int n_rows, int nq, int nkv,
+                                        int hd, int page_size, int num_pages, int window, float scale,
+                                        int num_splits, int dtype, int* status, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (num_splits <= 0 || nq <= 0 || hd <= 0) return CCB_REFUSE_SIZE;
+  float* part_acc = nullptr;
+  float* part_ml = nullptr;
+  if (num_splits > 1) {
+    // accumulators first, then (maximum, sum) pairs; both are written in full by every launch before they
+    // are read, so nothing has to be cleared between calls
+    const size_t n_acc = (size_t)n_rows * nq * num_splits * hd;
+    const size_t n_ml = (size_t)n_rows * nq * num_splits * 2;
+    if (n_acc + n_ml > (size_t)CCB_NOALLOC_SCRATCH_FLOATS) return CCB_REFUSE_NOALLOC_TOO_LARGE;
+    float* base = nullptr;
+    const int rc = noalloc_scratch(&base);
+    if (rc != 0) return rc;
+    part_acc = base;
+    part_ml = base + n_acc;
+  }
+  return ccb_attention_split(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
+                             bt_stride, n_entries, row0, n_rows, nq, nkv, hd, page_size, num_pages, window, scale,
+                             num_splits, dtype, status, stream);
+}
