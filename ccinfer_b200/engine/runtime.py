@@ -56,15 +56,33 @@ class Runtime:
         self.scratch = ScratchPool(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.cublas = kernels.CublasHandle(self.device) if dtype == torch.bfloat16 else None
+        self.tc_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)  # split-K tile counters
 
     def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """out[M, N] = x[M, K] @ w[N, K]^T; out may be float for bfloat16 operands (the logits)."""
         if self.dtype == torch.float32:
             kernels.gemm_f32(out, x, w)
-        elif kernels.gemm_skinny_fits(x.shape[0], x.shape[1], x, w):
-            kernels.gemm_skinny_bf16(out, x, w)   # a few tokens: stream the weights with our own kernel
-        else:
-            self.cublas.gemm_bf16(out, x, w)
+            return out
+        M, K = x.shape
+        N = w.shape[0]
+        if M <= kernels.SKINNY_MAX_ROWS:
+            # A few tokens: the product is a stream of the weights.  Measured on B200 (graph-timed, weights
+            # larger than L2): the TMA + tcgen05 kernel wins where one block per 128 features fills the
+            # machine or K is long enough to be cut into slices; the register-streaming kernel wins on the
+            # small square products.
+            tc = kernels.gemm_tc_fits(K, x, w) and (-(-N // 128) >= kernels.TC_TARGET_BLOCKS or K >= 8192)
+            if tc:
+                splits = kernels.gemm_tc_splits(M, N, K)
+                partial = counters = None
+                if splits > 1:
+                    partial = self.scratch.get("tc_partial", (splits * kernels.SKINNY_MAX_ROWS * N,), torch.float32)
+                    counters = self.tc_counters
+                kernels.gemm_tc_bf16(out, x, w, splits, partial, counters, self.status)
+                return out
+            if kernels.gemm_skinny_fits(M, K, x, w):
+                kernels.gemm_skinny_bf16(out, x, w)
+                return out
+        self.cublas.gemm_bf16(out, x, w)
         return out
 
     def check_status(self) -> None:
