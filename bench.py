@@ -124,6 +124,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, '' for none")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--pdl", type=int, default=1, help="0 off, 1 products start early, 2 every kernel")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -158,7 +159,8 @@ def main() -> int:
     page = 16
     per_req = -(-(ctx + W + K + 2) // page) * page
     opt = EngineOptions(dtype="bfloat16", page_size=page, kv_tokens=max(batches) * per_req,
-                        max_requests=max(batches), max_tokens_per_step=max(2048, ctx), max_context=per_req)
+                        max_requests=max(batches), max_tokens_per_step=max(2048, ctx), max_context=per_req,
+                        use_pdl=args.pdl)
     t0 = time.time()
     engine = Engine.from_random(cfg, seed=42, std=0.02, options=opt)
     torch.cuda.synchronize()

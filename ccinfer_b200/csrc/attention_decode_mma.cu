@@ -29,6 +29,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             const int* __restrict__ block_table, int bt_stride, int n_entries, int row0, int nq,
                             int nkv, int page_size, int num_pages, int window, float scale, int num_splits,
                             int* status) {
+  ccb::pdl_begin();
   constexpr int CH = HD / 8;            // 16-byte chunks per row
   constexpr int KS = HD / 16;           // k steps of q.k, and pairs of 8-wide output blocks of P v
   constexpr int TILE_ELEMS = kTileKeys * HD;
@@ -200,6 +201,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       }
     }
     cp_async_wait<0>();
+    pdl_trigger();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -256,6 +258,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 __global__ void attention_merge_bf16_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_acc,
                                             const float* __restrict__ part_ml, int row0, int nq, int hd,
                                             int num_splits) {
+  ccb::pdl_begin();
   const int r = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)r * nq + h) * num_splits;
   float mm = -CUDART_INF_F;
@@ -289,13 +292,13 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
     configured = true;
   }
   dim3 grid(n_rows, nkv * gchunks, num_splits);
-  attention_decode_mma_kernel<HD><<<grid, kThreads, smem, stream>>>(
+  ccb_launch(attention_decode_mma_kernel<HD>, grid, kThreads, smem, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
       part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries, row0, nq, nkv, page_size,
       num_pages, window, scale, num_splits, status);
   int rc = ccb_launch_status();
   if (rc != 0 || num_splits == 1) return rc;
-  attention_merge_bf16_kernel<<<dim3(n_rows, nq), 128, 0, stream>>>((__nv_bfloat16*)out, part_acc, part_ml, row0,
+  ccb_launch(attention_merge_bf16_kernel, dim3(n_rows, nq), 128, 0, stream, (__nv_bfloat16*)out, part_acc, part_ml, row0,
                                                                      nq, HD, num_splits);
   return ccb_launch_status();
 }

@@ -46,6 +46,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                                const int* __restrict__ block_table, int bt_stride, int n_entries, int nq, int nkv,
                                int hd, int page_size, int num_pages, int window, float scale, int* status) {
+  ccb::pdl_begin();
   extern __shared__ float smem[];
   float* q_s = smem;                          // [hd]
   float* acc_s = smem + hd;                   // [warps][hd]
@@ -164,11 +165,11 @@ CCB_API int ccb_paged_attention_generic(const void* q, const void* k_cache, cons
   dim3 grid(T_, nq);
   const size_t smem = sizeof(float) * (hd + kAttnWarps * hd + 2 * kAttnWarps);
   if (dtype == CCB_F32)
-    paged_attention_generic_kernel<float><<<grid, kAttnWarps * 32, smem, stream>>>(
+    ccb_launch(paged_attention_generic_kernel<float>, grid, kAttnWarps * 32, smem, stream, 
         (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, positions, entry_of_token,
         block_table, bt_stride, n_entries, nq, nkv, hd, page_size, num_pages, window, scale, status);
   else if (dtype == CCB_BF16)
-    paged_attention_generic_kernel<__nv_bfloat16><<<grid, kAttnWarps * 32, smem, stream>>>(
+    ccb_launch(paged_attention_generic_kernel<__nv_bfloat16>, grid, kAttnWarps * 32, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, positions, entry_of_token, block_table, bt_stride, n_entries, nq, nkv, hd, page_size,
         num_pages, window, scale, status);

@@ -32,6 +32,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
                              const int* __restrict__ cu_q, const int* __restrict__ pos0,
                              const int* __restrict__ block_table, int bt_stride, int entry0, int nq, int nkv,
                              int page_size, int num_pages, int window, float scale_log2, int* status) {
+  ccb::pdl_begin();
   constexpr int CH = HD / 8;
   constexpr int KS = HD / 16;
   constexpr int TILE_ELEMS = kKTile * HD;
@@ -247,7 +248,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
     configured = true;
   }
   dim3 grid((max_new + kQTile - 1) / kQTile, nq, n_entries);
-  attention_prefill_mma_kernel<HD><<<grid, kPThreads, smem, stream>>>(
+  ccb_launch(attention_prefill_mma_kernel<HD>, grid, kPThreads, smem, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
       cu_q, pos0, block_table, bt_stride, entry0, nq, nkv, page_size, num_pages, window,
       scale * 1.4426950408889634f, status);

@@ -57,6 +57,7 @@ attention_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                        const int* __restrict__ block_table, int bt_stride, int n_entries, int row0, int nq, int nkv,
                        int hd, int page_size, int num_pages, int window, float scale, int num_splits,
                        int* status) {
+  ccb::pdl_begin();
   extern __shared__ float smem[];  // [warps][GT][hd] accumulators, then [warps][GT] max, [warps][GT] sum
   const int G = nq / nkv;
   const int gchunks = (G + GT - 1) / GT;
@@ -271,6 +272,7 @@ attention_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
 template <typename T>
 __global__ void attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
                                        const float* __restrict__ part_ml, int row0, int nq, int hd, int num_splits) {
+  ccb::pdl_begin();
   const int r = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)r * nq + h) * num_splits;
   float mm = -CUDART_INF_F;
@@ -298,16 +300,16 @@ int launch_split(const void* q, const void* k_cache, const void* v_cache, void* 
   const int G = nq / nkv, gchunks = (G + GT - 1) / GT;
   dim3 grid(n_rows, nkv * gchunks, num_splits);
   const size_t smem = sizeof(float) * (kWarps * GT * hd + 2 * kWarps * GT);
-  attention_split_kernel<T, GT, NV><<<grid, kWarps * 32, smem, stream>>>(
+  ccb_launch(attention_split_kernel<T, GT, NV>, grid, kWarps * 32, smem, stream, 
       (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, part_acc, part_ml, positions, entry_of_token,
       block_table, bt_stride, n_entries, row0, nq, nkv, hd, page_size, num_pages, window, scale, num_splits, status);
   int rc = ccb_launch_status();
   if (rc != 0 || num_splits == 1) return rc;
   if (std::is_same<T, float>::value)
-    attention_merge_kernel<float><<<dim3(n_rows, nq), 128, 0, stream>>>((float*)out, part_acc, part_ml, row0, nq, hd,
+    ccb_launch(attention_merge_kernel<float>, dim3(n_rows, nq), 128, 0, stream, (float*)out, part_acc, part_ml, row0, nq, hd,
                                                                          num_splits);
   else
-    attention_merge_kernel<__nv_bfloat16><<<dim3(n_rows, nq), 128, 0, stream>>>((__nv_bfloat16*)out, part_acc,
+    ccb_launch(attention_merge_kernel<__nv_bfloat16>, dim3(n_rows, nq), 128, 0, stream, (__nv_bfloat16*)out, part_acc,
                                                                                  part_ml, row0, nq, hd, num_splits);
   return ccb_launch_status();
 }

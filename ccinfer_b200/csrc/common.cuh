@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <utility>
 
 #define CCB_API extern "C" __attribute__((visibility("default")))
 
@@ -62,6 +63,18 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return total;
 }
 
+// Programmatic dependent launch.  A kernel launched with the attribute may start while its predecessor in
+// the stream still runs; `pdl_wait` blocks until the predecessor has completed and its writes are visible,
+// `pdl_trigger` lets the successor start early in turn.  Without the attribute both are no-ops.
+// Every kernel calls pdl_begin() (or the two halves, with read-only prefetching of weights in between)
+// before it touches memory that another kernel may have written.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Kernels without weights to prefetch: wait first; they trigger their successor late (pdl_trigger() after
+// their main loop, or implicitly at exit), so that the successor's launch overlaps only their tail and does
+// not take SM resources away while they still need them.
+__device__ __forceinline__ void pdl_begin() { pdl_wait(); }
+
 __device__ __forceinline__ void set_status(int* status, int bit) {
   if (status != nullptr) atomicOr(status, bit);
 }
@@ -75,3 +88,31 @@ __device__ __forceinline__ void set_status(int* status, int bit) {
 #define CCB_REFUSE_ARG (-4)
 
 static inline int ccb_launch_status() { return (int)cudaGetLastError(); }
+
+// One switch for the whole library (ccb_set_pdl): launch kernels with programmatic stream serialization.
+extern int g_ccb_pdl;
+
+// `early`: this kernel gains from starting before its predecessor has finished (it prefetches weights).
+template <typename... KArgs, typename... Args>
+static inline void ccb_launch_ex(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (g_ccb_pdl && (early || g_ccb_pdl > 1)) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // the error is read by ccb_launch_status()
+}
+
+template <typename... KArgs, typename... Args>
+static inline void ccb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  ccb_launch_ex(false, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
+}

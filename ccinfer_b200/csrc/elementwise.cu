@@ -8,9 +8,18 @@
 
 using namespace ccb;
 
+int g_ccb_pdl = 0;
+
+// 1: launch every kernel of the library so that it may overlap the end of its predecessor (see common.cuh)
+CCB_API int ccb_set_pdl(int on) {
+  g_ccb_pdl = on < 0 ? 0 : (on > 2 ? 2 : on);  // 1: products only; 2: every kernel
+  return 0;
+}
+
 template <typename T>
 __global__ void embed_gather_kernel(float* __restrict__ h, const T* __restrict__ table,
                                     const int* __restrict__ ids, int D, int V, int* status) {
+  ccb::pdl_begin();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* out = h + (size_t)t * D;
@@ -29,9 +38,9 @@ CCB_API int ccb_embed_gather(float* h, const void* table, const int* ids, int T_
   if (D <= 0 || V <= 0) return CCB_REFUSE_SIZE;
   const int threads = D >= 1024 ? 256 : 128;
   if (dtype == CCB_F32)
-    embed_gather_kernel<float><<<T_, threads, 0, stream>>>(h, (const float*)table, ids, D, V, status);
+    ccb_launch(embed_gather_kernel<float>, T_, threads, 0, stream, h, (const float*)table, ids, D, V, status);
   else if (dtype == CCB_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(h, (const __nv_bfloat16*)table, ids, D, V, status);
+    ccb_launch(embed_gather_kernel<__nv_bfloat16>, T_, threads, 0, stream, h, (const __nv_bfloat16*)table, ids, D, V, status);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
@@ -44,6 +53,7 @@ template <> __device__ __forceinline__ float silu<__nv_bfloat16>(float g) { retu
 
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ act, const T* __restrict__ gu, int F, size_t total) {
+  ccb::pdl_begin();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += stride) {
@@ -59,6 +69,7 @@ __global__ void silu_mul_kernel(T* __restrict__ act, const T* __restrict__ gu, i
 // bf16, F even: two elements per thread
 __global__ void silu_mul_bf16x2_kernel(__nv_bfloat162* __restrict__ act, const __nv_bfloat162* __restrict__ gu,
                                        int F2, size_t total2) {
+  ccb::pdl_begin();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total2; i += stride) {
@@ -79,15 +90,15 @@ CCB_API int ccb_silu_mul(void* act, const void* gate_up, int T_, int F, int dtyp
   if (dtype == CCB_BF16 && (F % 2) == 0) {
     const size_t total2 = total / 2;
     const int blocks = (int)((total2 + threads - 1) / threads < 148 * 16 ? (total2 + threads - 1) / threads : 148 * 16);
-    silu_mul_bf16x2_kernel<<<blocks, threads, 0, stream>>>((__nv_bfloat162*)act, (const __nv_bfloat162*)gate_up,
+    ccb_launch(silu_mul_bf16x2_kernel, blocks, threads, 0, stream, (__nv_bfloat162*)act, (const __nv_bfloat162*)gate_up,
                                                             F / 2, total2);
     return ccb_launch_status();
   }
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == CCB_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)act, (const float*)gate_up, F, total);
+    ccb_launch(silu_mul_kernel<float>, blocks, threads, 0, stream, (float*)act, (const float*)gate_up, F, total);
   else if (dtype == CCB_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)act, (const __nv_bfloat16*)gate_up, F, total);
+    ccb_launch(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)act, (const __nv_bfloat16*)gate_up, F, total);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();

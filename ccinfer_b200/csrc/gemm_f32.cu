@@ -16,6 +16,7 @@ template <int TM>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A, const float* __restrict__ W, int M, int N,
                 int K, int lda, int ldw, int ldc) {
+  ccb::pdl_begin();
   constexpr int BM = 16 * TM;
   __shared__ __align__(16) float As[kBK][BM];
   __shared__ __align__(16) float Ws[kBK][kBN];
@@ -103,12 +104,12 @@ CCB_API int ccb_gemm_f32(float* C, const float* A, const float* W, int M, int N,
   if (K <= 0 || lda < K || ldw < K || ldc < N) return CCB_REFUSE_SIZE;
   const int gx = (N + kBN - 1) / kBN;
   if (M <= 16)
-    gemm_f32_kernel<1><<<dim3(gx, (M + 15) / 16), 256, 0, stream>>>(C, A, W, M, N, K, lda, ldw, ldc);
+    ccb_launch(gemm_f32_kernel<1>, dim3(gx, (M + 15) / 16), 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
   else if (M <= 32)
-    gemm_f32_kernel<2><<<dim3(gx, (M + 31) / 32), 256, 0, stream>>>(C, A, W, M, N, K, lda, ldw, ldc);
+    ccb_launch(gemm_f32_kernel<2>, dim3(gx, (M + 31) / 32), 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
   else if (M <= 64)
-    gemm_f32_kernel<4><<<dim3(gx, (M + 63) / 64), 256, 0, stream>>>(C, A, W, M, N, K, lda, ldw, ldc);
+    ccb_launch(gemm_f32_kernel<4>, dim3(gx, (M + 63) / 64), 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
   else
-    gemm_f32_kernel<8><<<dim3(gx, (M + 127) / 128), 256, 0, stream>>>(C, A, W, M, N, K, lda, ldw, ldc);
+    ccb_launch(gemm_f32_kernel<8>, dim3(gx, (M + 127) / 128), 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
   return ccb_launch_status();
 }

@@ -58,6 +58,16 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
   for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.f;
 
   constexpr int U = 4;  // 32-wide k blocks in flight per warp
+  // The weights do not depend on the kernel before this one: ask L2 for this warp's first lines, then wait
+  // for that kernel (programmatic dependent launch) before the token operand is read.
+#pragma unroll
+  for (int u = 0; u < 2 * U; ++u) {
+    if (kb0 + u < kb1) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(w0 + ((kb0 + u) << 5)));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(w1 + ((kb0 + u) << 5)));
+    }
+  }
+  pdl_wait();
   int kb = kb0;
   for (; kb + U <= kb1; kb += U) {
     uint4 a0[U], a1[U], x[U][NB];
@@ -93,6 +103,7 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
       mma_bf16_16816(c[nb], fb, x.z, x.w);
     }
   }
+  pdl_trigger();
   // c[nb]: (feature gid, tokens 8 nb + 2 tig, + 1), (feature gid + 8, same tokens)
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {
@@ -118,10 +129,10 @@ int launch_skinny(void* C, const void* A, const void* W, int M, int N, int K, in
                   int out_dtype, cudaStream_t stream) {
   const int blocks = (N + 15) / 16;
   if (out_dtype == CCB_F32)
-    gemm_skinny_kernel<NB, float><<<blocks, kSkinnyWarps * 32, 0, stream>>>(
+    ccb_launch_ex(true, gemm_skinny_kernel<NB, float>, blocks, kSkinnyWarps * 32, 0, stream, 
         (float*)C, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
   else
-    gemm_skinny_kernel<NB, __nv_bfloat16><<<blocks, kSkinnyWarps * 32, 0, stream>>>(
+    ccb_launch_ex(true, gemm_skinny_kernel<NB, __nv_bfloat16>, blocks, kSkinnyWarps * 32, 0, stream, 
         (__nv_bfloat16*)C, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
   return ccb_launch_status();
 }

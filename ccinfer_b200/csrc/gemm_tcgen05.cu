@@ -179,7 +179,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer ----
-      for (int i = 0; i < nkb; ++i) {
+      // The weight operand does not depend on the kernel before this one: its first copies start at once
+      // and run while that kernel finishes; the token operand waits for it (programmatic dependent launch).
+      const int pre = min(nkb, STAGES);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full0 + 8 * i, A_STAGE_BYTES + B_STAGE_BYTES);
+        if (SWAP)
+          tma_load_2d(s32(sA + i * A_STAGE_BYTES), &tmA, (kb0 + i) * BK, tileA * BM, full0 + 8 * i);
+        else
+          tma_load_2d(s32(sB + i * B_STAGE_BYTES), &tmB, (kb0 + i) * BK, tileB * BN, full0 + 8 * i);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+        if (SWAP)
+          tma_load_2d(s32(sB + i * B_STAGE_BYTES), &tmB, (kb0 + i) * BK, tileB * BN, full0 + 8 * i);
+        else
+          tma_load_2d(s32(sA + i * A_STAGE_BYTES), &tmA, (kb0 + i) * BK, tileA * BM, full0 + 8 * i);
+      }
+      for (int i = pre; i < nkb; ++i) {
         const int s = i % STAGES, ph = (i / STAGES) & 1;
         if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) {
           set_status(status, CCB_ST_WAIT_TIMEOUT);
@@ -214,6 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int row = q * 32 + lane;
     const bool ok = mbar_wait(tfull, 0);
     if (!ok && lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
+    pdl_trigger();  // the main loop is over: the next kernel may start its prologue
     tc_fence_after();
     const int ga = tileA * BM + row;  // row of the A-side matrix
     if (ok) {
@@ -344,7 +362,7 @@ int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, 
     configured = true;
   }
   dim3 grid((rowsA + BM - 1) / BM, (rowsB + BN - 1) / BN, splits);
-  gemm_tc_kernel<BN, STAGES, SWAP, TOut><<<grid, kThreadsTc, smem, stream>>>(
+  ccb_launch_ex(true, gemm_tc_kernel<BN, STAGES, SWAP, TOut>, grid, kThreadsTc, smem, stream, 
       tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, status);
   return ccb_launch_status();
 }

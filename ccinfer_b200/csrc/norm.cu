@@ -19,6 +19,7 @@ template <typename T>
 __global__ void residual_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ h, const T* __restrict__ delta,
                                         const float* __restrict__ w, const int* __restrict__ row_idx,
                                         int n_src_rows, int D, float eps, int write_h, int* status) {
+  ccb::pdl_begin();
   __shared__ float red[32];
   const int r = blockIdx.x;
   int src = row_idx ? row_idx[r] : r;
@@ -79,6 +80,7 @@ __global__ void __launch_bounds__(kNormThreads)
 residual_rmsnorm_vec_kernel(T* __restrict__ y, float* __restrict__ h, const T* __restrict__ delta,
                             const float* __restrict__ w, const int* __restrict__ row_idx, int n_src_rows, int D,
                             float eps, int write_h, int* status) {
+  ccb::pdl_begin();
   __shared__ float red[32];
   const int r = blockIdx.x;
   const int src = row_idx ? row_idx[r] : r;
@@ -108,6 +110,7 @@ residual_rmsnorm_vec_kernel(T* __restrict__ y, float* __restrict__ h, const T* _
     }
   }
   ss = block_sum<kNormThreads>(ss, red);
+  pdl_trigger();
   const float inv = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
   for (int j = 0; j < kNormVecs; ++j) {
@@ -130,20 +133,20 @@ CCB_API int ccb_residual_rmsnorm(void* y, float* h, const void* delta, const flo
                    ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(h) |
                      reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   if (vec && dtype == CCB_F32) {
-    residual_rmsnorm_vec_kernel<float><<<rows, kNormThreads, 0, stream>>>(
+    ccb_launch(residual_rmsnorm_vec_kernel<float>, rows, kNormThreads, 0, stream, 
         (float*)y, h, (const float*)delta, w, row_idx, n_src_rows, D, eps, write_h, status);
     return ccb_launch_status();
   }
   if (vec && dtype == CCB_BF16) {
-    residual_rmsnorm_vec_kernel<__nv_bfloat16><<<rows, kNormThreads, 0, stream>>>(
+    ccb_launch(residual_rmsnorm_vec_kernel<__nv_bfloat16>, rows, kNormThreads, 0, stream, 
         (__nv_bfloat16*)y, h, (const __nv_bfloat16*)delta, w, row_idx, n_src_rows, D, eps, write_h, status);
     return ccb_launch_status();
   }
   if (dtype == CCB_F32)
-    residual_rmsnorm_kernel<float><<<rows, kNormThreads, 0, stream>>>(
+    ccb_launch(residual_rmsnorm_kernel<float>, rows, kNormThreads, 0, stream, 
         (float*)y, h, (const float*)delta, w, row_idx, n_src_rows, D, eps, write_h, status);
   else if (dtype == CCB_BF16)
-    residual_rmsnorm_kernel<__nv_bfloat16><<<rows, kNormThreads, 0, stream>>>(
+    ccb_launch(residual_rmsnorm_kernel<__nv_bfloat16>, rows, kNormThreads, 0, stream, 
         (__nv_bfloat16*)y, h, (const __nv_bfloat16*)delta, w, row_idx, n_src_rows, D, eps, write_h, status);
   else
     return CCB_REFUSE_DTYPE;
@@ -154,6 +157,7 @@ CCB_API int ccb_residual_rmsnorm(void* y, float* h, const void* delta, const flo
 template <typename T>
 __global__ void rmsnorm_kernel(T* __restrict__ y, const T* __restrict__ x, const float* __restrict__ w, int D,
                                float eps) {
+  ccb::pdl_begin();
   __shared__ float red[32];
   const T* xr = x + (size_t)blockIdx.x * D;
   T* yr = y + (size_t)blockIdx.x * D;
@@ -172,9 +176,9 @@ CCB_API int ccb_rmsnorm(void* y, const void* x, const float* w, int rows, int D,
   if (rows <= 0) return 0;
   if (D <= 0) return CCB_REFUSE_SIZE;
   if (dtype == CCB_F32)
-    rmsnorm_kernel<float><<<rows, kNormThreads, 0, stream>>>((float*)y, (const float*)x, w, D, eps);
+    ccb_launch(rmsnorm_kernel<float>, rows, kNormThreads, 0, stream, (float*)y, (const float*)x, w, D, eps);
   else if (dtype == CCB_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<rows, kNormThreads, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x, w, D, eps);
+    ccb_launch(rmsnorm_kernel<__nv_bfloat16>, rows, kNormThreads, 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)x, w, D, eps);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();

@@ -24,6 +24,7 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, int row_
                                              const float* __restrict__ inv_freq, const float* __restrict__ q_w,
                                              const float* __restrict__ k_w, float eps, int nq, int nkv, int hd,
                                              int page_size, int num_slots, int* status) {
+  ccb::pdl_begin();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31;
   const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -113,11 +114,11 @@ CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_o
   const int heads = nq + 2 * nkv;
   dim3 grid(T_, (heads + 3) / 4);
   if (dtype == CCB_F32)
-    qk_norm_rope_kv_write_kernel<float><<<grid, 128, 0, stream>>>(
+    ccb_launch(qk_norm_rope_kv_write_kernel<float>, grid, 128, 0, stream, 
         (const float*)qkv, row_stride, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slot_map,
         inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots, status);
   else if (dtype == CCB_BF16)
-    qk_norm_rope_kv_write_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+    ccb_launch(qk_norm_rope_kv_write_kernel<__nv_bfloat16>, grid, 128, 0, stream, 
         (const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots,
         status);

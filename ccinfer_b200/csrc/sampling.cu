@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, size_t ld, int* __restrict__ tokens,
                    const float* __restrict__ temperature, const unsigned* __restrict__ seed,
                    const int* __restrict__ out_index, int V) {
+  ccb::pdl_begin();
   __shared__ float sv[kSampleThreads];
   __shared__ int si[kSampleThreads];
   const int r = blockIdx.x;
@@ -85,6 +86,6 @@ CCB_API int ccb_sample_rows(const float* logits, long long ld, int* tokens, cons
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) return CCB_REFUSE_SIZE;
   if (temperature != nullptr && (seed == nullptr || out_index == nullptr)) return CCB_REFUSE_ARG;
-  sample_rows_kernel<<<R, kSampleThreads, 0, stream>>>(logits, (size_t)ld, tokens, temperature, seed, out_index, V);
+  ccb_launch(sample_rows_kernel, R, kSampleThreads, 0, stream, logits, (size_t)ld, tokens, temperature, seed, out_index, V);
   return ccb_launch_status();
 }

@@ -47,6 +47,7 @@ class EngineOptions:
     max_tokens_per_step: int = 4096  # the reference's compute budget (src/scheduler/scheduler.cpp:25)
     max_context: Optional[int] = None  # longest request; default min(model limit, pool)
     use_graphs: bool = True
+    use_pdl: bool = True             # kernels may start while their predecessor finishes (see csrc/common.cuh)
 
 
 class Engine:
@@ -63,6 +64,7 @@ class Engine:
         self.plan = plan
         self.vocab_size = plan.vocab_size
         self.rt = rt = Runtime(opt.device, self.dtype, opt.max_tokens_per_step, opt.max_requests)
+        kernels.set_pdl(int(opt.use_pdl))
         for part in plan.parts():
             part.bind(rt, fetch)
 

@@ -86,6 +86,15 @@ def lib(group: str = "core"):
         return handle
 
 
+def set_pdl(on) -> None:
+    """Launch the library's kernels so that each may start while its predecessor finishes (programmatic
+    dependent launch); every kernel waits for its predecessor before it reads what that one wrote."""
+    fn = lib().ccb_set_pdl
+    fn.argtypes = [c_int]
+    fn.restype = c_int
+    fn(int(on))
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
