@@ -4,7 +4,7 @@
 //   has cached, its own new keys included (7QiC/ccInfer: src/kernel/attention/prefill_attn.cu:42-242, where
 //   one block serves ONE query token and one head, re-reading the keys for every token).  Here a block
 //   serves 64 consecutive query tokens of one request and one q head: 4 warps x 16 rows.  Keys and values
-//   of 64 positions at a time travel global -> shared memory through a three-stage cp.async pipeline shared
+//   of 64 positions at a time travel global -> shared memory through a two-stage cp.async pipeline shared
 //   by the 4 warps; S = Q K^T and O += P V by mma.sync m16n8k16, online softmax in float registers (base-2
 //   exponentials), one pass over the keys, no scores stored.
 //
@@ -22,11 +22,11 @@ namespace {
 
 constexpr int kQTile = 64;
 constexpr int kKTile = 64;
-constexpr int kPStages = 3;
+constexpr int kPStages = 2;
 constexpr int kPThreads = 128;
 
 template <int HD>
-__global__ void __launch_bounds__(kPThreads)
+__global__ void __launch_bounds__(kPThreads, 3)
 attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                              const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                              const int* __restrict__ cu_q, const int* __restrict__ pos0,
@@ -37,9 +37,11 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   constexpr int KS = HD / 16;
   constexpr int TILE_ELEMS = kKTile * HD;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][HD]
-  __nv_bfloat16* k_s = q_s + kQTile * HD;                            // [stages][64][HD]
+  // Two stages of a key tile and a value tile.  The query tile borrows the second stage's key buffer until
+  // its fragments sit in registers, which keeps a block at 64 KB (head size 128): three blocks per SM.
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [stages][64][HD]
   __nv_bfloat16* v_s = k_s + kPStages * TILE_ELEMS;
+  __nv_bfloat16* q_s = k_s + TILE_ELEMS;                             // [64][HD], before the pipeline starts
 
   const int b = entry0 + blockIdx.z;
   const int h = blockIdx.y;
@@ -105,14 +107,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     }
   };
 
-#pragma unroll
-  for (int s = 0; s < kPStages - 1; ++s) {
-    if (s < n_tiles) issue(first_tile + s, s);
-    cp_async_commit();
-  }
-
-  // Q fragments of this warp's 16 rows (the Q copy is the oldest group: wait for it alone)
-  cp_async_wait<kPStages - 1>();
+  // Q fragments of this warp's 16 rows
+  cp_async_wait<0>();
   __syncthreads();
   uint32_t qa[KS][4];
   {
@@ -122,6 +118,9 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     for (int ks = 0; ks < KS; ++ks)
       ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], smem_u32(q_s + swz<HD>(qrow, 2 * ks + qchunk)));
   }
+  __syncthreads();  // everybody has its fragments: the buffer is a pipeline stage from here on
+  issue(first_tile, 0);
+  cp_async_commit();
   // rows gid and gid + 8 of the warp: their positions and the first key each may see
   const int pr0 = p_first + warp * 16 + gid, pr1 = pr0 + 8;
   const int lo0 = window > 0 ? max(0, pr0 - window + 1) : 0, lo1 = window > 0 ? max(0, pr1 - window + 1) : 0;
@@ -239,7 +238,7 @@ template <int HD>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q, const int* pos0,
            const int* block_table, int bt_stride, int entry0, int n_entries, int max_new, int nq, int nkv,
            int page_size, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
-  const size_t smem = (size_t)(kQTile * HD + 2 * kPStages * kKTile * HD) * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(2 * kPStages * kKTile * HD) * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_mma_kernel<HD>,

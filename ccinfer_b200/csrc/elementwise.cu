@@ -82,11 +82,41 @@ __global__ void silu_mul_bf16x2_kernel(__nv_bfloat162* __restrict__ act, const _
   }
 }
 
+// bf16, F a multiple of 8: eight elements (16 bytes) per thread and access
+__global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ act, const uint4* __restrict__ gu, int F8, size_t total8) {
+  ccb::pdl_begin();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total8; i += stride) {
+    const size_t t = i / F8;
+    const int f = (int)(i - t * F8);
+    const uint4* row = gu + t * 2 * (size_t)F8;
+    const uint4 g = row[f], u = row[F8 + f];
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(gh[e]), b = __bfloat1622float2(uh[e]);
+      oh[e] = __floats2bfloat162_rn(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+    }
+    act[i] = o;
+  }
+}
+
 CCB_API int ccb_silu_mul(void* act, const void* gate_up, int T_, int F, int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (F <= 0) return CCB_REFUSE_SIZE;
   const size_t total = (size_t)T_ * F;
   const int threads = 256;
+  if (dtype == CCB_BF16 && (F % 8) == 0 && ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(gate_up)) & 15) == 0) {
+    const size_t total8 = total / 8;
+    const size_t want = (total8 + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+    ccb_launch(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (uint4*)act, (const uint4*)gate_up, F / 8, total8);
+    return ccb_launch_status();
+  }
   if (dtype == CCB_BF16 && (F % 2) == 0) {
     const size_t total2 = total / 2;
     const int blocks = (int)((total2 + threads - 1) / threads < 148 * 16 ? (total2 + threads - 1) / threads : 148 * 16);

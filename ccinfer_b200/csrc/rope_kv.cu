@@ -102,6 +102,109 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, int row_
   }
 }
 
+// The same with two neighbouring elements per lane and access (head size a multiple of 4): a warp reads
+// and writes 128 (bfloat16) or 256 (float) contiguous bytes per instruction.
+template <typename T> struct Pair2 {};
+template <> struct Pair2<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+};
+template <> struct Pair2<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 v) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y);
+  }
+};
+
+template <typename T>
+__global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int row_stride, T* __restrict__ q_out,
+                                                 T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                 const int* __restrict__ positions,
+                                                 const int* __restrict__ slot_map, const float* __restrict__ inv_freq,
+                                                 const float* __restrict__ q_w, const float* __restrict__ k_w,
+                                                 float eps, int nq, int nkv, int hd, int page_size, int num_slots,
+                                                 int* status) {
+  ccb::pdl_begin();
+  constexpr int kIters = 2;  // pairs of elements per lane: head sizes up to 256
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (head >= nq + 2 * nkv) return;
+  const int half = hd >> 1;
+  const T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+  const bool is_q = head < nq;
+  const bool is_k = !is_q && head < nq + nkv;
+  T* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)t * nq + head) * hd;
+  } else {
+    const int slot = slot_map[t];
+    if (slot < 0) return;
+    if (slot >= num_slots) {
+      if (lane == 0) set_status(status, CCB_ST_BAD_SLOT);
+      return;
+    }
+    const int kvh = is_k ? head - nq : head - nq - nkv;
+    const int page = slot / page_size, off = slot - page * page_size;
+    dst = (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+  }
+  float2 x0[kIters], x1[kIters];
+  float ss = 0.f;
+#pragma unroll
+  for (int m = 0; m < kIters; ++m) {
+    const int i = 2 * lane + 64 * m;
+    if (i < half) {
+      x0[m] = Pair2<T>::load(src + i);
+      x1[m] = Pair2<T>::load(src + i + half);
+      ss += x0[m].x * x0[m].x + x0[m].y * x0[m].y + x1[m].x * x1[m].x + x1[m].y * x1[m].y;
+    }
+  }
+  if (!is_q && !is_k) {
+#pragma unroll
+    for (int m = 0; m < kIters; ++m) {
+      const int i = 2 * lane + 64 * m;
+      if (i < half) {
+        Pair2<T>::store(dst + i, x0[m]);
+        Pair2<T>::store(dst + i + half, x1[m]);
+      }
+    }
+    return;
+  }
+  const float* w = is_q ? q_w : k_w;
+  float inv = 1.f;
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    inv = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  const float fpos = (float)positions[t];
+#pragma unroll
+  for (int m = 0; m < kIters; ++m) {
+    const int i = 2 * lane + 64 * m;
+    if (i < half) {
+      float a[2] = {x0[m].x, x0[m].y}, b[2] = {x1[m].x, x1[m].y};
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (w != nullptr) {
+          a[e] = a[e] * inv * w[i + e];
+          b[e] = b[e] * inv * w[i + e + half];
+        }
+        if (inv_freq != nullptr) {
+          float sn, cs;
+          sincosf(fpos * inv_freq[i + e], &sn, &cs);
+          const float ra = a[e] * cs - b[e] * sn;
+          const float rb = b[e] * cs + a[e] * sn;
+          a[e] = ra;
+          b[e] = rb;
+        }
+      }
+      Pair2<T>::store(dst + i, make_float2(a[0], a[1]));
+      Pair2<T>::store(dst + i + half, make_float2(b[0], b[1]));
+    }
+  }
+}
+
 CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_out, void* k_cache, void* v_cache,
                                       const int* positions, const int* slot_map, const float* inv_freq,
                                       const float* q_w, const float* k_w, float eps, int T_, int nq, int nkv,
@@ -113,6 +216,22 @@ CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_o
   if (nkv > 0 && (k_cache == nullptr || v_cache == nullptr || slot_map == nullptr)) return CCB_REFUSE_ARG;
   const int heads = nq + 2 * nkv;
   dim3 grid(T_, (heads + 3) / 4);
+  // two elements per access where every pointer and stride allows it
+  const bool vec = (hd % 4 == 0) && (row_stride % 2 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                     reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 7) == 0;
+  if (vec && dtype == CCB_F32) {
+    ccb_launch(qk_norm_rope_kv_write_vec_kernel<float>, grid, 128, 0, stream, (const float*)qkv, row_stride,
+               (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, nq, nkv,
+               hd, page_size, num_slots, status);
+    return ccb_launch_status();
+  }
+  if (vec && dtype == CCB_BF16) {
+    ccb_launch(qk_norm_rope_kv_write_vec_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)qkv,
+               row_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, positions,
+               slot_map, inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots, status);
+    return ccb_launch_status();
+  }
   if (dtype == CCB_F32)
     ccb_launch(qk_norm_rope_kv_write_kernel<float>, grid, 128, 0, stream, 
         (const float*)qkv, row_stride, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slot_map,
