@@ -58,16 +58,7 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
   for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.f;
 
   constexpr int U = 4;  // 32-wide k blocks in flight per warp
-  // The weights do not depend on the kernel before this one: ask L2 for this warp's first lines, then wait
-  // for that kernel (programmatic dependent launch) before the token operand is read.
-#pragma unroll
-  for (int u = 0; u < 2 * U; ++u) {
-    if (kb0 + u < kb1) {
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(w0 + ((kb0 + u) << 5)));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(w1 + ((kb0 + u) << 5)));
-    }
-  }
-  pdl_wait();
+  pdl_wait();  // before the token operand (written by the kernel before this one) is read
   int kb = kb0;
   for (; kb + U <= kb1; kb += U) {
     uint4 a0[U], a1[U], x[U][NB];

@@ -285,10 +285,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (*last_flag) {
           __threadfence();
           if (ga < rowsA) {
-            for (int t = tileB * BN; t < min(rowsB, tileB * BN + BN); ++t) {
-              float acc = 0.f;
-              for (int s = 0; s < splits; ++s) acc += __ldcg(&partial[((size_t)s * rowsB + t) * rowsA + ga]);
-              C[(size_t)t * ldc + ga] = from_f32<TOut>(acc);
+            // all loads of a group of tokens are issued before the first sum: the slices are added in
+            // ascending order, but nobody waits for one load at a time
+            constexpr int TG = 4, SMAX = 16;
+            const int t_end = min(rowsB, tileB * BN + BN);
+            for (int t0 = tileB * BN; t0 < t_end; t0 += TG) {
+              float v[TG][SMAX];
+#pragma unroll
+              for (int i = 0; i < TG; ++i)
+#pragma unroll
+                for (int s = 0; s < SMAX; ++s)
+                  v[i][s] = (t0 + i < t_end && s < splits)
+                                ? __ldcg(&partial[((size_t)s * rowsB + t0 + i) * rowsA + ga]) : 0.f;
+#pragma unroll
+              for (int i = 0; i < TG; ++i) {
+                if (t0 + i < t_end) {
+                  float acc = 0.f;
+#pragma unroll
+                  for (int s = 0; s < SMAX; ++s) acc += v[i][s];  // slices beyond `splits` are exact zeros
+                  C[(size_t)(t0 + i) * ldc + ga] = from_f32<TOut>(acc);
+                }
+              }
             }
           }
         }
@@ -398,7 +415,7 @@ CCB_API int ccb_gemm_tc_bf16(void* C, const void* A, const void* W, int M, int N
       (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return CCB_REFUSE_SIZE;
   const int kb_total = (K + BK - 1) / BK;
-  if (splits < 1 || splits > kb_total || (splits > 1 && (M > 64 || partial == nullptr || counters == nullptr)))
+  if (splits < 1 || splits > 16 || splits > kb_total || (splits > 1 && (M > 64 || partial == nullptr || counters == nullptr)))
     return CCB_REFUSE_ARG;
   if (splits > 1) {  // every slice must hold at least one k block
     const int per = (kb_total + splits - 1) / splits;

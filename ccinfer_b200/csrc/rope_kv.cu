@@ -125,14 +125,24 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
                                                  const int* __restrict__ slot_map, const float* __restrict__ inv_freq,
                                                  const float* __restrict__ q_w, const float* __restrict__ k_w,
                                                  float eps, int nq, int nkv, int hd, int page_size, int num_slots,
-                                                 int* status) {
+                                                 int heads_per_block, int* status) {
   ccb::pdl_begin();
   constexpr int kIters = 2;  // pairs of elements per lane: head sizes up to 256
+  __shared__ float2 cs_table[128];  // (cos, sin) of this token's angles, shared by all heads of the block
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31;
-  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (head >= nq + 2 * nkv) return;
   const int half = hd >> 1;
+  if (inv_freq != nullptr) {
+    const float fpos_t = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float sn, cs;
+      sincosf(fpos_t * inv_freq[i], &sn, &cs);
+      cs_table[i] = make_float2(cs, sn);
+    }
+  }
+  __syncthreads();
+  const int head_end = min(nq + 2 * nkv, (int)(blockIdx.y + 1) * heads_per_block);
+  for (int head = blockIdx.y * heads_per_block + (threadIdx.x >> 5); head < head_end; head += (blockDim.x >> 5)) {
   const T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
   const bool is_q = head < nq;
   const bool is_k = !is_q && head < nq + nkv;
@@ -141,10 +151,10 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
     dst = q_out + ((size_t)t * nq + head) * hd;
   } else {
     const int slot = slot_map[t];
-    if (slot < 0) return;
+    if (slot < 0) continue;
     if (slot >= num_slots) {
       if (lane == 0) set_status(status, CCB_ST_BAD_SLOT);
-      return;
+      continue;
     }
     const int kvh = is_k ? head - nq : head - nq - nkv;
     const int page = slot / page_size, off = slot - page * page_size;
@@ -170,7 +180,7 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
         Pair2<T>::store(dst + i + half, x1[m]);
       }
     }
-    return;
+    continue;
   }
   const float* w = is_q ? q_w : k_w;
   float inv = 1.f;
@@ -178,7 +188,6 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
     ss = warp_sum(ss);
     inv = 1.0f / sqrtf(ss / (float)hd + eps);
   }
-  const float fpos = (float)positions[t];
 #pragma unroll
   for (int m = 0; m < kIters; ++m) {
     const int i = 2 * lane + 64 * m;
@@ -191,10 +200,9 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
           b[e] = b[e] * inv * w[i + e + half];
         }
         if (inv_freq != nullptr) {
-          float sn, cs;
-          sincosf(fpos * inv_freq[i + e], &sn, &cs);
-          const float ra = a[e] * cs - b[e] * sn;
-          const float rb = b[e] * cs + a[e] * sn;
+          const float2 c = cs_table[i + e];
+          const float ra = a[e] * c.x - b[e] * c.y;
+          const float rb = b[e] * c.x + a[e] * c.y;
           a[e] = ra;
           b[e] = rb;
         }
@@ -202,6 +210,7 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
       Pair2<T>::store(dst + i, make_float2(a[0], a[1]));
       Pair2<T>::store(dst + i + half, make_float2(b[0], b[1]));
     }
+  }
   }
 }
 
@@ -220,16 +229,19 @@ CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_o
   const bool vec = (hd % 4 == 0) && (row_stride % 2 == 0) &&
                    ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                      reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 7) == 0;
+  // few tokens: many small blocks; many tokens: 16 heads a block, so the angles are computed 16x less often
+  const int hpb = T_ <= 64 ? 4 : 16;
+  dim3 vgrid(T_, (heads + hpb - 1) / hpb);
   if (vec && dtype == CCB_F32) {
-    ccb_launch(qk_norm_rope_kv_write_vec_kernel<float>, grid, 128, 0, stream, (const float*)qkv, row_stride,
+    ccb_launch(qk_norm_rope_kv_write_vec_kernel<float>, vgrid, 128, 0, stream, (const float*)qkv, row_stride,
                (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, nq, nkv,
-               hd, page_size, num_slots, status);
+               hd, page_size, num_slots, hpb, status);
     return ccb_launch_status();
   }
   if (vec && dtype == CCB_BF16) {
-    ccb_launch(qk_norm_rope_kv_write_vec_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)qkv,
+    ccb_launch(qk_norm_rope_kv_write_vec_kernel<__nv_bfloat16>, vgrid, 128, 0, stream, (const __nv_bfloat16*)qkv,
                row_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, positions,
-               slot_map, inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots, status);
+               slot_map, inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots, hpb, status);
     return ccb_launch_status();
   }
   if (dtype == CCB_F32)
