@@ -1,0 +1,345 @@
+// Prefill attention on the 5th-generation tensor cores (bfloat16, head size 128 or 64).
+//
+//   causal (optionally windowed) attention of the new tokens of each request over its paged cache, as
+//   attention_prefill_mma_kernel computes it (7QiC/ccInfer: src/kernel/attention/prefill_attn.cu:42-242),
+//   but with both products on tcgen05.mma and both accumulators in tensor memory:
+//
+//   block = (128 query tokens of one request, one q head); per tile of 128 key positions
+//     S = Q K^T          tcgen05.mma  M=128 N=128 K=head   -> TMEM columns [0, 128)
+//     P = softmax part   four warps, one query row per thread: tcgen05.ld S, mask, running max and sum in
+//                        float (base-2 exponentials), P as bfloat16 into shared memory in the 128-byte
+//                        swizzle; the running output in TMEM is rescaled when the maximum moved
+//     O += P V           tcgen05.mma  M=128 N=head K=128  (V is the MN-major operand) -> TMEM columns [128, ..)
+//   Q, K and V tiles arrive by TMA: Q as two boxes of 128 rows x 64 columns, K and V page by page (a box is
+//   one page of one kv head: page_size rows x 64 columns), two stages.  Warp 0 issues the copies, warp 1 the
+//   products, warps 2..5 do the softmax, the rescaling and the final division and store.
+//
+// Key tiles are aligned to absolute positions, so a row's result depends on its position and its request's
+// keys only.  Every mbarrier wait is bounded (CCB_ST_WAIT_TIMEOUT, then the block tears down and returns).
+#include "common.cuh"
+#include "tc_common.cuh"
+#include "tma_host.h"
+#include <math_constants.h>
+
+using namespace ccb;
+
+namespace {
+
+constexpr int kTQ = 128;     // query rows per block = TMEM lanes
+constexpr int kTK = 128;     // keys per tile
+constexpr int kTcThreads = 192;
+constexpr int kKvStages = 2;
+
+// HD = 64 * NH
+template <int NH>
+__global__ void __launch_bounds__(kTcThreads, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                            const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
+                            const int* __restrict__ cu_q, const int* __restrict__ pos0,
+                            const int* __restrict__ block_table, int bt_stride, int entry0, int nq, int nkv,
+                            int page_size, int page_shift, int num_pages, int window, float scale_log2,
+                            int* status) {
+  constexpr int HD = 64 * NH;
+  constexpr int HALF_BYTES = 128 * 128;            // 128 rows x 128 bytes: one 64-column half of a tile
+  constexpr int TILE_BYTES = NH * HALF_BYTES;      // Q, K or V tile
+  constexpr int P_BYTES = 2 * HALF_BYTES;          // 128 rows x 128 keys
+  constexpr int TMEM_COLS = 256;                   // S: 128 columns, O: HD columns
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;                   // [stages]
+  uint8_t* sV = sK + kKvStages * TILE_BYTES;       // [stages]
+  uint8_t* sP = sV + kKvStages * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_full, p_ready, pv_done
+  const uint32_t b_q = s32(bars), b_kf = s32(bars + 1), b_vf = s32(bars + 3), b_ke = s32(bars + 5),
+                 b_sf = s32(bars + 7), b_pr = s32(bars + 8), b_pv = s32(bars + 9);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+
+  const int b = entry0 + blockIdx.z;
+  const int h = blockIdx.y;
+  const int row_begin = cu_q[b], n_new = cu_q[b + 1] - row_begin;
+  const int n_qtiles = (n_new + kTQ - 1) / kTQ;
+  const int qt = n_qtiles - 1 - (int)blockIdx.x;   // long tiles first
+  if (qt < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = h / (nq / nkv);
+  const int p0 = pos0[b];
+  const int q_first = qt * kTQ;
+  const int rows_here = min(kTQ, n_new - q_first);
+  const int p_first = p0 + q_first, p_last = p_first + rows_here - 1;
+  const int* bt = block_table + (size_t)b * bt_stride;
+  const int j_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int first_tile = j_lo / kTK, last_tile = p_last / kTK;
+  const int n_tiles = last_tile - first_tile + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(b_q, 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(b_kf + 8 * s, 1);
+      mbar_init(b_vf + 8 * s, 1);
+      mbar_init(b_ke + 8 * s, 1);
+    }
+    mbar_init(b_sf, 1);
+    mbar_init(b_pr, 128);
+    mbar_init(b_pv, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer ----
+      pdl_wait();
+      mbar_expect_tx(b_q, TILE_BYTES);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf)
+        tma_load_2d(s32(sQ + hf * HALF_BYTES), &tmQ, h * HD + hf * 64, row_begin + q_first, b_q);
+      const int pages_per_tile = kTK >> page_shift;
+      const int lp_last = p_last >> page_shift;  // a page that certainly exists: stands in for pages a tile
+                                                 // reaches but the request does not hold (their keys are masked)
+      for (int i = 0; i < n_tiles; ++i) {
+        const int s = i % kKvStages, ph = (i / kKvStages) & 1;
+        if (!mbar_wait(b_ke + 8 * s, ph ^ 1)) {
+          set_status(status, CCB_ST_WAIT_TIMEOUT);
+          break;
+        }
+        const int lp0 = ((first_tile + i) * kTK) >> page_shift;
+        mbar_expect_tx(b_kf + 8 * s, TILE_BYTES);
+        mbar_expect_tx(b_vf + 8 * s, TILE_BYTES);
+        for (int pass = 0; pass < 2; ++pass) {  // all of K first: the first product waits for it alone
+          for (int pg = 0; pg < pages_per_tile; ++pg) {
+            int lp = lp0 + pg;
+            int page = (lp <= lp_last && lp < bt_stride) ? bt[lp] : -1;
+            if (page < 0 || page >= num_pages) page = bt[lp_last];
+            if (page < 0 || page >= num_pages) {
+              set_status(status, CCB_ST_BAD_PAGE);
+              page = 0;
+            }
+            const int grow = (page * nkv + kvh) * page_size;  // first row of the page in the [rows, HD] view
+            const uint32_t off = (uint32_t)(pg * page_size) * 128u;
+#pragma unroll
+            for (int hf = 0; hf < NH; ++hf) {
+              if (pass == 0)
+                tma_load_2d(s32(sK + s * TILE_BYTES + hf * HALF_BYTES) + off, &tmK, hf * 64, grow, b_kf + 8 * s);
+              else
+                tma_load_2d(s32(sV + s * TILE_BYTES + hf * HALF_BYTES) + off, &tmV, hf * 64, grow, b_vf + 8 * s);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // ---- MMA issuer ----
+      // S = Q K^T: M 128, N 128, both K-major.  O += P V: M 128, N HD, A K-major, B (V) MN-major (bit 16).
+      constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
+                                   ((uint32_t)(128 >> 4) << 24);
+      bool alive = mbar_wait(b_q, 0);
+      for (int i = 0; i < n_tiles && alive; ++i) {
+        const int s = i % kKvStages, ph = (i / kKvStages) & 1;
+        // S of tile i (its buffer is free: the softmax of tile i-1 has read it before it signalled p_ready)
+        alive = mbar_wait(b_kf + 8 * s, ph);
+        if (!alive) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t da = smem_desc(s32(sQ + (ks >> 2) * HALF_BYTES)) + 2 * (ks & 3);
+          const uint64_t db = smem_desc(s32(sK + s * TILE_BYTES + (ks >> 2) * HALF_BYTES)) + 2 * (ks & 3);
+          tc_mma(tmem_s, da, db, idesc_s, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(b_sf);
+        // O += P V once the softmax warps have written P (and rescaled O) and V has landed
+        alive = mbar_wait(b_pr, i & 1) && mbar_wait(b_vf + 8 * s, ph);
+        if (!alive) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kTK / 16; ++ks) {
+          const uint64_t da = smem_desc(s32(sP + (ks >> 2) * HALF_BYTES)) + 2 * (ks & 3);
+          // 16 keys further = 16 rows of 128 bytes; 64 head columns further = the next half; 8 keys = 1024 bytes
+          const uint64_t db = smem_desc_mn(s32(sV + s * TILE_BYTES) + ks * 2048, HALF_BYTES, 1024);
+          tc_mma(tmem_o, da, db, idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(b_ke + 8 * s);  // the stage may be refilled
+        tc_commit(b_pv);          // P and O may be touched again
+      }
+      if (!alive) set_status(status, CCB_ST_WAIT_TIMEOUT);
+    }
+  } else {  // ---- softmax, rescaling, epilogue: thread = query row = TMEM lane ----
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const int pr = p_first + row;                                   // this row's position
+    const int lo = window > 0 ? max(0, pr - window + 1) : 0;        // first key it may see
+    float m = -CUDART_INF_F, l = 0.f;
+    bool alive = true;
+    for (int i = 0; i < n_tiles; ++i) {
+      alive = mbar_wait(b_sf, i & 1);
+      if (!alive) break;
+      tc_fence_after();
+      const int jt = (first_tile + i) * kTK;
+      // pass 1: the row's maximum over the tile
+      float mx = -CUDART_INF_F;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kTK; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(tmem_s + lane_addr + c0, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int j = jt + c0 + e;
+          if (j <= pr && j >= lo) mx = fmaxf(mx, __uint_as_float(v[e]) * scale_log2);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float corr = m_new == -CUDART_INF_F ? 1.f : exp2f(m - m_new);
+      const float sub = m_new == -CUDART_INF_F ? 0.f : m_new;
+      m = m_new;
+      // the previous tile's P V must be complete before P is overwritten and O rescaled
+      if (i > 0) {
+        alive = mbar_wait(b_pv, (i - 1) & 1);
+        if (!alive) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t v[32];
+            tc_ld32(tmem_o + lane_addr + c0, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
+            tc_st32(tmem_o + lane_addr + c0, v);
+          }
+          tc_wait_st();
+        }
+      }
+      // pass 2: probabilities -> bfloat16 -> shared memory (K-major rows of 128 bytes, 16-byte chunks
+      // XOR-swizzled by the row, two halves of 64 keys), and the row sum
+      float ps = 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kTK; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(tmem_s + lane_addr + c0, v);
+        tc_wait_ld();
+        uint32_t packed[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const int j = jt + c0 + e;
+          const float a = (j <= pr && j >= lo) ? exp2f(__uint_as_float(v[e]) * scale_log2 - sub) : 0.f;
+          const float c = (j + 1 <= pr && j + 1 >= lo) ? exp2f(__uint_as_float(v[e + 1]) * scale_log2 - sub) : 0.f;
+          ps += a + c;
+          const __nv_bfloat162 hh = __floats2bfloat162_rn(a, c);
+          packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        uint8_t* prow = sP + (c0 >> 6) * HALF_BYTES + row * 128;
+        const int chunk0 = (c0 & 63) >> 3;  // first 16-byte chunk of these 32 keys inside the half
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int chunk = (chunk0 + cc) ^ (row & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) =
+              make_uint4(packed[4 * cc], packed[4 * cc + 1], packed[4 * cc + 2], packed[4 * cc + 3]);
+        }
+      }
+      l = l * corr + ps;
+      fence_async_smem();   // P (generic writes) before the tensor core's reads
+      tc_fence_before();    // S reads and O writes before the next products
+      mbar_arrive(b_pr);
+    }
+    if (alive) {
+      alive = mbar_wait(b_pv, (n_tiles - 1) & 1);
+      tc_fence_after();
+    }
+    if (!alive && lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
+    pdl_trigger();
+    if (alive) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = out + ((size_t)(row_begin + q_first + row) * nq + h) * HD;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(tmem_o + lane_addr + c0, v);
+        tc_wait_ld();
+        if (row < rows_here) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint32_t p4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[e + 2 * u]) * inv,
+                                                              __uint_as_float(v[e + 2 * u + 1]) * inv);
+              p4[u] = *reinterpret_cast<const uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(orow + c0 + e) = make_uint4(p4[0], p4[1], p4[2], p4[3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+template <int NH>
+int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q, const int* pos0,
+           const int* block_table, int bt_stride, int entry0, int n_entries, int max_new, int n_tokens, int nq,
+           int nkv, int page_size, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+  constexpr int HD = 64 * NH;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  CUtensorMap tmQ, tmK, tmV;
+  const unsigned long long cache_rows = (unsigned long long)num_pages * nkv * page_size;
+  if (!ccb_tensor_map_2d(q, n_tokens, (unsigned long long)nq * HD, (unsigned long long)nq * HD, 64, 128, &tmQ) ||
+      !ccb_tensor_map_2d(k_cache, cache_rows, HD, HD, 64, page_size, &tmK) ||
+      !ccb_tensor_map_2d(v_cache, cache_rows, HD, HD, 64, page_size, &tmV))
+    return CCB_REFUSE_ARG;
+  const size_t smem = (size_t)(1 + 2 * kKvStages) * NH * 128 * 128 + 2 * 128 * 128 + 16 * 8 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<NH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_new + kTQ - 1) / kTQ, nq, n_entries);
+  ccb_launch(attention_prefill_tc_kernel<NH>, grid, kTcThreads, smem, stream, tmQ, tmK, tmV, (__nv_bfloat16*)out, cu_q,
+             pos0, block_table, bt_stride, entry0, nq, nkv, page_size, page_shift, num_pages, window,
+             scale * 1.4426950408889634f, status);
+  return ccb_launch_status();
+}
+
+}  // namespace
+
+// As ccb_attention_prefill_mma; n_tokens = rows of q / out.  bfloat16, head size 64 or 128, page size a power
+// of two from 8 to 128; anything else is refused (CCB_REFUSE_SIZE) and belongs to the other kernels.
+CCB_API int ccb_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                     const int* cu_q, const int* pos0, const int* block_table, int bt_stride,
+                                     int entry0, int n_entries, int max_new, int n_tokens, int nq, int nkv, int hd,
+                                     int page_size, int num_pages, int window, float scale, int* status,
+                                     cudaStream_t stream) {
+  if (n_entries <= 0 || max_new <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || bt_stride <= 0 || n_entries > 65535 || nq > 65535 || page_size < 8 ||
+      page_size > 128 || (page_size & (page_size - 1)) != 0 ||
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+        reinterpret_cast<uintptr_t>(out)) & 15) != 0)
+    return CCB_REFUSE_SIZE;
+  if (hd == 128)
+    return launch<2>(q, k_cache, v_cache, out, cu_q, pos0, block_table, bt_stride, entry0, n_entries, max_new,
+                     n_tokens, nq, nkv, page_size, num_pages, window, scale, status, stream);
+  if (hd == 64)
+    return launch<1>(q, k_cache, v_cache, out, cu_q, pos0, block_table, bt_stride, entry0, n_entries, max_new,
+                     n_tokens, nq, nkv, page_size, num_pages, window, scale, status, stream);
+  return CCB_REFUSE_SIZE;
+}

@@ -36,6 +36,7 @@ GROUPS = {
         "attention_split.cu",
         "attention_decode_mma.cu",
         "attention_prefill_mma.cu",
+        "attention_prefill_tc.cu",
         "gemm_f32.cu",
         "gemm_cublas.cu",
         "gemm_skinny.cu",

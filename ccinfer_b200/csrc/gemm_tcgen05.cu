@@ -24,6 +24,9 @@
 #include <mutex>
 #include <tuple>
 
+#include "tc_common.cuh"
+#include "tma_host.h"
+
 using namespace ccb;
 
 namespace {
@@ -32,73 +35,7 @@ constexpr int BM = 128;           // tile rows (TMEM lanes)
 constexpr int BK = 64;            // k elements per stage: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr uint32_t kWaitLimit = 1u << 20;
 constexpr int kThreadsTc = 192;
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// bounded wait: false after kWaitLimit polls
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile of 128-byte rows in the 128-byte swizzle: rows 128 bytes
-// apart, groups of 8 rows 1024 bytes apart (stride byte offset), leading byte offset 1 (unused with a
-// swizzle), descriptor version 1, layout type 2 (SWIZZLE_128B).  The tile base is 1024-byte aligned;
-// stepping 16 k elements along the row is +32 bytes on the start address.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
 
 // instruction descriptor: float accumulate, bfloat16 x bfloat16, both K-major, M = 128, N = n
 __host__ __device__ constexpr uint32_t instr_desc(int n) {
@@ -337,13 +274,17 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-// tensor maps are cached by (pointer, rows, K, row stride, box rows): weights and the engine's scratch
-// buffers keep their addresses for the life of the process
-std::mutex g_mu;
-std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> g_maps;
+}  // namespace
 
-bool tensor_map(const void* ptr, int rows, int K, int ld, int box_rows, CUtensorMap* out) {
-  const auto key = std::make_tuple(ptr, rows, K, ld, box_rows);
+// tensor maps are cached by (pointer, rows, columns, row stride, box): weights and the engine's scratch
+// buffers keep their addresses for the life of the process
+static std::mutex g_mu;
+static std::map<std::tuple<const void*, unsigned long long, unsigned long long, unsigned long long, unsigned, unsigned>,
+                CUtensorMap> g_maps;
+
+bool ccb_tensor_map_2d(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
+                       unsigned box_cols, unsigned box_rows, CUtensorMap* out) {
+  const auto key = std::make_tuple(ptr, rows, cols, ld, box_cols, box_rows);
   std::lock_guard<std::mutex> lock(g_mu);
   auto it = g_maps.find(key);
   if (it != g_maps.end()) {
@@ -353,9 +294,9 @@ bool tensor_map(const void* ptr, int rows, int K, int ld, int box_rows, CUtensor
   auto fn = encode_fn();
   if (fn == nullptr) return false;
   CUtensorMap tm;
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -365,6 +306,12 @@ bool tensor_map(const void* ptr, int rows, int K, int ld, int box_rows, CUtensor
   g_maps[key] = tm;
   *out = tm;
   return true;
+}
+
+namespace {
+
+bool tensor_map(const void* ptr, int rows, int K, int ld, int box_rows, CUtensorMap* out) {
+  return ccb_tensor_map_2d(ptr, rows, K, ld, BK, box_rows, out);
 }
 
 template <int BN, int STAGES, bool SWAP, typename TOut>

@@ -53,6 +53,9 @@ _SIGNATURES = {
     "ccb_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                   c_void_p],
+    "ccb_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                 c_void_p],
     "ccb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_cublas_create": [ctypes.POINTER(c_void_p)],
     "ccb_cublas_destroy": [c_void_p],
@@ -312,6 +315,26 @@ def attention_prefill_mma(q, k_cache, v_cache, out, cu_q, pos0, block_table, ent
                                            _p(block_table), block_table.stride(0), entry0, n_entries, max_new,
                                            nq, nkv, hd, page_size, num_pages, int(window), float(scale),
                                            _p(status), _stream()), "attention_prefill_mma")
+
+
+def attention_prefill_tc_fits(hd: int, page_size: int) -> bool:
+    return hd in (64, 128) and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0
+
+
+def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, pos0, block_table, entry0: int, n_entries: int,
+                         max_new: int, window: int, scale: float, status=None) -> None:
+    """As attention_prefill_mma, with both products on tcgen05 tensor cores and the accumulators in tensor
+    memory (128-token query tiles, TMA loads page by page).  Page size a power of two from 8 to 128."""
+    _cuda(q, k_cache, v_cache, out, cu_q, pos0, block_table, status)
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    assert hd2 == hd and out.shape == q.shape
+    assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16
+    assert entry0 >= 0 and entry0 + n_entries <= block_table.shape[0] and cu_q.numel() >= entry0 + n_entries + 1
+    _check(lib().ccb_attention_prefill_tc(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(cu_q), _p(pos0),
+                                          _p(block_table), block_table.stride(0), entry0, n_entries, max_new, T,
+                                          nq, nkv, hd, page_size, num_pages, int(window), float(scale),
+                                          _p(status), _stream()), "attention_prefill_tc")
 
 
 def gemm_f32(c, a, w) -> None:

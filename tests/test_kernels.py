@@ -387,6 +387,77 @@ def test_attention_prefill_mma(case):
         assert torch.equal(part[new[0]:], out[new[0]:]) and float(part[:new[0]].abs().max()) == 0.0
 
 
+TC_PREFILL_CASES = [
+    # ctx, new, nq, nkv, hd, page, window
+    ([0], [1], 2, 1, 64, 16, None),
+    ([0], [128], 4, 2, 128, 16, None),
+    ([0, 5, 31], [70, 2, 130], 6, 3, 64, 8, None),
+    ([100, 0, 63], [1, 300, 65], 8, 2, 128, 16, None),
+    ([0, 40, 129], [150, 3, 64], 4, 4, 64, 32, 24),
+    ([17, 250], [300, 1], 5, 1, 128, 128, 100),
+    ([1000], [200], 8, 2, 128, 64, None),
+]
+
+
+@pytest.mark.parametrize("case", TC_PREFILL_CASES)
+def test_attention_prefill_tc(case):
+    ctx, new, nq, nkv, hd, P, window = case
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", ctx, new, nq, nkv, hd, P, seed=hd + len(ctx),
+                                               window=window)
+    cu = torch.tensor([0] + list(np.cumsum(new)), dtype=torch.int32, device="cuda")
+    pos0 = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q)
+    _k().attention_prefill_tc(q, kc, vc, out, cu, pos0, bt, 0, len(ctx), max(new), window or 0, 1 / math.sqrt(hd),
+                              status)
+    assert int(status.item()) == 0
+    assert _rel(out, ref) <= 1.5e-2
+    if len(ctx) > 1:
+        part = torch.zeros_like(q)
+        _k().attention_prefill_tc(q, kc, vc, part, cu, pos0, bt, 1, len(ctx) - 1, max(new[1:]), window or 0,
+                                  1 / math.sqrt(hd), status)
+        assert torch.equal(part[new[0]:], out[new[0]:]) and float(part[:new[0]].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("far_key", [0, 63, 64, 127, 128, 400, 449])
+def test_attention_prefill_tc_reads_far_key(far_key):
+    nq, nkv, hd, P = 4, 2, 128, 16
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [450], [150], nq, nkv, hd, P, seed=far_key,
+                                               peak=(0, far_key))
+    cu = torch.tensor([0, 150], dtype=torch.int32, device="cuda")
+    pos0 = torch.tensor([450], dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _k().attention_prefill_tc(q, kc, vc, out, cu, pos0, bt, 0, 1, 150, 0, 1 / math.sqrt(hd), status)
+    assert int(status.item()) == 0
+    assert _rel(out, ref) <= 1.5e-2 and _rel(out[-1:], ref[-1:]) <= 1.5e-2
+
+
+@pytest.mark.parametrize("edge", [-1, 0, 1])
+def test_attention_prefill_tc_window_edge(edge):
+    nq, nkv, hd, P, W = 2, 1, 64, 8, 40
+    ctx, new = 130, 70
+    L = ctx + new
+    key = (L - 1) - W + 1 + edge
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [ctx], [new], nq, nkv, hd, P, seed=7, window=W,
+                                               peak=(0, key))
+    cu = torch.tensor([0, new], dtype=torch.int32, device="cuda")
+    pos0 = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q)
+    _k().attention_prefill_tc(q, kc, vc, out, cu, pos0, bt, 0, 1, new, W, 1 / math.sqrt(hd))
+    assert _rel(out, ref) <= 1.5e-2 and _rel(out[-1:], ref[-1:]) <= 1.5e-2
+
+
+def test_attention_prefill_tc_refuses_small_pages():
+    from ccinfer_b200.errors import Unsupported
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [0], [20], 2, 1, 64, 4, seed=1)
+    cu = torch.tensor([0, 20], dtype=torch.int32, device="cuda")
+    pos0 = torch.tensor([0], dtype=torch.int32, device="cuda")
+    assert not _k().attention_prefill_tc_fits(64, 4) and _k().attention_prefill_tc_fits(128, 16)
+    with pytest.raises(Unsupported):
+        _k().attention_prefill_tc(q, kc, vc, torch.zeros_like(q), cu, pos0, bt, 0, 1, 20, 0, 0.125)
+
+
 @pytest.mark.parametrize("far_key", [0, 63, 64, 127, 128, 400, 449])
 def test_attention_prefill_mma_reads_far_key(far_key):
     nq, nkv, hd, P = 4, 2, 128, 16
