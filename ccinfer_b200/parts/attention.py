@@ -75,8 +75,8 @@ class GroupedQueryAttention(Mixer):
 
         A step lists its single-token requests first.  On the tensor-core path (bfloat16, head size 64 or
         128) those rows go to the decode kernel (key range split over blocks) and the portions of prompts to
-        the prefill kernel (64 query tokens a block); otherwise every row is a single query of the split
-        kernel, which takes all sizes and both types."""
+        a prefill kernel (tcgen05 with 128 query tokens a block, or mma.sync with 64); otherwise every row is
+        a single query of the split kernel, which takes all sizes and both types."""
         rt, g = self.rt, cache.group
         mma = rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
         n_rows = step.n_single if mma else T
@@ -89,9 +89,12 @@ class GroupedQueryAttention(Mixer):
             fn(q, cache.k, cache.v, o, part_acc, part_ml, step.positions, step.entry_of_token, g.block_table,
                step.n_entries, 0, n_rows, self.window or 0, self.scale, splits, status=rt.status)
         if mma and step.n_entries > step.n_single:
-            kernels.attention_prefill_mma(q, cache.k, cache.v, o, step.cu_q, step.pos0, g.block_table,
-                                          step.n_single, step.n_entries - step.n_single, step.max_q_len,
-                                          self.window or 0, self.scale, status=rt.status)
+            # long portions: 128-token tiles on tcgen05 with the accumulators in tensor memory; short ones
+            # (and page sizes a TMA box cannot take): 64-token tiles on mma.sync
+            tc = step.max_q_len > 64 and kernels.attention_prefill_tc_fits(self.hd, g.page_size)
+            fn = kernels.attention_prefill_tc if tc else kernels.attention_prefill_mma
+            fn(q, cache.k, cache.v, o, step.cu_q, step.pos0, g.block_table, step.n_single,
+               step.n_entries - step.n_single, step.max_q_len, self.window or 0, self.scale, status=rt.status)
 
     # -- a step ----------------------------------------------------------------
     def forward(self, x, step, cache, state):
