@@ -5,11 +5,12 @@
 //   but with both products on tcgen05.mma and both accumulators in tensor memory:
 //
 //   block = (128 query tokens of one request, one q head); per tile of 128 key positions
-//     S = Q K^T          tcgen05.mma  M=128 N=128 K=head   -> TMEM columns [0, 128)
+//     S = Q K^T          tcgen05.mma  M=128 N=128 K=head   -> TMEM, two buffers: the product of tile i+1 runs
+//                        while the softmax warps work on tile i
 //     P = softmax part   four warps, one query row per thread: tcgen05.ld S, mask, running max and sum in
 //                        float (base-2 exponentials), P as bfloat16 into shared memory in the 128-byte
 //                        swizzle; the running output in TMEM is rescaled when the maximum moved
-//     O += P V           tcgen05.mma  M=128 N=head K=128  (V is the MN-major operand) -> TMEM columns [128, ..)
+//     O += P V           tcgen05.mma  M=128 N=head K=128  (V is the MN-major operand) -> TMEM
 //   Q, K and V tiles arrive by TMA: Q as two boxes of 128 rows x 64 columns, K and V page by page (a box is
 //   one page of one kv head: page_size rows x 64 columns), two stages.  Warp 0 issues the copies, warp 1 the
 //   products, warps 2..5 do the softmax, the rescaling and the final division and store.
@@ -30,6 +31,13 @@ constexpr int kTK = 128;     // keys per tile
 constexpr int kTcThreads = 192;
 constexpr int kKvStages = 2;
 
+// 2^x by the special-function unit alone (one instruction; 2^-inf = 0)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // HD = 64 * NH
 template <int NH>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -43,7 +51,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   constexpr int HALF_BYTES = 128 * 128;            // 128 rows x 128 bytes: one 64-column half of a tile
   constexpr int TILE_BYTES = NH * HALF_BYTES;      // Q, K or V tile
   constexpr int P_BYTES = 2 * HALF_BYTES;          // 128 rows x 128 keys
-  constexpr int TMEM_COLS = 256;                   // S: 128 columns, O: HD columns
+  constexpr int TMEM_COLS = 512;                   // S: two buffers of 128 columns, O: HD columns
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -51,10 +59,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   uint8_t* sV = sK + kKvStages * TILE_BYTES;       // [stages]
   uint8_t* sP = sV + kKvStages * TILE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_full, p_ready, pv_done
+  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_ready, pv_done
   const uint32_t b_q = s32(bars), b_kf = s32(bars + 1), b_vf = s32(bars + 3), b_ke = s32(bars + 5),
-                 b_sf = s32(bars + 7), b_pr = s32(bars + 8), b_pv = s32(bars + 9);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+                 b_sf = s32(bars + 7), b_pr = s32(bars + 9), b_pv = s32(bars + 10);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
 
   const int b = entry0 + blockIdx.z;
   const int h = blockIdx.y;
@@ -81,6 +89,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
       mbar_init(b_ke + 8 * s, 1);
     }
     mbar_init(b_sf, 1);
+    mbar_init(b_sf + 8, 1);
     mbar_init(b_pr, 128);
     mbar_init(b_pv, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -94,48 +103,53 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
+  const uint32_t tmem_s = *tmem_slot, tmem_o = tmem_s + 256;  // S buffers at columns 0 and 128
 
   if (warp == 0) {
-    if (lane == 0) {  // ---- TMA producer ----
-      pdl_wait();
+    // ---- TMA producer: the whole warp, one lane per page of a tile, so that the page look-ups (dependent
+    // global loads) of a tile run side by side instead of one after the other ----
+    pdl_wait();
+    if (lane == 0) {
       mbar_expect_tx(b_q, TILE_BYTES);
 #pragma unroll
       for (int hf = 0; hf < NH; ++hf)
         tma_load_2d(s32(sQ + hf * HALF_BYTES), &tmQ, h * HD + hf * 64, row_begin + q_first, b_q);
-      const int pages_per_tile = kTK >> page_shift;
-      const int lp_last = p_last >> page_shift;  // a page that certainly exists: stands in for pages a tile
-                                                 // reaches but the request does not hold (their keys are masked)
-      for (int i = 0; i < n_tiles; ++i) {
-        const int s = i % kKvStages, ph = (i / kKvStages) & 1;
-        if (!mbar_wait(b_ke + 8 * s, ph ^ 1)) {
+    }
+    const int pages_per_tile = kTK >> page_shift;
+    const int lp_last = p_last >> page_shift;  // a page that certainly exists: stands in for pages a tile
+                                               // reaches but the request does not hold (their keys are masked)
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % kKvStages, ph = (i / kKvStages) & 1;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(b_ke + 8 * s, ph ^ 1) ? 1 : 0;
+        if (ok) {
+          mbar_expect_tx(b_kf + 8 * s, TILE_BYTES);
+          mbar_expect_tx(b_vf + 8 * s, TILE_BYTES);
+        } else {
           set_status(status, CCB_ST_WAIT_TIMEOUT);
-          break;
-        }
-        const int lp0 = ((first_tile + i) * kTK) >> page_shift;
-        mbar_expect_tx(b_kf + 8 * s, TILE_BYTES);
-        mbar_expect_tx(b_vf + 8 * s, TILE_BYTES);
-        for (int pass = 0; pass < 2; ++pass) {  // all of K first: the first product waits for it alone
-          for (int pg = 0; pg < pages_per_tile; ++pg) {
-            int lp = lp0 + pg;
-            int page = (lp <= lp_last && lp < bt_stride) ? bt[lp] : -1;
-            if (page < 0 || page >= num_pages) page = bt[lp_last];
-            if (page < 0 || page >= num_pages) {
-              set_status(status, CCB_ST_BAD_PAGE);
-              page = 0;
-            }
-            const int grow = (page * nkv + kvh) * page_size;  // first row of the page in the [rows, HD] view
-            const uint32_t off = (uint32_t)(pg * page_size) * 128u;
-#pragma unroll
-            for (int hf = 0; hf < NH; ++hf) {
-              if (pass == 0)
-                tma_load_2d(s32(sK + s * TILE_BYTES + hf * HALF_BYTES) + off, &tmK, hf * 64, grow, b_kf + 8 * s);
-              else
-                tma_load_2d(s32(sV + s * TILE_BYTES + hf * HALF_BYTES) + off, &tmV, hf * 64, grow, b_vf + 8 * s);
-            }
-          }
         }
       }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        const int lp = (((first_tile + i) * kTK) >> page_shift) + lane;
+        int page = (lp <= lp_last && lp < bt_stride) ? bt[lp] : -1;
+        if (page < 0 || page >= num_pages) page = bt[lp_last];
+        if (page < 0 || page >= num_pages) {
+          set_status(status, CCB_ST_BAD_PAGE);
+          page = 0;
+        }
+        const int grow = (page * nkv + kvh) * page_size;  // first row of the page in the [rows, HD] view
+        const uint32_t off = (uint32_t)(lane * page_size) * 128u;
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf)
+          tma_load_2d(s32(sK + s * TILE_BYTES + hf * HALF_BYTES) + off, &tmK, hf * 64, grow, b_kf + 8 * s);
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf)
+          tma_load_2d(s32(sV + s * TILE_BYTES + hf * HALF_BYTES) + off, &tmV, hf * 64, grow, b_vf + 8 * s);
+      }
+      __syncwarp();
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer ----
@@ -143,20 +157,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
       constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
                                    ((uint32_t)(128 >> 4) << 24);
-      bool alive = mbar_wait(b_q, 0);
-      for (int i = 0; i < n_tiles && alive; ++i) {
-        const int s = i % kKvStages, ph = (i / kKvStages) & 1;
-        // S of tile i (its buffer is free: the softmax of tile i-1 has read it before it signalled p_ready)
-        alive = mbar_wait(b_kf + 8 * s, ph);
-        if (!alive) break;
+      // S of tile t goes to buffer t & 1: the product of the NEXT tile is issued before this tile's P V, so it
+      // runs while the softmax warps work on this tile, and their next S is ready when they come back.
+      auto issue_qk = [&](int t) -> bool {
+        const int s = t % kKvStages, ph = (t / kKvStages) & 1;
+        if (!mbar_wait(b_kf + 8 * s, ph)) return false;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint64_t da = smem_desc(s32(sQ + (ks >> 2) * HALF_BYTES)) + 2 * (ks & 3);
           const uint64_t db = smem_desc(s32(sK + s * TILE_BYTES + (ks >> 2) * HALF_BYTES)) + 2 * (ks & 3);
-          tc_mma(tmem_s, da, db, idesc_s, ks > 0 ? 1u : 0u);
+          tc_mma(tmem_s + (t & 1) * 128, da, db, idesc_s, ks > 0 ? 1u : 0u);
         }
-        tc_commit(b_sf);
+        tc_commit(b_sf + 8 * (t & 1));
+        return true;
+      };
+      bool alive = mbar_wait(b_q, 0);
+      if (alive) alive = issue_qk(0);
+      for (int i = 0; i < n_tiles && alive; ++i) {
+        const int s = i % kKvStages, ph = (i / kKvStages) & 1;
+        // buffer (i + 1) & 1 is free: the softmax of tile i - 1 read it before it signalled p_ready(i - 1)
+        if (i + 1 < n_tiles) {
+          alive = issue_qk(i + 1);
+          if (!alive) break;
+        }
         // O += P V once the softmax warps have written P (and rescaled O) and V has landed
         alive = mbar_wait(b_pr, i & 1) && mbar_wait(b_vf + 8 * s, ph);
         if (!alive) break;
@@ -182,25 +206,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     float m = -CUDART_INF_F, l = 0.f;
     bool alive = true;
     for (int i = 0; i < n_tiles; ++i) {
-      alive = mbar_wait(b_sf, i & 1);
+      alive = mbar_wait(b_sf + 8 * (i & 1), (i >> 1) & 1);
       if (!alive) break;
       tc_fence_after();
       const int jt = (first_tile + i) * kTK;
-      // pass 1: the row's maximum over the tile
-      float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kTK; c0 += 32) {
-        uint32_t v[32];
-        tc_ld32(tmem_s + lane_addr + c0, v);
-        tc_wait_ld();
+      const uint32_t tmem_si = tmem_s + (i & 1) * 128;
+      // Most tiles lie wholly in every row's past (and inside its window): they need no mask.
+      const bool need_mask = (jt + kTK - 1 > p_first) || (window > 0 && jt < p_first + kTQ - window);
+      // the row's 128 scores, read once
+      uint32_t v[kTK];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int j = jt + c0 + e;
-          if (j <= pr && j >= lo) mx = fmaxf(mx, __uint_as_float(v[e]) * scale_log2);
+      for (int c0 = 0; c0 < kTK; c0 += 32) tc_ld32(tmem_si + lane_addr + c0, v + c0);
+      tc_wait_ld();
+      if (need_mask) {
+#pragma unroll
+        for (int e = 0; e < kTK; ++e) {
+          const int j = jt + e;
+          if (!(j <= pr && j >= lo)) v[e] = 0xff800000u;  // -inf: 2^(-inf) = 0 below
         }
       }
-      const float m_new = fmaxf(m, mx);
-      const float corr = m_new == -CUDART_INF_F ? 1.f : exp2f(m - m_new);
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};  // four independent chains
+#pragma unroll
+      for (int e = 0; e < kTK; e += 4)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(v[e + u]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      // The running maximum only has to keep the exponentials in range, it need not be the true maximum:
+      // it moves when the new one is more than 2^8 larger (or at the first visible key), which spares most
+      // rescalings of O; the final division by l makes the result the same.
+      const float m_new = (m == -CUDART_INF_F || mx > m + 8.f) ? fmaxf(m, mx) : m;
+      const float corr = m_new == -CUDART_INF_F ? 1.f : ex2(m - m_new);
       const float sub = m_new == -CUDART_INF_F ? 0.f : m_new;
       m = m_new;
       // the previous tile's P V must be complete before P is overwritten and O rescaled
@@ -211,31 +246,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
           for (int c0 = 0; c0 < HD; c0 += 32) {
-            uint32_t v[32];
-            tc_ld32(tmem_o + lane_addr + c0, v);
+            uint32_t o[32];
+            tc_ld32(tmem_o + lane_addr + c0, o);
             tc_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
-            tc_st32(tmem_o + lane_addr + c0, v);
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+            tc_st32(tmem_o + lane_addr + c0, o);
           }
           tc_wait_st();
         }
       }
-      // pass 2: probabilities -> bfloat16 -> shared memory (K-major rows of 128 bytes, 16-byte chunks
-      // XOR-swizzled by the row, two halves of 64 keys), and the row sum
-      float ps = 0.f;
-#pragma unroll 1
+      // probabilities -> bfloat16 -> shared memory (K-major rows of 128 bytes, 16-byte chunks XOR-swizzled by
+      // the row, two halves of 64 keys), and the row sum
+      float ps2[2] = {0.f, 0.f};
+      const float nsub = -sub;
+#pragma unroll
       for (int c0 = 0; c0 < kTK; c0 += 32) {
-        uint32_t v[32];
-        tc_ld32(tmem_s + lane_addr + c0, v);
-        tc_wait_ld();
         uint32_t packed[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          const int j = jt + c0 + e;
-          const float a = (j <= pr && j >= lo) ? exp2f(__uint_as_float(v[e]) * scale_log2 - sub) : 0.f;
-          const float c = (j + 1 <= pr && j + 1 >= lo) ? exp2f(__uint_as_float(v[e + 1]) * scale_log2 - sub) : 0.f;
-          ps += a + c;
+          const float a = ex2(fmaf(__uint_as_float(v[c0 + e]), scale_log2, nsub));
+          const float c = ex2(fmaf(__uint_as_float(v[c0 + e + 1]), scale_log2, nsub));
+          ps2[0] += a;
+          ps2[1] += c;
           const __nv_bfloat162 hh = __floats2bfloat162_rn(a, c);
           packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
         }
@@ -248,7 +281,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
               make_uint4(packed[4 * cc], packed[4 * cc + 1], packed[4 * cc + 2], packed[4 * cc + 3]);
         }
       }
-      l = l * corr + ps;
+      l = l * corr + (ps2[0] + ps2[1]);
       fence_async_smem();   // P (generic writes) before the tensor core's reads
       tc_fence_before();    // S reads and O writes before the next products
       mbar_arrive(b_pr);
