@@ -1,0 +1,354 @@
+// Decode attention on tensor cores with TMA page loads (bfloat16, head size 64 or 128, page size a power of
+// two from 8 to 64): the same computation as attention_decode_mma_kernel (single query tokens over paged keys,
+// the group's q heads as the 16 rows of an m16n8k16 tile, four warps each taking 16 of a tile's 64 keys, online
+// softmax, split key range merged afterwards; 7QiC/ccInfer: src/kernel/attention/decode_attn.cu:417-473).
+//
+// What differs is how keys and values reach shared memory.  There a tile costs 2,048 16-byte cp.async copies
+// issued by all threads, and the load/store path is what holds the kernel (mio / lg throttle stalls).  Here a
+// fifth warp is the producer: one lane per page issues cp.async.bulk.tensor boxes of one page of one kv head
+// (page_size rows x 64 columns, 128-byte swizzle) - 16 copies a tile at page size 16 - signalled by one
+// mbarrier per stage; pages a tile reaches but the request does not hold are replaced by its last page (their
+// keys are masked).  Every mbarrier wait is bounded.
+#include "common.cuh"
+#include "mma_common.cuh"
+#include "tc_common.cuh"
+#include "tma_host.h"
+#include <math_constants.h>
+
+using namespace ccb;
+
+namespace {
+
+constexpr int kTileKeys = 64;
+constexpr int kStages = 3;
+constexpr int kComputeThreads = 128;
+constexpr int kThreads = 160;  // four compute warps and the producer warp
+constexpr int kHalfBytes = kTileKeys * 128;  // 64 rows x 64 columns of bfloat16
+
+// byte address of 16-byte chunk `chunk` (of the whole head) of row `row`: halves of 64 columns, rows 128 bytes
+// apart, chunks XOR-swizzled by the row as the TMA unit wrote them
+__device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int row, int chunk) {
+  return tile + (chunk >> 3) * kHalfBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                            const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                            float* __restrict__ part_acc, float* __restrict__ part_ml,
+                            const int* __restrict__ positions, const int* __restrict__ entry_of_token,
+                            const int* __restrict__ block_table, int bt_stride, int n_entries, int row0, int nq,
+                            int nkv, int page_size, int page_shift, int num_pages, int window, float scale,
+                            int num_splits, int* status) {
+  ccb::pdl_begin();
+  constexpr int NH = HD / 64;
+  constexpr int KS = HD / 16;
+  constexpr int TILE_BYTES = NH * kHalfBytes;        // one K or V tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* k_sm = smem;                               // [stages][tile]
+  uint8_t* v_sm = k_sm + kStages * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + kStages * TILE_BYTES);
+  const uint32_t bar0 = s32(bars);
+
+  const int G = nq / nkv;
+  const int gchunks = (G + 15) / 16;
+  const int r = blockIdx.x, t = row0 + r;
+  const int kvh = blockIdx.y / gchunks, gc = blockIdx.y - kvh * gchunks;
+  const int split = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int h0 = kvh * G + gc * 16;
+  const int n_heads = min(16, G - gc * 16);
+
+  const int b = entry_of_token[t];
+  const int p = positions[t];
+  const bool padded = b < 0 || b >= n_entries || p < 0;
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  float o[2 * KS][4];
+#pragma unroll
+  for (int i = 0; i < 2 * KS; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+  if (!padded) {
+    // q as A fragments: rows = heads of the group (zero beyond n_heads); the producer warp has none
+    uint32_t qa[KS][4];
+    if (warp < 4) {
+      const __nv_bfloat16* q0 = q + ((size_t)t * nq + h0 + gid) * HD;
+      const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
+      const bool v0 = gid < n_heads, v1 = gid + 8 < n_heads;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const int c = ks * 16 + 2 * tig;
+        qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+        qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+        qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+        qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+      }
+    }
+    const int* bt = block_table + (size_t)b * bt_stride;
+    const int j0 = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int first_tile = j0 / kTileKeys, last_tile = p / kTileKeys;
+    const int n_tiles = last_tile - first_tile + 1;
+    const int per_split = (n_tiles + num_splits - 1) / num_splits;
+    const int my_first = first_tile + split * per_split;
+    const int my_tiles = min(my_first + per_split, last_tile + 1) - my_first;
+    const int pages_per_tile = kTileKeys >> page_shift;
+    const int lp_last = p >> page_shift;
+
+    // producer warp: lane pg copies page pg of the tile (NH boxes of K, NH of V); lane 0 arms the barrier
+    auto issue = [&](int tile, int stage) {
+      if (lane == 0) mbar_expect_tx(bar0 + 8 * stage, 2 * TILE_BYTES);
+      __syncwarp();
+      if (lane < pages_per_tile) {
+        const int lp = ((tile * kTileKeys) >> page_shift) + lane;
+        int page = (lp <= lp_last && lp < bt_stride) ? bt[lp] : -1;
+        if (page < 0 || page >= num_pages) page = bt[lp_last];
+        if (page < 0 || page >= num_pages) {
+          set_status(status, CCB_ST_BAD_PAGE);
+          page = 0;
+        }
+        const int grow = (page * nkv + kvh) * page_size;
+        const uint32_t off = (uint32_t)(lane * page_size) * 128u;
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) {
+          tma_load_2d(s32(k_sm + stage * TILE_BYTES + hf * kHalfBytes) + off, &tmK, hf * 64, grow, bar0 + 8 * stage);
+          tma_load_2d(s32(v_sm + stage * TILE_BYTES + hf * kHalfBytes) + off, &tmV, hf * 64, grow, bar0 + 8 * stage);
+        }
+      }
+    };
+
+    if (warp == 4) {
+#pragma unroll
+      for (int s = 0; s < kStages - 1; ++s)
+        if (s < my_tiles) issue(my_first + s, s);
+    }
+    for (int it = 0; it < my_tiles; ++it) {
+      const int st = it % kStages;
+      bool alive = mbar_wait(bar0 + 8 * st, (it / kStages) & 1);
+      // the tile has landed for everybody, and everybody has left the stage that is refilled below
+      alive = __syncthreads_and(alive);
+      if (!alive) {
+        if (tid == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
+        break;
+      }
+      if (warp == 4) {
+        if (it + kStages - 1 < my_tiles) issue(my_first + it + kStages - 1, (it + kStages - 1) % kStages);
+        continue;
+      }
+      const uint32_t ks_ = s32(k_sm + st * TILE_BYTES);
+      const uint32_t vs_ = s32(v_sm + st * TILE_BYTES);
+
+      // S[16 heads, 16 keys of this warp] = Q K^T
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      {
+        const int krow = warp * 16 + (lane & 7) + 8 * (lane >> 4);
+        const int kchunk = (lane >> 3) & 1;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          uint32_t b00, b01, b10, b11;
+          ldmatrix_x4(b00, b01, b10, b11, tile_addr(ks_, krow, 2 * ks + kchunk));
+          mma_bf16_16816(s[0], qa[ks], b00, b01);
+          mma_bf16_16816(s[1], qa[ks], b10, b11);
+        }
+      }
+      // mask, online softmax (rows gid and gid + 8)
+      const int jbase = (my_first + it) * kTileKeys + warp * 16 + 2 * tig;
+      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = jbase + nb * 8 + e;
+          const bool vis = j >= j0 && j <= p;
+          s[nb][e] = vis ? s[nb][e] * scale : -CUDART_INF_F;
+          s[nb][2 + e] = vis ? s[nb][2 + e] * scale : -CUDART_INF_F;
+          mx0 = fmaxf(mx0, s[nb][e]);
+          mx1 = fmaxf(mx1, s[nb][2 + e]);
+        }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      // a row that has seen no key yet keeps max -inf: its probabilities are 0 and nothing is rescaled
+      const float c0 = mn0 == -CUDART_INF_F ? 1.f : __expf(m0 - mn0);
+      const float c1 = mn1 == -CUDART_INF_F ? 1.f : __expf(m1 - mn1);
+      const float sub0 = mn0 == -CUDART_INF_F ? 0.f : mn0, sub1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+      m0 = mn0;
+      m1 = mn1;
+      float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          s[nb][e] = __expf(s[nb][e] - sub0);          // exp(-inf) = 0 for masked keys
+          s[nb][2 + e] = __expf(s[nb][2 + e] - sub1);
+          ps0 += s[nb][e];
+          ps1 += s[nb][2 + e];
+        }
+      l0 = l0 * c0 + ps0;   // per-lane partial sums; the four lanes of a row are added at the end
+      l1 = l1 * c1 + ps1;
+#pragma unroll
+      for (int i = 0; i < 2 * KS; ++i) {
+        o[i][0] *= c0; o[i][1] *= c0;
+        o[i][2] *= c1; o[i][3] *= c1;
+      }
+      // O += P V
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[0][0], s[0][1]);
+      pa[1] = pack_bf16(s[0][2], s[0][3]);
+      pa[2] = pack_bf16(s[1][0], s[1][1]);
+      pa[3] = pack_bf16(s[1][2], s[1][3]);
+      {
+        const int vrow = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int vchunk = lane >> 4;
+#pragma unroll
+        for (int nn = 0; nn < KS; ++nn) {
+          uint32_t b00, b01, b10, b11;
+          ldmatrix_x4_trans(b00, b01, b10, b11, tile_addr(vs_, vrow, 2 * nn + vchunk));
+          mma_bf16_16816(o[2 * nn], pa, b00, b01);
+          mma_bf16_16816(o[2 * nn + 1], pa, b10, b11);
+        }
+      }
+    }
+    pdl_trigger();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  }
+  __syncthreads();  // every copy has landed and every warp is done with the tiles: reuse the memory
+
+  float* o_s = reinterpret_cast<float*>(smem);  // [4 warps][16 rows][HD]
+  float* m_s = o_s + 4 * 16 * HD;                   // [4][16]
+  float* l_s = m_s + 64;
+  if (warp < 4) {
+#pragma unroll
+  for (int i = 0; i < 2 * KS; ++i) {
+    const int d = i * 8 + 2 * tig;
+    float* dst0 = o_s + ((size_t)(warp * 16 + gid)) * HD + d;
+    float* dst1 = o_s + ((size_t)(warp * 16 + gid + 8)) * HD + d;
+    dst0[0] = o[i][0]; dst0[1] = o[i][1];
+    dst1[0] = o[i][2]; dst1[1] = o[i][3];
+  }
+  if (tig == 0) {
+    m_s[warp * 16 + gid] = m0;
+    m_s[warp * 16 + gid + 8] = m1;
+    l_s[warp * 16 + gid] = l0;
+    l_s[warp * 16 + gid + 8] = l1;
+  }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < n_heads * HD; idx += kThreads) {
+    const int row = idx / HD, d = idx - row * HD;
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, m_s[w * 16 + row]);
+    float a = 0.f, ll = 0.f;
+    if (mm != -CUDART_INF_F) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = __expf(m_s[w * 16 + row] - mm);
+        a += o_s[(size_t)(w * 16 + row) * HD + d] * f;
+        ll += l_s[w * 16 + row] * f;
+      }
+    }
+    const int h = h0 + row;
+    if (num_splits == 1) {
+      out[((size_t)t * nq + h) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+    } else {
+      const size_t slot = ((size_t)r * nq + h) * num_splits + split;
+      part_acc[slot * HD + d] = a;
+      if (d == 0) {
+        part_ml[slot * 2] = mm;
+        part_ml[slot * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+__global__ void attention_merge_bf16_kernel2(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_acc,
+                                            const float* __restrict__ part_ml, int row0, int nq, int hd,
+                                            int num_splits) {
+  ccb::pdl_begin();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const size_t base = ((size_t)r * nq + h) * num_splits;
+  float mm = -CUDART_INF_F;
+  for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+  __nv_bfloat16* o = out + ((size_t)(row0 + r) * nq + h) * hd;
+  if (mm == -CUDART_INF_F) {
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  float ll = 0.f;
+  for (int s = 0; s < num_splits; ++s) ll += part_ml[(base + s) * 2 + 1] * __expf(part_ml[(base + s) * 2] - mm);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < num_splits; ++s) a += part_acc[(base + s) * hd + d] * __expf(part_ml[(base + s) * 2] - mm);
+    o[d] = __float2bfloat16_rn(a / ll);
+  }
+}
+
+template <int HD>
+int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_acc, float* part_ml,
+           const int* positions, const int* entry_of_token, const int* block_table, int bt_stride, int n_entries,
+           int row0, int n_rows, int nq, int nkv, int page_size, int num_pages, int window, float scale,
+           int num_splits, int* status, cudaStream_t stream) {
+  const int G = nq / nkv, gchunks = (G + 15) / 16;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  CUtensorMap tmK, tmV;
+  const unsigned long long cache_rows = (unsigned long long)num_pages * nkv * page_size;
+  if (!ccb_tensor_map_2d(k_cache, cache_rows, HD, HD, 64, page_size, &tmK) ||
+      !ccb_tensor_map_2d(v_cache, cache_rows, HD, HD, 64, page_size, &tmV))
+    return CCB_REFUSE_ARG;
+  const size_t smem = (size_t)2 * kStages * (HD / 64) * kHalfBytes + kStages * 8 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_rows, nkv * gchunks, num_splits);
+  ccb_launch(attention_decode_tma_kernel<HD>, grid, kThreads, smem, stream, tmK, tmV, (const __nv_bfloat16*)q,
+             (__nv_bfloat16*)out, part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries,
+             row0, nq, nkv, page_size, page_shift, num_pages, window, scale, num_splits, status);
+  int rc = ccb_launch_status();
+  if (rc != 0 || num_splits == 1) return rc;
+  ccb_launch(attention_merge_bf16_kernel2, dim3(n_rows, nq), 128, 0, stream, (__nv_bfloat16*)out, part_acc, part_ml,
+             row0, nq, HD, num_splits);
+  return ccb_launch_status();
+}
+
+}  // namespace
+
+// As ccb_attention_decode_mma, for page sizes that are a power of two from 8 to 64 (others: CCB_REFUSE_SIZE).
+CCB_API int ccb_attention_decode_tma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                     float* part_acc, float* part_ml, const int* positions,
+                                     const int* entry_of_token, const int* block_table, int bt_stride,
+                                     int n_entries, int row0, int n_rows, int nq, int nkv, int hd, int page_size,
+                                     int num_pages, int window, float scale, int num_splits, int* status,
+                                     cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || bt_stride <= 0 || num_splits <= 0 || num_splits > 64 ||
+      page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0 ||
+      ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) != 0)
+    return CCB_REFUSE_SIZE;
+  if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return CCB_REFUSE_ARG;
+  if (hd == 128)
+    return launch<128>(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
+                       bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale, num_splits,
+                       status, stream);
+  if (hd == 64)
+    return launch<64>(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
+                      bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale, num_splits,
+                      status, stream);
+  return CCB_REFUSE_SIZE;
+}

@@ -35,6 +35,7 @@ GROUPS = {
         "attention_generic.cu",
         "attention_split.cu",
         "attention_decode_mma.cu",
+        "attention_decode_tma.cu",
         "attention_prefill_mma.cu",
         "attention_prefill_tc.cu",
         "gemm_f32.cu",

@@ -50,6 +50,9 @@ _SIGNATURES = {
     "ccb_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_int, c_void_p, c_void_p],
+    "ccb_attention_decode_tma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_float, c_int, c_void_p, c_void_p],
     "ccb_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                   c_void_p],
@@ -296,6 +299,33 @@ def attention_decode_mma(q, k_cache, v_cache, out, part_acc, part_ml, positions,
                                           block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
                                           num_pages, int(window), float(scale), num_splits, _p(status),
                                           _stream()), "attention_decode_mma")
+    if num_splits > 1:
+        counters.own += 1  # the merge kernel
+
+
+def attention_decode_tma_fits(hd: int, page_size: int) -> bool:
+    return hd in DECODE_MMA_HEAD_SIZES and 8 <= page_size <= 64 and page_size & (page_size - 1) == 0
+
+
+def attention_decode_tma(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
+                         n_entries: int, row0: int, n_rows: int, window: int, scale: float, num_splits: int,
+                         status=None) -> None:
+    """As attention_decode_mma, with keys and values loaded page by page through TMA boxes by a producer warp
+    (page size a power of two from 8 to 64)."""
+    _cuda(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status)
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    assert hd2 == hd and out.shape == q.shape
+    assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16
+    assert 0 <= row0 and row0 + n_rows <= T
+    if num_splits > 1:
+        assert part_acc.dtype == part_ml.dtype == torch.float32
+        assert part_acc.numel() >= n_rows * nq * num_splits * hd and part_ml.numel() >= n_rows * nq * num_splits * 2
+    _check(lib().ccb_attention_decode_tma(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml),
+                                          _p(positions), _p(entry_of_token), _p(block_table),
+                                          block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
+                                          num_pages, int(window), float(scale), num_splits, _p(status),
+                                          _stream()), "attention_decode_tma")
     if num_splits > 1:
         counters.own += 1  # the merge kernel
 

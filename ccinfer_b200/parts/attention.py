@@ -85,7 +85,10 @@ class GroupedQueryAttention(Mixer):
             splits, n_acc, n_ml = kernels.attention_split_plan(n_rows, self.nq, self.nkv, self.hd, per_block)
             part_acc = rt.scratch.get("attn_part_acc", (n_acc,), torch.float32)
             part_ml = rt.scratch.get("attn_part_ml", (n_ml,), torch.float32)
-            fn = kernels.attention_decode_mma if mma else kernels.attention_split
+            if mma and kernels.attention_decode_tma_fits(self.hd, g.page_size):
+                fn = kernels.attention_decode_tma     # pages arrive as TMA boxes
+            else:
+                fn = kernels.attention_decode_mma if mma else kernels.attention_split
             fn(q, cache.k, cache.v, o, part_acc, part_ml, step.positions, step.entry_of_token, g.block_table,
                step.n_entries, 0, n_rows, self.window or 0, self.scale, splits, status=rt.status)
         if mma and step.n_entries > step.n_single:

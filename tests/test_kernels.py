@@ -333,6 +333,51 @@ def test_attention_decode_mma(case, splits):
         assert torch.equal(part[1:-1], out[1:-1]) and float(part[0].abs().max()) == 0 == float(part[-1].abs().max())
 
 
+@pytest.mark.parametrize("splits", [1, 3, 32])
+@pytest.mark.parametrize("case", [c for c in MMA_CASES if c[5] >= 8])
+def test_attention_decode_tma(case, splits):
+    ctx, new, nq, nkv, hd, P, window = case
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", ctx, new, nq, nkv, hd, P, seed=hd + len(ctx),
+                                               window=window)
+    out = _run_split(q, kc, vc, pos, eot, bt, len(ctx), window, hd, splits, fn=_k().attention_decode_tma)
+    assert _rel(out, ref) <= 1.5e-2
+    if q.shape[0] > 2:
+        part = _run_split(q, kc, vc, pos, eot, bt, len(ctx), window, hd, splits, row0=1, n_rows=q.shape[0] - 2,
+                          fn=_k().attention_decode_tma)
+        assert torch.equal(part[1:-1], out[1:-1]) and float(part[0].abs().max()) == 0 == float(part[-1].abs().max())
+
+
+@pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 257, 511, 598])
+def test_attention_decode_tma_reads_far_key(far_key):
+    nq, nkv, hd, P = 8, 2, 128, 16
+    L = 600
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [L - 1], [1], nq, nkv, hd, P, seed=far_key,
+                                               peak=(0, far_key))
+    for splits in (1, 5):
+        out = _run_split(q, kc, vc, pos, eot, bt, 1, None, hd, splits, fn=_k().attention_decode_tma)
+        assert _rel(out, ref) <= 1.5e-2
+
+
+@pytest.mark.parametrize("edge", [-1, 0, 1])
+def test_attention_decode_tma_window_edge(edge):
+    nq, nkv, hd, P, W = 4, 1, 64, 8, 40
+    L = 200
+    key = (L - 1) - W + 1 + edge
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [L - 1], [1], nq, nkv, hd, P, seed=7, window=W,
+                                               peak=(0, key))
+    for splits in (1, 4):
+        out = _run_split(q, kc, vc, pos, eot, bt, 1, W, hd, splits, fn=_k().attention_decode_tma)
+        assert _rel(out, ref) <= 1.5e-2
+
+
+def test_attention_decode_tma_padding_rows():
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [40, 9], [1, 1], 4, 2, 64, 16, seed=3)
+    eot2 = eot.clone()
+    eot2[1] = -1
+    out = _run_split(q, kc, vc, pos, eot2, bt, 2, None, 64, 4, fn=_k().attention_decode_tma)
+    assert float(out[1].abs().max()) == 0.0 and _rel(out[:1], ref[:1]) <= 1.5e-2
+
+
 @pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 257, 511, 598])
 def test_attention_decode_mma_reads_far_key(far_key):
     nq, nkv, hd, P = 8, 2, 128, 16
