@@ -287,3 +287,87 @@ def test_toy_mixer_with_state_of_its_own(tmp_path):
     rows["c"].append(out[:11]); rows["a"].append(out[11:])
     for rid, toks in (("a", a), ("b", b), ("c", c)):
         assert _rel(torch.cat(rows[rid]), _toy_plain(w, cfg, toks)) <= 2e-5, rid
+
+
+# ---------------------------------------------------------------------------------------------
+# more toy parts defined here: a feed-forward with routing, and other position encodings
+# ---------------------------------------------------------------------------------------------
+def _toy_routed_ffn():
+    from ccinfer_b200.parts.base import FeedForward, TensorSpec
+
+    class Top1Experts(FeedForward):
+        """Router logits in float, one expert per token (ties to the lowest id), y = p_e * (x W_e^T)."""
+
+        def __init__(self, dim, n_experts, prefix):
+            self.dim, self.n, self.prefix = dim, n_experts, prefix
+
+        def tensor_specs(self):
+            return [TensorSpec(f"{self.prefix}.router", (self.n, self.dim))] + \
+                   [TensorSpec(f"{self.prefix}.expert{e}", (self.dim, self.dim)) for e in range(self.n)]
+
+        def bind(self, rt, fetch):
+            self.router = fetch(f"{self.prefix}.router")
+            self.experts = torch.stack([fetch(f"{self.prefix}.expert{e}") for e in range(self.n)])
+
+        def forward(self, x, step):
+            logits = x.float() @ self.router.float().T
+            p = torch.softmax(logits, dim=-1)
+            e = torch.argmax(logits, dim=-1)  # first maximum
+            y = torch.einsum("td,tod->to", x.float(), self.experts[e].float())
+            return (y * p.gather(1, e[:, None])).to(x.dtype)
+
+    return Top1Experts
+
+
+@pytest.mark.parametrize("pos_kind", ["scaled", "none"])
+def test_toy_routed_feed_forward_and_other_position_encodings(pos_kind):
+    """A block of the package's attention with a position encoding defined here (interpolated rotary, or none
+    at all) and a routed feed-forward defined here, against the plain functions."""
+    from ccinfer_b200.engine.engine import StepEntry
+    from ccinfer_b200.engine.plan import ModelPlan, RunEntry
+    from ccinfer_b200.parts import (GroupedQueryAttention, NoPosition, OutputHead, PreNormBlock, RMSNorm, RotaryHalf,
+                                    TokenEmbedding)
+    Top1Experts = _toy_routed_ffn()
+    D, nq, nkv, hd, V, eps, theta, factor = 48, 3, 1, 16, 71, 1e-6, 1e4, 4.0
+
+    class InterpolatedRotary(RotaryHalf):
+        """Positions divided by a factor: the same kernel, another table."""
+
+        def bind(self, rt, fetch):
+            super().bind(rt, fetch)
+            self.inv_freq = (self.inv_freq.double() / factor).float()
+
+    position = InterpolatedRotary(hd, theta) if pos_kind == "scaled" else NoPosition()
+    names = {k: f"a.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+    block = PreNormBlock(RMSNorm(D, eps, "n1"), GroupedQueryAttention(D, nq, nkv, hd, position, names, qk_norm_eps=eps),
+                         RMSNorm(D, eps, "n2"), Top1Experts(D, 4, "moe"))
+    plan = ModelPlan(TokenEmbedding(V, D, "emb"), [block], [RunEntry(0)], RMSNorm(D, eps, "nf"),
+                     OutputHead(D, V, "head"), V, 256)
+    w = _weights(plan.tensor_specs(), 11, std=0.2)
+    eng = _engine(plan, w, "float32")
+    assert not hasattr(block.ffn, "rt")  # the toy part is not one of the package's
+    toks = list(np.random.RandomState(3).randint(0, V, size=37))
+    eng.open_request("r")
+    got = torch.cat([eng.step([StepEntry("r", toks[:20], range(20))]), eng.step([StepEntry("r", toks[20:22], [0, 1])]),
+                     eng.step([StepEntry("r", toks[22:], range(15))])]).cpu()
+    eng.check()
+
+    wd = {k: v.double() for k, v in w.items()}
+    T = len(toks)
+    pos = torch.arange(T)
+    h = plain.embed(wd["emb"], toks)
+    x = plain.rms_norm(h, wd["n1"], eps)
+    q = plain.rms_norm((x @ wd["a.q"].T).view(T, nq, hd), wd["a.q_norm"], eps)
+    k = plain.rms_norm((x @ wd["a.k"].T).view(T, nkv, hd), wd["a.k_norm"], eps)
+    v = (x @ wd["a.v"].T).view(T, nkv, hd)
+    if pos_kind == "scaled":
+        inv = (plain.rope_inv_freq(hd, theta).double() / factor).float()
+        q, k = plain.apply_rope(q, pos, inv), plain.apply_rope(k, pos, inv)
+    h = h + plain.causal_attention(q, k, v).reshape(T, -1) @ wd["a.o"].T
+    x = plain.rms_norm(h, wd["n2"], eps)
+    logits = x @ wd["moe.router"].T
+    p = torch.softmax(logits, -1)
+    e = torch.argmax(logits, -1)
+    y = torch.stack([x[t] @ wd[f"moe.expert{int(e[t])}"].T * p[t, e[t]] for t in range(T)])
+    ref = plain.rms_norm(h + y, wd["nf"], eps) @ wd["head"].T
+    assert _rel(got, ref) <= 2e-5
