@@ -201,7 +201,6 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       }
     }
     cp_async_wait<0>();
-    pdl_trigger();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);

@@ -217,7 +217,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         }
       }
     }
-    pdl_trigger();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);

@@ -70,10 +70,13 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // before it touches memory that another kernel may have written.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// Kernels without weights to prefetch: wait first; they trigger their successor late (pdl_trigger() after
-// their main loop, or implicitly at exit), so that the successor's launch overlaps only their tail and does
-// not take SM resources away while they still need them.
-__device__ __forceinline__ void pdl_begin() { pdl_wait(); }
+// Kernels without weights to prefetch: let the successor start at once (only the products are launched
+// with the attribute: their blocks then stream the first weight tiles while this kernel runs), then wait
+// for the predecessor.
+__device__ __forceinline__ void pdl_begin() {
+  pdl_trigger();
+  pdl_wait();
+}
 
 __device__ __forceinline__ void set_status(int* status, int bit) {
   if (status != nullptr) atomicOr(status, bit);

@@ -58,15 +58,28 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
   for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.f;
 
   constexpr int U = 4;  // 32-wide k blocks in flight per warp
-  pdl_wait();  // before the token operand (written by the kernel before this one) is read
+  // The weights do not depend on the kernel before this one: the loads of the first group of k blocks are
+  // issued before waiting for it (programmatic dependent launch), the token operand after.
   int kb = kb0;
+  uint4 a0[U], a1[U];
+  const bool first_full = kb + U <= kb1;
+  if (first_full) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      a0[u] = ld_stream16(w0 + ((kb + u) << 5));
+      a1[u] = ld_stream16(w1 + ((kb + u) << 5));
+    }
+  }
+  pdl_wait();
   for (; kb + U <= kb1; kb += U) {
-    uint4 a0[U], a1[U], x[U][NB];
+    uint4 x[U][NB];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = (kb + u) << 5;
-      a0[u] = ld_stream16(w0 + k);
-      a1[u] = ld_stream16(w1 + k);
+      if (kb != kb0) {  // the first group is already on its way
+        a0[u] = ld_stream16(w0 + k);
+        a1[u] = ld_stream16(w1 + k);
+      }
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb)
         x[u][nb] = xv[nb] ? *reinterpret_cast<const uint4*>(xa[nb] + k) : make_uint4(0u, 0u, 0u, 0u);

@@ -110,7 +110,6 @@ residual_rmsnorm_vec_kernel(T* __restrict__ y, float* __restrict__ h, const T* _
     }
   }
   ss = block_sum<kNormThreads>(ss, red);
-  pdl_trigger();
   const float inv = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
   for (int j = 0; j < kNormVecs; ++j) {
