@@ -29,6 +29,8 @@ import collections
 import dataclasses
 from typing import Dict, Hashable, List, Optional, Tuple
 
+import numpy as np
+
 from ..errors import (InvalidArgument, KVBlockDoubleFree, KVBlockExhausted, KVInvalidBlockTable, SlotExhausted)
 
 
@@ -133,12 +135,35 @@ class RequestCache:
         self.slot = slot
         self.ctx_len = 0
         self.tables: List[List[int]] = [[] for _ in range(n_groups)]
+        # the same tables as int32 arrays (with spare capacity), kept in step by the manager: what the step
+        # function copies into its pinned buffer without walking a Python list per request and step
+        self._arrays: List[np.ndarray] = [np.full(16, -1, dtype=np.int32) for _ in range(n_groups)]
         # pages taken by reserve() and not yet committed: [(group, logical index)]
         self._pending: List[Tuple[int, int]] = []
         self._pending_tokens = 0
 
     def pages_held(self, g: int) -> int:
         return sum(1 for p in self.tables[g] if p >= 0)
+
+    def table_array(self, g: int) -> np.ndarray:
+        """The block table of group g as an int32 array (a view: do not keep it across steps)."""
+        return self._arrays[g][:len(self.tables[g])]
+
+    def _append(self, g: int, page: int) -> None:
+        n = len(self.tables[g])
+        if n == self._arrays[g].size:
+            grown = np.full(2 * n, -1, dtype=np.int32)
+            grown[:n] = self._arrays[g]
+            self._arrays[g] = grown
+        self._arrays[g][n] = page
+        self.tables[g].append(page)
+
+    def _pop(self, g: int) -> None:
+        self.tables[g].pop()
+
+    def _drop(self, g: int, i: int) -> None:
+        self.tables[g][i] = -1
+        self._arrays[g][i] = -1
 
 
 class CacheManager:
@@ -168,6 +193,7 @@ class CacheManager:
         for g, pool in enumerate(self.pools):
             pool.give_back(req_id, [p for p in rc.tables[g] if p >= 0])
             rc.tables[g] = []
+            rc._arrays[g] = np.full(16, -1, dtype=np.int32)
         self.slots.give_back(rc.slot)
         del self.requests[req_id]
 
@@ -211,7 +237,7 @@ class CacheManager:
                 n = self._pages_needed(rc, g, n_new)
                 pages = pool.take(req_id, n)
                 for p in pages:
-                    rc.tables[g].append(p)
+                    rc._append(g, p)
                     taken.append((g, len(rc.tables[g]) - 1))
         except KVBlockExhausted:
             self._undo(rc, taken)
@@ -226,7 +252,7 @@ class CacheManager:
             self.pools[g].give_back(rc.req_id, pages)
             for i in idx:  # they are the tail of the table
                 assert i == len(rc.tables[g]) - 1
-                rc.tables[g].pop()
+                rc._pop(g)
 
     def rollback(self, req_id: Hashable) -> None:
         """Returns the pages of a reservation whose step did not happen."""
@@ -249,7 +275,7 @@ class CacheManager:
             if stale:
                 self.pools[g].give_back(req_id, [rc.tables[g][i] for i in stale])
                 for i in stale:
-                    rc.tables[g][i] = -1
+                    rc._drop(g, i)
 
     # -- addressing -------------------------------------------------------------------
     def slot_of(self, rc: RequestCache, g: int, position: int) -> int:
@@ -293,3 +319,6 @@ class CacheManager:
             for p, owner in held.items():
                 if pool.owner_of(p) != owner:
                     raise AssertionError(f"group {g}: page {p} owner mismatch")
+            for rc in self.requests.values():
+                if rc.table_array(g).tolist() != rc.tables[g]:
+                    raise AssertionError(f"group {g}: the array of request {rc.req_id!r} differs from its table")

@@ -276,11 +276,18 @@ class Engine:
             P, stride = spec.page_size, lay.group_strides[g]
             sm = host[lay.o_slot_map[g]:lay.o_slot_map[g] + Tp]
             bt = host[lay.o_block_table[g]:lay.o_block_table[g] + Bp * stride].reshape(Bp, stride)
-            for b, rc in enumerate(rcs):
-                table = np.asarray(rc.tables[g], dtype=np.int32)
-                bt[b, :table.size] = table
-                p = np.arange(pos0[b], pos0[b] + counts[b])
-                sm[cu[b]:cu[b + 1]] = table[p // P] * P + p % P
+            if T == B:  # every entry brings one token: no per-entry arrays
+                for b, rc in enumerate(rcs):
+                    table = rc.table_array(g)
+                    bt[b, :table.size] = table
+                    pb = int(pos0[b])
+                    sm[b] = int(table[pb // P]) * P + pb % P
+            else:
+                for b, rc in enumerate(rcs):
+                    table = rc.table_array(g)
+                    bt[b, :table.size] = table
+                    p = np.arange(pos0[b], pos0[b] + counts[b])
+                    sm[cu[b]:cu[b + 1]] = table[p // P] * P + p % P
             sm[T:Tp] = -1
             step.groups.append(GroupStep(
                 index=g, page_size=P, num_pages=spec.num_pages, window=spec.window,

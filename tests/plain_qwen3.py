@@ -3,7 +3,8 @@
 It rests on the formulas of 7QiC/ccInfer's kernels and model code (cited per
 function as ``path:line`` within that project); the reference's own model code
 cannot run without a GPU, boost and real weights, so nothing here was compared
-with it live.  Whole sequences, no cache, one function per part, CPU only, and
+with it live (the one part of it that does run on a CPU, its config.json
+parser, is compared in tests/golden/).  Whole sequences, no cache, one function per part, CPU only, and
 no code shared with the ``ccinfer_b200`` package: this file imports nothing
 from it.  Everything is computed in float64 by default so that the error of
 the engine's 32-bit path is visible down to 32-bit round-off.

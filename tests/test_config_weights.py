@@ -202,3 +202,29 @@ def test_damaged_files(tmp_path, damage):
         path.unlink()
     with pytest.raises(ModelLoadFailed):
         open_weights(str(d), [], "cpu", torch.float32)
+
+
+def _golden_config_cases():
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "config_parse.json")) as f:
+        g = json.load(f)
+    return [(name, g["cases"][name], g["parsed"][name]) for name in sorted(g["cases"])]
+
+
+@pytest.mark.parametrize("name,config_json,theirs", _golden_config_cases(), ids=lambda v: v if isinstance(v, str) else "")
+def test_parser_agrees_with_the_reference_parser(name, config_json, theirs):
+    """golden/config_parse.json holds what ModelConfig::from_json of 7QiC/ccInfer (src/model/config.h:41-160)
+    read from these files (made by golden/make_config_golden.py).  Same fields, same error class; the
+    reference stores theta and eps as 32-bit floats, this package as given."""
+    import ccinfer_b200.errors as errors
+    if "error" in theirs:
+        with pytest.raises(getattr(errors, theirs["error"])):
+            architecture_of(config_json).parse_config(config_json)
+        return
+    cfg = architecture_of(config_json).parse_config(config_json)
+    for key in ("num_hidden_layers", "num_attention_heads", "num_key_value_heads", "hidden_size", "head_dim",
+                "intermediate_size", "vocab_size", "max_position_embeddings"):
+        assert getattr(cfg, key) == theirs[key], key
+    for key in ("rope_theta", "rms_norm_eps"):
+        assert getattr(cfg, key) == pytest.approx(theirs[key], rel=1e-6), key
