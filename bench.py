@@ -9,8 +9,10 @@ vocabulary 151936, bfloat16, a batch of 8 requests decoding after 2,048-token
 prompts.  It prints ONE JSON line:
 
   value      decoded tokens a second, from CUDA events around each of the K timed steps
-  e2e        the same through the Python entry point's scheduler: host token ids in (pinned
-             memory, one copy a step) and sampled token ids out (one read a step), by wall clock
+  e2e        the same through the Python entry point's scheduler, by wall clock: host prompts in, every
+             step one copy of the step's arrays from pinned memory and one read of the sampled token
+             ids into host lists.  The scheduler runs one step ahead: a step is launched before the
+             tokens of the step before it are read (the embedding takes them from the device)
   prefill    one 2,048-token prompt in one step: tokens a second and the fraction of the bf16 peak
   roofline   the decode step's bytes (every weight once + the cache of the live requests) / its time
   points     decode at batch 1 and 64
@@ -236,7 +238,8 @@ def main() -> int:
 
     def decode_e2e(B):
         """The same K steps through the scheduler: host token lists in, sampled host tokens out, wall clock."""
-        sched = Scheduler(engine, prefill_chunk_size=0, max_tokens_per_step=opt.max_tokens_per_step, max_running=B)
+        sched = Scheduler(engine, prefill_chunk_size=0, max_tokens_per_step=opt.max_tokens_per_step, max_running=B,
+                          run_ahead=True)
         fill(B, sched)
         while any(not r.prefill_done for r in sched.active.values()) or sched.waiting:
             sched.step()
@@ -245,7 +248,7 @@ def main() -> int:
         torch.cuda.synchronize()
         t = time.perf_counter()
         produced = 0
-        for _ in range(K):
+        for _ in range(K):  # each call launches a step and returns the host tokens of the step before it
             produced += sum(1 for ev in sched.step() if ev.token is not None)
         torch.cuda.synchronize()
         wall = time.perf_counter() - t
@@ -271,7 +274,7 @@ def main() -> int:
     step_bytes = weight_bytes + args.batch * mean_ctx * kv_per_token
     achieved = step_bytes / (main_r["ms_per_step"] * 1e-3) / 1e9
     line = {
-        "metric": "decode tokens/s (Qwen3-8B shape, batch 8, after 2,048-token prompts)",
+        "metric": f"decode tokens/s (Qwen3-8B shape, batch {args.batch}, after {ctx:,}-token prompts)",
         "value": round(main_r["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(main_r["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights (seed 42, N(0, 0.02))",

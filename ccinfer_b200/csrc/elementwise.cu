@@ -18,10 +18,14 @@ CCB_API int ccb_set_pdl(int on) {
 
 template <typename T>
 __global__ void embed_gather_kernel(float* __restrict__ h, const T* __restrict__ table,
-                                    const int* __restrict__ ids, int D, int V, int* status) {
+                                    const int* __restrict__ ids, int D, int V, const int* __restrict__ pending,
+                                    int n_pending, int* status) {
   ccb::pdl_begin();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  // id = -1 - s names the token that the sampling kernel last stored for request slot s: the host has
+  // launched this step before it has read that token
+  if (id < 0 && pending != nullptr && -1 - id < n_pending) id = pending[-1 - id];
   float* out = h + (size_t)t * D;
   if (id < 0 || id >= V) {
     if (threadIdx.x == 0) set_status(status, CCB_ST_BAD_TOKEN);
@@ -33,14 +37,15 @@ __global__ void embed_gather_kernel(float* __restrict__ h, const T* __restrict__
 }
 
 CCB_API int ccb_embed_gather(float* h, const void* table, const int* ids, int T_, int D, int V,
-                             int dtype, int* status, cudaStream_t stream) {
+                             int dtype, const int* pending, int n_pending, int* status, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (D <= 0 || V <= 0) return CCB_REFUSE_SIZE;
   const int threads = D >= 1024 ? 256 : 128;
   if (dtype == CCB_F32)
-    ccb_launch(embed_gather_kernel<float>, T_, threads, 0, stream, h, (const float*)table, ids, D, V, status);
+    ccb_launch(embed_gather_kernel<float>, T_, threads, 0, stream, h, (const float*)table, ids, D, V, pending, n_pending, status);
   else if (dtype == CCB_BF16)
-    ccb_launch(embed_gather_kernel<__nv_bfloat16>, T_, threads, 0, stream, h, (const __nv_bfloat16*)table, ids, D, V, status);
+    ccb_launch(embed_gather_kernel<__nv_bfloat16>, T_, threads, 0, stream, h, (const __nv_bfloat16*)table, ids, D, V, pending,
+               n_pending, status);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();

@@ -43,7 +43,8 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, size_t ld, int* __restrict__ tokens,
                    const float* __restrict__ temperature, const unsigned* __restrict__ seed,
-                   const int* __restrict__ out_index, int V) {
+                   const int* __restrict__ out_index, int V, const int* __restrict__ slot_of_row,
+                   int* __restrict__ by_slot, int n_slots) {
   ccb::pdl_begin();
   __shared__ float sv[kSampleThreads];
   __shared__ int si[kSampleThreads];
@@ -76,16 +77,27 @@ sample_rows_kernel(const float* __restrict__ logits, size_t ld, int* __restrict_
     __syncthreads();
   }
   // a row of NaNs or -inf only leaves the sentinel: report id 0 as the reference's kernel does
-  if (threadIdx.x == 0) tokens[r] = si[0] == 0x7fffffff ? 0 : si[0];
+  if (threadIdx.x == 0) {
+    const int tok = si[0] == 0x7fffffff ? 0 : si[0];
+    tokens[r] = tok;
+    // also kept per request slot, where the next step's embedding finds it without a round trip to the host
+    if (slot_of_row != nullptr) {
+      const int s = slot_of_row[r];
+      if (s >= 0 && s < n_slots) by_slot[s] = tok;
+    }
+  }
 }
 
 }  // namespace
 
 CCB_API int ccb_sample_rows(const float* logits, long long ld, int* tokens, const float* temperature,
-                            const unsigned* seed, const int* out_index, int R, int V, cudaStream_t stream) {
+                            const unsigned* seed, const int* out_index, int R, int V, const int* slot_of_row,
+                            int* by_slot, int n_slots, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) return CCB_REFUSE_SIZE;
   if (temperature != nullptr && (seed == nullptr || out_index == nullptr)) return CCB_REFUSE_ARG;
-  ccb_launch(sample_rows_kernel, R, kSampleThreads, 0, stream, logits, (size_t)ld, tokens, temperature, seed, out_index, V);
+  if (slot_of_row != nullptr && (by_slot == nullptr || n_slots <= 0)) return CCB_REFUSE_ARG;
+  ccb_launch(sample_rows_kernel, R, kSampleThreads, 0, stream, logits, (size_t)ld, tokens, temperature, seed, out_index, V,
+             slot_of_row, by_slot, n_slots);
   return ccb_launch_status();
 }

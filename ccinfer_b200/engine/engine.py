@@ -33,8 +33,25 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 @dataclasses.dataclass
 class StepEntry:
     req_id: Hashable
-    tokens: Sequence[int]
+    tokens: Sequence[int]        # [PENDING] = the token that the last sampling stored for this request
     want: Sequence[int] = ()     # places among ``tokens`` whose logits are wanted
+
+
+# In place of a token id in a one-token entry: the token that ``Engine.sample_async`` last drew for the
+# request.  It is still on the device; a scheduler that runs one step ahead has not read it yet.
+PENDING = -1
+
+
+class SampledTokens:
+    """Tokens drawn by ``Engine.sample_async``: on their way to pinned host memory."""
+
+    def __init__(self, host: torch.Tensor, event: "torch.cuda.Event", n: int):
+        self._host, self._event, self._n = host, event, n
+
+    def tokens(self) -> List[int]:
+        """Waits for the copy and returns one host integer per logits row."""
+        self._event.synchronize()
+        return self._host[:self._n].tolist()
 
 
 @dataclasses.dataclass
@@ -120,7 +137,15 @@ class Engine:
         self._dev_buf = torch.zeros(lay.size, dtype=torch.int32, device=rt.device)
         n_rows = max(opt.max_requests, 1)
         self._sample_tokens = torch.zeros(opt.max_tokens_per_step, dtype=torch.int32, device=rt.device)
-        self._sample_host = torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32).pin_memory()
+        self._sample_host = [torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32).pin_memory()
+                             for _ in range(2)]
+        self._sample_out = [torch.zeros(opt.max_tokens_per_step, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._sample_events = [None, None]
+        self._sample_turn = 0
+        # the token last drawn for each request slot, read by the next step's embedding for PENDING entries
+        self._pending_tokens = torch.zeros(opt.max_requests, dtype=torch.int32, device=rt.device)
+        self._pending_slots = set()   # slots whose pending token is valid
+        self._last_row_slot = None    # (device view, host list) of the most recent step's logits rows
         self._sample_dev = torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32, device=rt.device)
         self.steps_run = 0
         self.graph_replays = 0
@@ -165,6 +190,9 @@ class Engine:
 
     def close_request(self, req_id: Hashable) -> None:
         """Gives back what the request holds: its pages in every group and its slot."""
+        rc = self.cache.requests.get(req_id)
+        if rc is not None:
+            self._pending_slots.discard(rc.slot)
         self.cache.close(req_id)
 
     def context_len(self, req_id: Hashable) -> int:
@@ -190,6 +218,10 @@ class Engine:
             if rc.ctx_len + n > self.max_context:
                 raise RequestTooLong(f"request {e.req_id!r}: {rc.ctx_len} cached + {n} new tokens exceed the "
                                      f"limit of {self.max_context}")
+            if min(e.tokens) < 0:
+                if n != 1 or e.tokens[0] != PENDING or rc.slot not in self._pending_slots:
+                    raise InvalidArgument(f"request {e.req_id!r}: token ids are non-negative (PENDING stands alone, "
+                                          f"after a sample_async for the request)")
             for w in e.want:
                 if not (0 <= w < n):
                     raise InvalidArgument(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
@@ -227,6 +259,12 @@ class Engine:
             tok[cu[b]:cu[b + 1]] = e.tokens
         eot[:T] = np.repeat(np.arange(B, dtype=np.int32), counts)
         posv[:T] = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1] - pos0, counts)
+        slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=B)
+        n_single = int((counts == 1).sum())  # they come first
+        first = tok[:n_single]
+        pending = first < 0
+        if pending.any():
+            first[pending] = -1 - slots[:n_single][pending]  # resolved on the device from the pending tokens
         tok[T:Tp] = 0
         posv[T:Tp] = 0
         eot[T:Tp] = -1
@@ -237,8 +275,14 @@ class Engine:
             rows = [int(cu[place[i]]) + int(w) for i, e in enumerate(given) for w in e.want]
         R = len(rows)
         lr = host[lay.o_logit_rows:lay.o_logit_rows + max(R, 1)]
+        rs = host[lay.o_row_slot:lay.o_row_slot + max(R, 1)]
+        if pad_to:
+            row_slots = slots.tolist() + [-1] * (Bp - B)
+        else:
+            row_slots = [rcs[place[i]].slot for i, e in enumerate(given) for _ in e.want]
         if R:
             lr[:R] = rows
+            rs[:R] = row_slots
         hcu = host[lay.o_cu_q:lay.o_cu_q + Bp + 1]
         hcu[:B + 1] = cu
         hcu[B + 1:] = np.arange(T + 1, Tp + 1)
@@ -247,14 +291,13 @@ class Engine:
         hss = host[lay.o_state_slot:lay.o_state_slot + Bp]
         hp0[:B] = pos0
         hca[:B] = pos0 + counts
-        hss[:B] = [rc.slot for rc in rcs]
+        hss[:B] = slots
         hp0[B:] = 0
         hca[B:] = 0
         hss[B:] = -1
 
         step = StepContext()
         step.n_tokens, step.n_entries, step.n_logit_rows = Tp, Bp, R
-        n_single = int((counts == 1).sum())
         step.n_single = n_single + (Bp - B) if n_single == B else n_single   # padding rows are single rows too
         step.max_q_len = int(counts.max())
         step.max_ctx = int((pos0 + counts).max())
@@ -267,6 +310,9 @@ class Engine:
         step.positions = dv(lay.o_positions, Tp)
         step.entry_of_token = dv(lay.o_entry_of_token, Tp)
         step.logit_rows = dv(lay.o_logit_rows, max(R, 1))
+        step.row_slot = dv(lay.o_row_slot, max(R, 1))
+        step.pending_tokens = self._pending_tokens
+        self._last_row_slot = (step.row_slot, row_slots[:len(given)] if pad_to else row_slots)
         step.cu_q = dv(lay.o_cu_q, Bp + 1)
         step.pos0 = dv(lay.o_pos0, Bp)
         step.ctx_after = dv(lay.o_ctx_after, Bp)
@@ -390,23 +436,48 @@ class Engine:
         row's request has produced so far.  A draw depends on (seed, out_index) only, not on the
         batch.  Returns host integers (this waits for the step).
         """
-        R = logits.shape[0]
-        if R == 0:
+        if logits.shape[0] == 0:
             return []
+        return self.sample_async(logits, params, out_index).tokens()
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence, out_index: Sequence[int]) -> SampledTokens:
+        """As ``sample`` for the logits of the most recent step, without waiting.
+
+        The tokens go to pinned host memory (``SampledTokens.tokens()`` waits for them) and stay on the
+        device per request: the request's next entry may bring ``[PENDING]`` in place of the token, so the
+        next step can be launched before this one's tokens have been read.  At most two results may be
+        outstanding."""
+        R = logits.shape[0]
         if len(params) != R or len(out_index) != R:
             raise InvalidArgument("one parameter set and one output index per logits row")
+        turn = self._sample_turn
+        self._sample_turn ^= 1
+        if self._sample_events[turn] is not None:
+            self._sample_events[turn].synchronize()  # the copies that used this turn's pinned buffers are over
         tokens = self._sample_tokens[:R]
-        if all(p.temperature <= 0 for p in params):
-            kernels.sample_rows(logits, tokens)
-        else:
-            hp = self._sample_host
+        slot_dev = slots = None
+        if self._last_row_slot is not None and len(self._last_row_slot[1]) == R:
+            slot_dev, slots = self._last_row_slot
+        if R and all(p.temperature <= 0 for p in params):
+            kernels.sample_rows(logits, tokens, slot_of_row=slot_dev, by_slot=self._pending_tokens)
+        elif R:
+            hp = self._sample_host[turn]
             hp[0, :R] = torch.tensor([float(p.temperature) for p in params], dtype=torch.float32).view(torch.int32)
             hp[1, :R] = torch.tensor([int(p.seed) & 0xFFFFFFFF for p in params], dtype=torch.int64).to(torch.int32)
             hp[2, :R] = torch.tensor(list(out_index), dtype=torch.int32)
             self._sample_dev.copy_(hp, non_blocking=True)
             d = self._sample_dev
-            kernels.sample_rows(logits, tokens, d[0, :R].view(torch.float32), d[1, :R], d[2, :R])
-        return tokens.tolist()
+            kernels.sample_rows(logits, tokens, d[0, :R].view(torch.float32), d[1, :R], d[2, :R],
+                                slot_of_row=slot_dev, by_slot=self._pending_tokens)
+        if slots is not None:
+            self._pending_slots.update(s for s in slots if s >= 0)
+        out = self._sample_out[turn]
+        if R:
+            out[:R].copy_(tokens, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._sample_events[turn] = ev
+        return SampledTokens(out, ev, R)
 
     def check(self) -> None:
         """Synchronises and raises DeviceFault if a kernel reported a bad index since the last check."""

@@ -25,9 +25,21 @@ Unlike the reference (one SamplingParams per batch, requests that differ are
 skipped, :489-498), every request keeps its own parameters and greedy and
 temperature requests share a step.
 
+Running ahead (``run_ahead=True``; the reference's loop waits for every step,
+src/scheduler/scheduler.cpp:206-284): a step is launched before the tokens of
+the step before it have been read.  A decoding request's entry then names the
+token by ``PENDING``; the engine finds it on the device, where the sampling
+kernel left it.  Everything that decides a step is known without the tokens
+(lengths, pages, how many tokens a request has produced), except an
+end-of-sequence stop: a request that stops that way has one more step in
+flight, whose token is dropped.  The events of a step are returned by the
+call after it; before a preemption or a cancellation the step in flight is
+read first, so those never see a token that is still on the device.
+
 The scheduler only needs of its engine: ``open_request``, ``close_request``,
 ``step(entries) -> logits``, ``sample(logits, params, out_index) -> tokens``,
 ``cache`` (a CacheManager) and ``max_context``; tests drive it with a fake.
+Running ahead also needs ``sample_async(...) -> object with tokens()``.
 """
 from __future__ import annotations
 
@@ -37,6 +49,8 @@ from typing import Dict, Hashable, List, Optional, Sequence
 
 from ..errors import InvalidArgument, KVBlockExhausted, RequestTooLong
 from ..sampling.params import SamplingParams
+
+PENDING = -1   # engine.PENDING: in place of a token that the sampling kernel left on the device
 
 
 @dataclasses.dataclass
@@ -67,6 +81,12 @@ class _Request:
         self.started_at = -1                # order of first scheduling (for the preemption victim)
         self.replaying = False              # the prompt's last portion does not sample
         self.finished = False
+        self.pending = 0                    # tokens drawn in a step whose results have not been read yet
+
+    @property
+    def n_out(self) -> int:
+        """Tokens produced so far, those still on the device included."""
+        return len(self.generated) + self.pending
 
     @property
     def prefill_done(self) -> bool:
@@ -75,7 +95,7 @@ class _Request:
 
 class Scheduler:
     def __init__(self, engine, prefill_chunk_size: int = 512, max_tokens_per_step: int = 4096,
-                 max_running: int = 16, eos_token_id: Optional[int] = None):
+                 max_running: int = 16, eos_token_id: Optional[int] = None, run_ahead: bool = False):
         if prefill_chunk_size < 0 or max_tokens_per_step <= 0 or max_running <= 0:
             raise InvalidArgument("prefill_chunk_size >= 0, max_tokens_per_step > 0, max_running > 0")
         self.engine = engine
@@ -89,6 +109,9 @@ class Scheduler:
         self._start_counter = 0
         self.preemptions = 0
         self.steps = 0
+        self.run_ahead = bool(run_ahead)
+        self._inflight = None                 # (items, requests that sample, SampledTokens) of the step not yet read
+        self._carry: List[TokenEvent] = []    # events read outside step(), returned by the next call
 
     # -- requests ---------------------------------------------------------------------
     def submit(self, req_id: Hashable, prompt: Sequence[int], params: SamplingParams = None) -> None:
@@ -115,6 +138,8 @@ class Scheduler:
             if r.req_id == req_id:
                 self.waiting.remove(r)
                 return True
+        if req_id in self.active:
+            self._resolve(self._carry)  # its last token may still be on the device
         r = self.active.get(req_id)
         if r is None:
             return False
@@ -122,7 +147,7 @@ class Scheduler:
         return True
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.active)
+        return bool(self.waiting or self.active or self._inflight is not None or self._carry)
 
     # -- building a step ------------------------------------------------------------------
     def _admit(self, events: List[TokenEvent]) -> None:
@@ -157,13 +182,15 @@ class Scheduler:
             r = self.active[rid]
             if not r.prefill_done or budget <= 0:
                 continue
+            if r.pending and (r.n_out >= r.params.max_tokens or cache.get(rid).ctx_len + 1 > self.engine.max_context):
+                continue  # it ends when its token has been read
             need = cache.pages_needed(rid, 1)
             if not fits(need):
                 self._blocked.append(rid)
                 continue
             take(need)
             budget -= 1
-            items.append(ScheduledItem(rid, [r.generated[-1]], True, "decode"))
+            items.append(ScheduledItem(rid, [PENDING if r.pending else r.generated[-1]], True, "decode"))
         # then portions of prompts
         started = sum(1 for r in self.active.values() if r.started_at >= 0)
         for rid in self.order:
@@ -204,6 +231,7 @@ class Scheduler:
 
     def _preempt_one(self) -> bool:
         """Frees the pages of the request that started last (it will be computed again); False if none can be."""
+        assert self._inflight is None  # step() reads the step in flight before it gets here
         victims = [r for r in self.active.values() if r.started_at >= 0 and self.engine.cache.get(r.req_id).ctx_len > 0]
         if len(victims) <= 1 and not self._blocked_other_than(victims):
             return False
@@ -229,13 +257,24 @@ class Scheduler:
 
     # -- running a step ----------------------------------------------------------------------
     def step(self) -> List[TokenEvent]:
-        """Admits, builds and runs one step; returns the tokens it produced and the requests it ended."""
-        events: List[TokenEvent] = []
+        """Admits, builds and runs one step; returns the tokens it produced and the requests it ended.
+
+        When running ahead, the tokens are those of the step before (this call launches its step first
+        and then reads the earlier one)."""
+        events: List[TokenEvent] = self._carry
+        self._carry = []
         self._admit(events)
         self._finish_exhausted(events)
+        items = self.plan() if self.active else []
+        if not items and self._inflight is not None:
+            # nothing to launch before the tokens in flight are known (requests at their last token, or
+            # pages that only an ending request gives back)
+            self._resolve(events)
+            self._admit(events)
+            self._finish_exhausted(events)
+            items = self.plan() if self.active else []
         if not self.active:
             return events
-        items = self.plan()
         guard = 0
         while not items:
             # nothing fits: give one request's pages to the others, or fail if there is nothing to give
@@ -247,14 +286,13 @@ class Scheduler:
         from .engine import StepEntry
         entries = [StepEntry(it.req_id, it.tokens, [len(it.tokens) - 1] if it.sample else []) for it in items]
         logits = self.engine.step(entries)
-        sampled = [it for it in items if it.sample]
-        tokens: List[int] = []
-        if sampled:
-            reqs = [self.active[it.req_id] for it in sampled]
-            tokens = self.engine.sample(logits, [r.params for r in reqs], [len(r.generated) for r in reqs])
+        reqs = [self.active[it.req_id] for it in items if it.sample]
+        handle = None
+        if reqs:
+            args = (logits, [r.params for r in reqs], [r.n_out for r in reqs])
+            handle = self.engine.sample_async(*args) if self.run_ahead else _Now(self.engine.sample(*args))
         self.steps += 1
-        # apply
-        k = 0
+        # what is known at launch
         ran = []
         for it in items:
             r = self.active[it.req_id]
@@ -264,25 +302,45 @@ class Scheduler:
                 if r.prefill_done and r.replaying:
                     r.replaying = False  # decoding goes on from the token it already has
             if it.sample:
-                tok = int(tokens[k])
-                k += 1
-                r.generated.append(tok)
-                reason = None
-                if len(r.generated) >= r.params.max_tokens:
-                    reason = "max_tokens"
-                elif self.eos_token_id is not None and tok == self.eos_token_id:
-                    reason = "eos"
-                events.append(TokenEvent(r.req_id, tok, reason is not None, reason))
-                if reason:
-                    self._retire(r)
+                r.pending += 1
         # whoever ran goes to the back (src/scheduler/scheduler.cpp:600-615)
-        keep = [rid for rid in self.order if rid not in ran and rid in self.active]
-        self.order = keep + [rid for rid in ran if rid in self.active]
+        keep = [rid for rid in self.order if rid not in ran]
+        self.order = keep + ran
+        previous, self._inflight = self._inflight, ((reqs, handle) if reqs else None)
+        if previous is not None:
+            self._read(previous, events)
+        if not self.run_ahead:
+            self._resolve(events)
         return events
+
+    def _resolve(self, events: List[TokenEvent]) -> None:
+        """Reads the tokens of the step in flight, if there is one."""
+        previous, self._inflight = self._inflight, None
+        if previous is not None:
+            self._read(previous, events)
+
+    def _read(self, record, events: List[TokenEvent]) -> None:
+        reqs, handle = record
+        for r, tok in zip(reqs, handle.tokens()):
+            if r.finished:
+                continue  # it ended while this step was in flight; the token is dropped
+            tok = int(tok)
+            r.pending -= 1
+            r.generated.append(tok)
+            reason = None
+            if len(r.generated) >= r.params.max_tokens:
+                reason = "max_tokens"
+            elif self.eos_token_id is not None and tok == self.eos_token_id:
+                reason = "eos"
+            events.append(TokenEvent(r.req_id, tok, reason is not None, reason))
+            if reason:
+                self._retire(r)
 
     def _finish_exhausted(self, events: List[TokenEvent]) -> None:
         """A request whose next token would not fit the longest context ends (src/scheduler/scheduler.cpp:477-481)."""
         for r in list(self.active.values()):
+            if r.pending:
+                continue  # after its token has been read
             if r.prefill_done and self.engine.cache.get(r.req_id).ctx_len + 1 > self.engine.max_context:
                 events.append(TokenEvent(r.req_id, None, True, "max_context"))
                 self._retire(r)
@@ -296,6 +354,12 @@ class Scheduler:
         if r.req_id in self.order:
             self.order.remove(r.req_id)
 
+    def drain(self) -> List[TokenEvent]:
+        """Reads what is still in flight; the events that step() has not returned yet."""
+        events, self._carry = self._carry, []
+        self._resolve(events)
+        return events
+
     def run(self) -> Dict[Hashable, List[int]]:
         """Steps until nothing is left; returns the new tokens of every request."""
         out: Dict[Hashable, List[int]] = {}
@@ -305,3 +369,13 @@ class Scheduler:
                 if ev.token is not None:
                     out[ev.req_id].append(ev.token)
         return out
+
+
+class _Now:
+    """Tokens that are already on the host, with the interface of the engine's asynchronous result."""
+
+    def __init__(self, tokens):
+        self._tokens = tokens
+
+    def tokens(self):
+        return self._tokens

@@ -63,6 +63,8 @@ class StepContext:
         self.max_ctx = 0
         self.token_ids = self.positions = self.entry_of_token = self.logit_rows = None
         self.cu_q = self.pos0 = self.ctx_after = self.state_slot = None
+        self.row_slot = None        # request slot of each logits row
+        self.pending_tokens = None  # int32 [slots]: the token last sampled per request slot (token id -1 - s)
         self.groups: List[GroupStep] = []
         self.host = None         # StepLayout.HostView of the same arrays
 
@@ -84,6 +86,7 @@ class StepLayout:
         self.o_positions = region(max_tokens)
         self.o_entry_of_token = region(max_tokens)
         self.o_logit_rows = region(max_tokens)
+        self.o_row_slot = region(max_tokens)
         self.o_cu_q = region(max_entries + 1)
         self.o_pos0 = region(max_entries)
         self.o_ctx_after = region(max_entries)

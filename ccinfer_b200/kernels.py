@@ -33,7 +33,8 @@ _lock = threading.Lock()
 _libs = {}
 
 _SIGNATURES = {
-    "ccb_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ccb_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                         c_void_p],
     "ccb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "ccb_residual_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                              c_int, c_void_p, c_void_p],
@@ -69,7 +70,8 @@ _SIGNATURES = {
                              c_void_p],
     "ccb_gemm_tc_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_void_p, c_void_p],
-    "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                        c_void_p, c_int, c_void_p],
 }
 
 
@@ -154,13 +156,17 @@ def status_message(word: int) -> str:
 
 
 # ---------------------------------------------------------------------------------------------
-def embed_gather(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status=None) -> None:
-    """h[t, :] = float(table[ids[t], :]); h is the float residual stream [T, D]."""
-    _cuda(h, table, ids, status)
+def embed_gather(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status=None, pending=None) -> None:
+    """h[t, :] = float(table[ids[t], :]); h is the float residual stream [T, D].
+
+    With ``pending`` (int32 [slots]) an id of -1 - s stands for pending[s]: the token that sample_rows
+    last stored for request slot s."""
+    _cuda(h, table, ids, status, pending)
     T, D = h.shape
     assert h.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == D and ids.numel() >= T
-    _check(lib().ccb_embed_gather(_p(h), _p(table), _p(ids), T, D, table.shape[0], _dt(table), _p(status),
-                                  _stream()), "embed_gather")
+    assert pending is None or pending.dtype == torch.int32
+    _check(lib().ccb_embed_gather(_p(h), _p(table), _p(ids), T, D, table.shape[0], _dt(table), _p(pending),
+                                  0 if pending is None else pending.numel(), _p(status), _stream()), "embed_gather")
 
 
 def silu_mul(act: torch.Tensor, gate_up: torch.Tensor) -> None:
@@ -459,16 +465,21 @@ class CublasHandle:
             self._h = c_void_p()
 
 
-def sample_rows(logits, tokens, temperature=None, seed=None, out_index=None) -> None:
+def sample_rows(logits, tokens, temperature=None, seed=None, out_index=None, slot_of_row=None, by_slot=None) -> None:
     """tokens[r] = greedy or temperature draw of logits[r, :] (float), per-row parameters.
 
     temperature float [R] (<= 0 greedy), seed uint32-valued int32/int64 [R] taken
     as 32 bits, out_index int32 [R].  temperature None = greedy for all rows.
+    With ``slot_of_row`` (int32 [R]) the token of row r is also stored in by_slot[slot_of_row[r]]
+    (rows with a slot outside by_slot are skipped).
     """
-    _cuda(tokens, temperature, seed, out_index)
+    _cuda(tokens, temperature, seed, out_index, slot_of_row, by_slot)
+    assert slot_of_row is None or (slot_of_row.dtype == torch.int32 and by_slot.dtype == torch.int32
+                                   and slot_of_row.numel() >= logits.shape[0])
     R, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and tokens.dtype == torch.int32
     assert temperature is None or (temperature.dtype == torch.float32 and seed.dtype == torch.int32
                                    and out_index.dtype == torch.int32)
     _check(lib().ccb_sample_rows(_p(logits), logits.stride(0), _p(tokens), _p(temperature), _p(seed),
-                                 _p(out_index), R, V, _stream()), "sample_rows")
+                                 _p(out_index), R, V, _p(slot_of_row), _p(by_slot),
+                                 0 if by_slot is None else by_slot.numel(), _stream()), "sample_rows")

@@ -33,7 +33,8 @@ class LLM:
         self.engine = engine
         self.scheduler = Scheduler(engine, prefill_chunk_size=prefill_chunk_size,
                                    max_tokens_per_step=min(max_tokens_per_step, engine.options.max_tokens_per_step),
-                                   max_running=max_running, eos_token_id=eos_token_id)
+                                   max_running=max_running, eos_token_id=eos_token_id,
+                                   run_ahead=hasattr(engine, "sample_async"))
         self._next_id = 0
 
     def generate(self, prompts: Sequence[Sequence[int]],

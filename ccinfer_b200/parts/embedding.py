@@ -31,7 +31,8 @@ class TokenEmbedding(Part):
     def forward(self, step) -> Residual:
         rt = self.rt
         h = rt.scratch.get("residual", (rt.max_tokens, self.hidden), torch.float32)[:step.n_tokens]
-        kernels.embed_gather(h, self.table, step.token_ids, status=rt.status)
+        kernels.embed_gather(h, self.table, step.token_ids, status=rt.status,
+                             pending=getattr(step, "pending_tokens", None))
         return Residual(h)
 
 

@@ -77,6 +77,48 @@ def test_pages_run_out_during_generation(model_b):
     llm.engine.cache.check_consistency()
 
 
+def test_running_ahead_reads_tokens_a_step_late_and_changes_none(model_b):
+    """The entry point launches a step before it reads the tokens of the step before (they stay on the
+    device for the next embedding).  Same tokens as a scheduler that waits for every step, also when a
+    request stops at an end-of-sequence token while its next step is already in flight."""
+    from ccinfer_b200 import LLM, SamplingParams
+    from ccinfer_b200.engine.engine import PENDING, StepEntry
+    from ccinfer_b200.engine.scheduler import Scheduler
+    from ccinfer_b200.errors import InvalidArgument
+    d, cfg, w, page = model_b
+    prompts = _prompts(cfg, [9, 30, 5], 4)
+    sp = [SamplingParams(max_tokens=14, temperature=0.5, seed=3), SamplingParams(max_tokens=16),
+          SamplingParams(max_tokens=11)]
+    want = [plain.generate(cfg, w, p, s.max_tokens, s.temperature, s.seed) for p, s in zip(prompts, sp)]
+    eos = want[1][7]
+    stop = [t[:t.index(eos) + 1] if eos in t else t for t in want]
+    for eos_id, expect in ((None, want), (eos, stop)):
+        llm = LLM(d, dtype="float32", page_size=page, kv_tokens=512, prefill_chunk_size=8, max_requests=4,
+                  max_tokens_per_step=64, eos_token_id=eos_id)
+        assert llm.scheduler.run_ahead
+        assert llm.generate(prompts, sp) == expect
+        waits = Scheduler(llm.engine, prefill_chunk_size=8, max_tokens_per_step=64, eos_token_id=eos_id)
+        for i, (p, s) in enumerate(zip(prompts, sp)):
+            waits.submit(i, p, s)
+        out = waits.run()
+        assert [out[i] for i in range(3)] == expect
+        assert all(p.used_pages == 0 for p in llm.engine.cache.pools)
+    # PENDING stands alone and needs a token drawn for the request
+    eng = llm.engine
+    eng.open_request("z")
+    with pytest.raises(InvalidArgument):
+        eng.step([StepEntry("z", [PENDING], [0])])
+    lg = eng.step([StepEntry("z", prompts[0], [len(prompts[0]) - 1])])
+    first = eng.sample_async(lg, [SamplingParams()], [0])
+    with pytest.raises(InvalidArgument):
+        eng.step([StepEntry("z", [PENDING, 3], [0])])
+    lg = eng.step([StepEntry("z", [PENDING], [0])])          # launched before the first token is read
+    second = eng.sample(lg, [SamplingParams()], [1])
+    assert first.tokens() + second == plain.generate(cfg, w, prompts[0], 2)
+    eng.close_request("z")
+    eng.check()
+
+
 def test_long_decoding_and_first_tokens(model_b):
     """A one-token prompt decoded far, every position compared; and the first tokens of a sequence."""
     from ccinfer_b200.engine.engine import Engine, EngineOptions

@@ -26,6 +26,9 @@ class FakeEngine:
         self.max_context = max_context or pages * page
         self.history = {}
         self.steps = []
+        self.pending = {}        # request -> token drawn by sample_async (what the device would hold)
+        self.reads = []          # number of steps launched when each result was read
+        self._last_want = []
 
     def open_request(self, rid):
         self.cache.open(rid)
@@ -34,6 +37,7 @@ class FakeEngine:
     def close_request(self, rid):
         self.cache.close(rid)
         del self.history[rid]
+        self.pending.pop(rid, None)
 
     def step(self, entries):
         self.steps.append([(e.req_id, list(e.tokens), list(e.want)) for e in entries])
@@ -47,10 +51,14 @@ class FakeEngine:
                 self.cache.rollback(rid)
             raise
         rows = []
+        self._last_want = [e.req_id for e in entries for _ in e.want]
         for e in entries:
             self.cache.commit(e.req_id)
             h = self.history[e.req_id]
             for i, t in enumerate(e.tokens):
+                if t == -1:  # PENDING: the token of the request's last sample_async
+                    assert len(e.tokens) == 1
+                    t = self.pending[e.req_id]
                 h.append(t)
                 if i in e.want:
                     rows.append(hashlib.sha256(repr(h).encode()).hexdigest())
@@ -63,6 +71,22 @@ class FakeEngine:
             key = row if p.temperature <= 0 else f"{row}:{p.seed}:{i}:{p.temperature}"
             out.append(int(hashlib.sha256(key.encode()).hexdigest(), 16) % 1000)
         return out
+
+
+    def sample_async(self, logits, params, out_index):
+        tokens = self.sample(logits, params, out_index)
+        for rid, t in zip(self._last_want, tokens):
+            self.pending[rid] = t
+        return _Later(self, tokens)
+
+
+class _Later:
+    def __init__(self, eng, tokens):
+        self._eng, self._tokens = eng, tokens
+
+    def tokens(self):
+        self._eng.reads.append(len(self._eng.steps))
+        return self._tokens
 
 
 class _Rows:
@@ -207,3 +231,57 @@ def test_a_request_that_cannot_fit_alone_fails_loudly():
     s.submit("a", _prompt(10), SamplingParams(max_tokens=20))
     with pytest.raises(KVBlockExhausted):
         s.run()
+
+
+def _workload(s):
+    s.submit("a", _prompt(9, 1), SamplingParams(max_tokens=14, temperature=0.5, seed=3))
+    s.submit("b", _prompt(11, 2), SamplingParams(max_tokens=1))
+    s.submit("c", _prompt(30, 3), SamplingParams(max_tokens=16))
+    s.submit("d", _prompt(5, 4), SamplingParams(max_tokens=40))   # ends at the context limit
+
+
+@pytest.mark.parametrize("pages,eos", [(64, False), (64, True), (12, False), (12, True)])
+def test_running_ahead_changes_no_token(pages, eos):
+    """One step in flight: same tokens, same reasons, also with too few pages and with an end-of-sequence stop."""
+    def run(ahead, eos_id):
+        eng = FakeEngine(pages=pages, page=4, max_context=40)
+        s = Scheduler(eng, prefill_chunk_size=8, run_ahead=ahead, eos_token_id=eos_id)
+        _workload(s)
+        out, reasons = {}, {}
+        while s.has_work():
+            for ev in s.step():
+                if ev.token is not None:
+                    out.setdefault(ev.req_id, []).append(ev.token)
+                if ev.finished:
+                    reasons[ev.req_id] = ev.reason
+        assert all(p.used_pages == 0 for p in eng.cache.pools) and eng.cache.slots.free_slots == 8
+        return out, reasons, s, eng
+
+    base, _, _, _ = run(False, None)
+    eos_id = base["c"][7] if eos else None
+    calm, calm_reasons, s0, _ = run(False, eos_id)
+    ahead, ahead_reasons, s1, eng = run(True, eos_id)
+    assert ahead == calm and ahead_reasons == calm_reasons
+    assert calm_reasons["d"] == "max_context" and calm_reasons["b"] == "max_tokens"
+    if eos:
+        assert calm_reasons["c"] == "eos" and len(calm["c"]) == 8
+    if pages == 12:
+        assert s1.preemptions > 0
+    # results were read after the next step had been launched, except where nothing could be launched
+    late = sum(1 for k, n in enumerate(eng.reads) if n > k + 1)
+    assert late >= len(eng.reads) // 2
+
+
+def test_cancel_while_a_step_is_in_flight():
+    eng = FakeEngine()
+    s = Scheduler(eng, run_ahead=True)
+    s.submit("a", _prompt(5), SamplingParams(max_tokens=10))
+    s.submit("b", _prompt(6, 9), SamplingParams(max_tokens=10))
+    assert s.step() == []            # the first step's tokens are still in flight
+    assert s.cancel("a")
+    events = []
+    while s.has_work():
+        events += s.step()
+    assert [e.req_id for e in events if e.req_id == "a"] == ["a"]   # the token that was in flight, no more
+    assert len([e for e in events if e.req_id == "b" and e.token is not None]) == 10
+    assert all(p.used_pages == 0 for p in eng.cache.pools)
