@@ -70,12 +70,13 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // before it touches memory that another kernel may have written.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// Kernels without weights to prefetch: let the successor start at once (only the products are launched
-// with the attribute: their blocks then stream the first weight tiles while this kernel runs), then wait
-// for the predecessor.
+// Kernels without weights to prefetch: wait for the predecessor, then let the successor start (a product
+// then streams its first weight tiles while this kernel runs).  The order matters: a kernel that let its
+// successor in BEFORE its predecessor had finished would put three kernels on the device at once, and a
+// product's blocks, resident but waiting, would keep the predecessor's last blocks from being scheduled.
 __device__ __forceinline__ void pdl_begin() {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
 }
 
 __device__ __forceinline__ void set_status(int* status, int bit) {

@@ -57,7 +57,7 @@ template <> __device__ __forceinline__ float silu<float>(float g) { return g / (
 template <> __device__ __forceinline__ float silu<__nv_bfloat16>(float g) { return g / (1.f + __expf(-g)); }
 
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ act, const T* __restrict__ gu, int F, size_t total) {
+__global__ void silu_mul_kernel(T* __restrict__ act, const T* __restrict__ gu, int F, int B, size_t total) {
   ccb::pdl_begin();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -65,15 +65,16 @@ __global__ void silu_mul_kernel(T* __restrict__ act, const T* __restrict__ gu, i
     const size_t t = i / F;
     const int f = (int)(i - t * F);
     const T* row = gu + t * 2 * (size_t)F;
-    const float g = to_f32(row[f]);
-    const float u = to_f32(row[F + f]);
+    const int gi = (f / B) * 2 * B + f % B;  // B gate columns, then the B up columns of the same channels
+    const float g = to_f32(row[gi]);
+    const float u = to_f32(row[gi + B]);
     act[i] = from_f32<T>(silu<T>(g) * u);
   }
 }
 
 // bf16, F even: two elements per thread
 __global__ void silu_mul_bf16x2_kernel(__nv_bfloat162* __restrict__ act, const __nv_bfloat162* __restrict__ gu,
-                                       int F2, size_t total2) {
+                                       int F2, int B2, size_t total2) {
   ccb::pdl_begin();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -81,14 +82,16 @@ __global__ void silu_mul_bf16x2_kernel(__nv_bfloat162* __restrict__ act, const _
     const size_t t = i / F2;
     const int f = (int)(i - t * F2);
     const __nv_bfloat162* row = gu + t * 2 * (size_t)F2;
-    const float2 g = __bfloat1622float2(row[f]);
-    const float2 u = __bfloat1622float2(row[F2 + f]);
+    const int gi = (f / B2) * 2 * B2 + f % B2;
+    const float2 g = __bfloat1622float2(row[gi]);
+    const float2 u = __bfloat1622float2(row[gi + B2]);
     act[i] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
   }
 }
 
 // bf16, F a multiple of 8: eight elements (16 bytes) per thread and access
-__global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ act, const uint4* __restrict__ gu, int F8, size_t total8) {
+__global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ act, const uint4* __restrict__ gu, int F8, int B8,
+                                       size_t total8) {
   ccb::pdl_begin();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -96,7 +99,8 @@ __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ act, const uint4* __r
     const size_t t = i / F8;
     const int f = (int)(i - t * F8);
     const uint4* row = gu + t * 2 * (size_t)F8;
-    const uint4 g = row[f], u = row[F8 + f];
+    const int gi = (f / B8) * 2 * B8 + f % B8;
+    const uint4 g = row[gi], u = row[gi + B8];
     const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
     const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
     uint4 o;
@@ -110,30 +114,35 @@ __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ act, const uint4* __r
   }
 }
 
-CCB_API int ccb_silu_mul(void* act, const void* gate_up, int T_, int F, int dtype, cudaStream_t stream) {
+// gate_up[t, :] holds the 2F columns either as [all gate | all up] (block = 0) or in blocks: `block` gate
+// columns followed by the `block` up columns of the same channels (F a multiple of block).
+CCB_API int ccb_silu_mul(void* act, const void* gate_up, int T_, int F, int block, int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
-  if (F <= 0) return CCB_REFUSE_SIZE;
+  if (F <= 0 || block < 0 || (block > 0 && F % block != 0)) return CCB_REFUSE_SIZE;
+  const int B = block == 0 ? F : block;
   const size_t total = (size_t)T_ * F;
   const int threads = 256;
-  if (dtype == CCB_BF16 && (F % 8) == 0 && ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(gate_up)) & 15) == 0) {
+  if (dtype == CCB_BF16 && (F % 8) == 0 && (B % 8) == 0 && ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(gate_up)) & 15) == 0) {
     const size_t total8 = total / 8;
     const size_t want = (total8 + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
-    ccb_launch(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (uint4*)act, (const uint4*)gate_up, F / 8, total8);
+    ccb_launch(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (uint4*)act, (const uint4*)gate_up, F / 8, B / 8,
+               total8);
     return ccb_launch_status();
   }
-  if (dtype == CCB_BF16 && (F % 2) == 0) {
+  if (dtype == CCB_BF16 && (F % 2) == 0 && (B % 2) == 0) {
     const size_t total2 = total / 2;
     const int blocks = (int)((total2 + threads - 1) / threads < 148 * 16 ? (total2 + threads - 1) / threads : 148 * 16);
     ccb_launch(silu_mul_bf16x2_kernel, blocks, threads, 0, stream, (__nv_bfloat162*)act, (const __nv_bfloat162*)gate_up,
-                                                            F / 2, total2);
+               F / 2, B / 2, total2);
     return ccb_launch_status();
   }
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == CCB_F32)
-    ccb_launch(silu_mul_kernel<float>, blocks, threads, 0, stream, (float*)act, (const float*)gate_up, F, total);
+    ccb_launch(silu_mul_kernel<float>, blocks, threads, 0, stream, (float*)act, (const float*)gate_up, F, B, total);
   else if (dtype == CCB_BF16)
-    ccb_launch(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)act, (const __nv_bfloat16*)gate_up, F, total);
+    ccb_launch(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)act, (const __nv_bfloat16*)gate_up, F, B,
+               total);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();

@@ -71,6 +71,7 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
     }
   }
   pdl_wait();
+  pdl_trigger();
   for (; kb + U <= kb1; kb += U) {
     uint4 x[U][NB];
 #pragma unroll
@@ -107,7 +108,6 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
       mma_bf16_16816(c[nb], fb, x.z, x.w);
     }
   }
-  pdl_trigger();
   // c[nb]: (feature gid, tokens 8 nb + 2 tig, + 1), (feature gid + 8, same tokens)
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {

@@ -76,7 +76,7 @@ template <int BN, int STAGES, bool SWAP, typename TOut>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TOut* __restrict__ C,
                int ldc, int rowsA, int rowsB, int K, int splits, float* __restrict__ partial,
-               int* __restrict__ counters, int* status) {
+               int* __restrict__ counters, int swiglu, int* status) {
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   extern __shared__ uint8_t smem_raw[];
@@ -127,6 +127,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tma_load_2d(s32(sB + i * B_STAGE_BYTES), &tmB, (kb0 + i) * BK, tileB * BN, full0 + 8 * i);
       }
       pdl_wait();
+      pdl_trigger();
       for (int i = 0; i < pre; ++i) {
         if (SWAP)
           tma_load_2d(s32(sB + i * B_STAGE_BYTES), &tmB, (kb0 + i) * BK, tileB * BN, full0 + 8 * i);
@@ -168,7 +169,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int row = q * 32 + lane;
     const bool ok = mbar_wait(tfull, 0);
     if (!ok && lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
-    pdl_trigger();  // the main loop is over: the next kernel may start its prologue
     tc_fence_after();
     const int ga = tileA * BM + row;  // row of the A-side matrix
     if (ok) {
@@ -181,6 +181,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_wait_ld();
           const int n_valid = min(16, rowsB - (tileB * BN + c0));
           if (ga < rowsA && n_valid > 0) store16<TOut>(crow + c0, v, n_valid);
+        }
+      } else if (BN == 16 && swiglu) {
+        // The weight rows come in blocks of 64 gate rows followed by the 64 up rows of the same channels:
+        // lanes 0..63 of this tile hold gate, lanes 64..127 up.  The up half goes through shared memory
+        // (the stages are idle: every product has completed), the gate half computes silu(g) * u and
+        // writes C[token, 64 tileA + lane]: the activation, without a round trip of gate|up through memory.
+        float* xch = reinterpret_cast<float*>(sA);  // [64][17]
+        uint32_t v[16];
+        tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16), v);
+        tc_wait_ld();
+        if (q >= 2) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) xch[(row - 64) * 17 + j] = __uint_as_float(v[j]);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (q < 2 && tileA * BM + 64 + row < rowsA) {
+          const int ch = tileA * 64 + row;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < rowsB) {
+              const float g = __uint_as_float(v[j]), u = xch[row * 17 + j];
+              C[(size_t)j * ldc + ch] = from_f32<TOut>(g / (1.f + __expf(-g)) * u);
+            }
+          }
         }
       } else if (splits == 1) {
 #pragma unroll 1
@@ -211,38 +235,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
         }
-        __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         if (threadIdx.x == 64) {
+          __threadfence();  // cumulative: the whole block's partial sums are visible before its count is
           const int old = atomicAdd(&counters[tileA * gridDim.y + tileB], 1);
           *last_flag = (old == splits - 1) ? 1 : 0;
           if (old == splits - 1) counters[tileA * gridDim.y + tileB] = 0;  // ready for the next launch
+          __threadfence();
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
-          __threadfence();
-          if (ga < rowsA) {
-            // all loads of a group of tokens are issued before the first sum: the slices are added in
-            // ascending order, but nobody waits for one load at a time
-            constexpr int TG = 4, SMAX = 16;
-            const int t_end = min(rowsB, tileB * BN + BN);
-            for (int t0 = tileB * BN; t0 < t_end; t0 += TG) {
-              float v[TG][SMAX];
+          const int t_begin = tileB * BN, t_end = min(rowsB, tileB * BN + BN);
+          const size_t slice = (size_t)rowsB * rowsA;
+          if ((rowsA & 3) == 0 && (ldc & 3) == 0) {
+            // a warp per token, a lane per four features: the slices of a token arrive as 16-byte loads
+            // that are all in flight at once, and are added in ascending order (a fixed order)
+            const int f = tileA * BM + 4 * lane;
+            if (f < rowsA) {  // rowsA % 4 == 0: the four features are all inside
+#pragma unroll 2
+              for (int t = t_begin + q; t < t_end; t += 4) {
+                const float* src = partial + (size_t)t * rowsA + f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                for (int s0 = 0; s0 < splits; s0 += 8) {
+                  float4 v[8];
 #pragma unroll
-              for (int i = 0; i < TG; ++i)
+                  for (int s = 0; s < 8; ++s)
+                    v[s] = s0 + s < splits ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s0 + s) * slice))
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                for (int s = 0; s < SMAX; ++s)
-                  v[i][s] = (t0 + i < t_end && s < splits)
-                                ? __ldcg(&partial[((size_t)s * rowsB + t0 + i) * rowsA + ga]) : 0.f;
-#pragma unroll
-              for (int i = 0; i < TG; ++i) {
-                if (t0 + i < t_end) {
-                  float acc = 0.f;
-#pragma unroll
-                  for (int s = 0; s < SMAX; ++s) acc += v[i][s];  // slices beyond `splits` are exact zeros
-                  C[(size_t)(t0 + i) * ldc + ga] = from_f32<TOut>(acc);
+                  for (int s = 0; s < 8; ++s) {  // slices beyond `splits` are exact zeros
+                    acc.x += v[s].x;
+                    acc.y += v[s].y;
+                    acc.z += v[s].z;
+                    acc.w += v[s].w;
+                  }
+                }
+                TOut* dst = C + (size_t)t * ldc + f;
+                if constexpr (sizeof(TOut) == 4) {
+                  *reinterpret_cast<float4*>(dst) = acc;
+                } else {
+                  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+                  const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+                  uint2 pk;
+                  pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                  pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                  *reinterpret_cast<uint2*>(dst) = pk;
                 }
               }
+            }
+          } else if (ga < rowsA) {  // odd widths: a thread per feature
+#pragma unroll 1
+            for (int t = t_begin; t < t_end; ++t) {
+              float acc = 0.f;
+              for (int s = 0; s < splits; ++s) acc += __ldcg(&partial[(size_t)s * slice + (size_t)t * rowsA + ga]);
+              C[(size_t)t * ldc + ga] = from_f32<TOut>(acc);
             }
           }
         }
@@ -316,7 +363,7 @@ bool tensor_map(const void* ptr, int rows, int K, int ld, int box_rows, CUtensor
 
 template <int BN, int STAGES, bool SWAP, typename TOut>
 int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, int rowsA, int rowsB, int K,
-              int splits, float* partial, int* counters, int* status, cudaStream_t stream) {
+              int splits, float* partial, int* counters, int* status, cudaStream_t stream, int swiglu = 0) {
   constexpr size_t smem = (size_t)STAGES * (A_STAGE_BYTES + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -327,7 +374,7 @@ int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, 
   }
   dim3 grid((rowsA + BM - 1) / BM, (rowsB + BN - 1) / BN, splits);
   ccb_launch_ex(true, gemm_tc_kernel<BN, STAGES, SWAP, TOut>, grid, kThreadsTc, smem, stream, 
-      tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, status);
+      tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, swiglu, status);
   return ccb_launch_status();
 }
 
@@ -371,4 +418,21 @@ CCB_API int ccb_gemm_tc_bf16(void* C, const void* A, const void* W, int M, int N
   if (out_dtype == CCB_F32)
     return dispatch<float>(C, A, W, M, N, K, lda, ldw, ldc, splits, partial, counters, status, stream);
   return dispatch<__nv_bfloat16>(C, A, W, M, N, K, lda, ldw, ldc, splits, partial, counters, status, stream);
+}
+
+// act[M, F] = silu(A W_gate^T) * (A W_up^T) in one kernel, for M <= 16 tokens.  W [2F, K] holds the rows in
+// blocks: 64 gate rows, then the 64 up rows of the same channels (F a multiple of 64), so that one 128-row
+// tile of the tensor-core product owns matching gate and up channels.  The products are accumulated in
+// float and the activation is rounded once (7QiC/ccInfer rounds gate and up to bfloat16 first:
+// src/model/qwen3/qwen3_model.cpp:325-370, src/kernel/mlp/silu_mul.cu:24-28).
+CCB_API int ccb_gemm_tc_swiglu_bf16(void* act, const void* A, const void* W, int M, int F, int K, int lda, int ldw,
+                                    int ld_act, int* status, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return 0;
+  if (M > 16 || (F & 63)) return CCB_REFUSE_SIZE;
+  if (K <= 0 || (K & 7) || lda < K || ldw < K || ld_act < F || (lda & 7) || (ldw & 7) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    return CCB_REFUSE_SIZE;
+  CUtensorMap tmW, tmX;
+  if (!tensor_map(W, 2 * F, K, ldw, BM, &tmW) || !tensor_map(A, M, K, lda, 16, &tmX)) return CCB_REFUSE_ARG;
+  return launch_tc<16, 6, true, __nv_bfloat16>(tmW, tmX, act, ld_act, 2 * F, M, K, 1, nullptr, nullptr, status, stream, 1);
 }

@@ -85,6 +85,23 @@ class Runtime:
         self.cublas.gemm_bf16(out, x, w)
         return out
 
+    def gated_up(self, act: torch.Tensor, x: torch.Tensor, w: torch.Tensor, block: int) -> torch.Tensor:
+        """act[M, F] = silu(x Wg^T) * (x Wu^T) for the merged weight w [2F, K] (``block``: see kernels.silu_mul).
+
+        A few tokens in bfloat16 with the blocked layout: one kernel (the activation is the product's
+        epilogue).  Otherwise the product into scratch and the activation kernel."""
+        M, K = x.shape
+        N = w.shape[0]
+        if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M <= kernels.SKINNY_MAX_ROWS
+                and kernels.gemm_tc_fits(K, x, w) and -(-N // 128) >= kernels.TC_TARGET_BLOCKS
+                and kernels.gemm_tc_splits(M, N, K) == 1):
+            kernels.gemm_tc_swiglu_bf16(act, x, w, self.status)
+            return act
+        gu = self.scratch.get("ffn_gate_up", (self.max_tokens, N), self.dtype)[:M]
+        self.linear(gu, x, w)
+        kernels.silu_mul(act, gu, block)
+        return act
+
     def check_status(self) -> None:
         """Reads the status word (synchronises) and raises if a kernel reported a bad index."""
         word = int(self.status.item())

@@ -35,7 +35,9 @@ _libs = {}
 _SIGNATURES = {
     "ccb_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
                          c_void_p],
-    "ccb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ccb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_gemm_tc_swiglu_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                c_void_p],
     "ccb_residual_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                              c_int, c_void_p, c_void_p],
     "ccb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -169,12 +171,35 @@ def embed_gather(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status
                                   0 if pending is None else pending.numel(), _p(status), _stream()), "embed_gather")
 
 
-def silu_mul(act: torch.Tensor, gate_up: torch.Tensor) -> None:
-    """act[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+def silu_mul(act: torch.Tensor, gate_up: torch.Tensor, block: int = 0) -> None:
+    """act[t, f] = silu(gate[t, f]) * up[t, f] for gate_up[t, :] = [all gate | all up] (block = 0) or in
+    blocks of ``block`` gate columns followed by the ``block`` up columns of the same channels."""
     _cuda(act, gate_up)
     T, F = act.shape
     assert gate_up.shape == (T, 2 * F) and act.dtype == gate_up.dtype
-    _check(lib().ccb_silu_mul(_p(act), _p(gate_up), T, F, _dt(act), _stream()), "silu_mul")
+    _check(lib().ccb_silu_mul(_p(act), _p(gate_up), T, F, int(block), _dt(act), _stream()), "silu_mul")
+
+
+SWIGLU_BLOCK = 64   # rows of gate, then of up, in a weight matrix laid out for gemm_tc_swiglu_bf16
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int) -> torch.Tensor:
+    """[2F, D]: ``block`` rows of gate, the ``block`` rows of up for the same channels, and so on."""
+    F, D = gate.shape
+    assert up.shape == (F, D) and F % block == 0
+    return torch.cat([gate.view(F // block, block, D), up.view(F // block, block, D)], dim=1).reshape(2 * F, D).contiguous()
+
+
+def gemm_tc_swiglu_bf16(act, a, w, status=None) -> None:
+    """act[M, F] = silu(a Wg^T) * (a Wu^T) in one tensor-core kernel; w [2F, K] interleaved in blocks of
+    SWIGLU_BLOCK rows (interleave_gate_up), M <= 16, F a multiple of 64."""
+    _cuda(act, a, w, status)
+    assert act.dtype == a.dtype == w.dtype == torch.bfloat16
+    M, K = a.shape
+    F = w.shape[0] // 2
+    assert w.shape == (2 * F, K) and act.shape == (M, F) and a.stride(1) == w.stride(1) == act.stride(1) == 1
+    _check(lib().ccb_gemm_tc_swiglu_bf16(_p(act), _p(a), _p(w), M, F, K, a.stride(0), w.stride(0), act.stride(0),
+                                         _p(status), _stream()), "gemm_tc_swiglu_bf16")
 
 
 def residual_rmsnorm(y, h, delta, w, eps: float, row_idx=None, n_rows=None, status=None) -> None:

@@ -93,6 +93,42 @@ def test_silu_mul(dtype, T, F):
     assert _rel(act, g / (1 + torch.exp(-g)) * u) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,F,block", [(3, 64, 64), (9, 192, 64), (2, 12288, 64), (5, 30, 6), (4, 21, 7)])
+def test_silu_mul_blocked_layout(dtype, T, F, block):
+    """Gate and up columns in blocks: `block` of gate, then the `block` of up for the same channels."""
+    k = _k()
+    gu, ref = _rand((T, 2 * F), DT[dtype], 7, 3.0)
+    g, u = ref[:, :F], ref[:, F:]
+    blocked = k.interleave_gate_up(gu[:, :F].T.contiguous(), gu[:, F:].T.contiguous(), block).T.contiguous()
+    act = torch.empty((T, F), dtype=DT[dtype], device="cuda")
+    k.silu_mul(act, blocked, block)
+    assert _rel(act, g / (1 + torch.exp(-g)) * u) <= TOL[dtype]
+    from ccinfer_b200.errors import Unsupported
+    with pytest.raises(Unsupported):
+        k.silu_mul(act, blocked, F + 1)
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 64, 64), (8, 192, 512), (16, 12288, 256), (5, 640, 4096), (13, 128, 96)])
+def test_gemm_tc_swiglu(M, F, K):
+    """silu(a Wg^T) * (a Wu^T) as the epilogue of the tensor-core product, against the plain formula."""
+    from ccinfer_b200.errors import Unsupported
+    k = _k()
+    a, a_ref = _rand((M, K), torch.bfloat16, 34)
+    wg, wg_ref = _rand((F, K), torch.bfloat16, 35)
+    wu, wu_ref = _rand((F, K), torch.bfloat16, 36)
+    w = k.interleave_gate_up(wg, wu, k.SWIGLU_BLOCK)
+    act = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.gemm_tc_swiglu_bf16(act, a, w, status)
+    assert int(status.item()) == 0
+    g, u = a_ref @ wg_ref.T, a_ref @ wu_ref.T
+    assert _rel(act, g / (1 + torch.exp(-g)) * u) <= 8e-3
+    with pytest.raises(Unsupported):  # more rows than the kernel takes
+        k.gemm_tc_swiglu_bf16(torch.empty((17, F), dtype=torch.bfloat16, device="cuda"),
+                              torch.zeros((17, K), dtype=torch.bfloat16, device="cuda"), w, status)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 17, 33), (5, 301, 80), (33, 130, 257), (70, 64, 12), (130, 500, 96)])
 def test_gemm_f32(M, N, K):
     a, a_ref = _rand((M, K), torch.float32, 8)
