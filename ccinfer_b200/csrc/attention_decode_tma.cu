@@ -39,8 +39,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                             const int* __restrict__ block_table, int bt_stride, int n_entries, int row0, int nq,
                             int nkv, int page_size, int page_shift, int num_pages, int window, float scale,
-                            int num_splits, int* status) {
-  ccb::pdl_begin();
+                            int num_splits, int* __restrict__ counters, int* status) {
+  // The kernel after this one is let in only when this one ends: a product that came in while the last
+  // blocks were still merging made the pair slower (measured), not faster.
+  ccb::pdl_wait();
   constexpr int NH = HD / 64;
   constexpr int KS = HD / 16;
   constexpr int TILE_BYTES = NH * kHalfBytes;        // one K or V tile
@@ -270,6 +272,57 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
       }
     }
   }
+  if (num_splits == 1 || counters == nullptr) return;  // without counters a second kernel merges the splits
+  // The block that arrives last at this (row, head group) merges the splits, in ascending order whichever
+  // block it is, so that no second kernel (and no gap before it) is needed.
+  __shared__ int last_flag;
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();  // cumulative: the whole block's partial results are visible before its count is
+    int* c = counters + (size_t)r * gridDim.y + blockIdx.y;
+    const int old = atomicAdd(c, 1);
+    last_flag = old == num_splits - 1;
+    if (last_flag) *c = 0;  // ready for the next launch
+    __threadfence();
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  float* f_s = reinterpret_cast<float*>(smem);  // [16 heads][splits]: each split's weight, then 1 / sum
+  float* inv_s = f_s + 16 * 64;
+  // a warp per head, a lane per split (two beyond 32): every load of the head is in flight at once
+  for (int hh = warp; hh < n_heads; hh += kThreads / 32) {
+    const size_t base = ((size_t)r * nq + h0 + hh) * num_splits;
+    const int s0 = lane, s1 = lane + 32;
+    const float ma = s0 < num_splits ? __ldcg(&part_ml[(base + s0) * 2]) : -CUDART_INF_F;
+    const float mb = s1 < num_splits ? __ldcg(&part_ml[(base + s1) * 2]) : -CUDART_INF_F;
+    const float la = s0 < num_splits ? __ldcg(&part_ml[(base + s0) * 2 + 1]) : 0.f;
+    const float lb = s1 < num_splits ? __ldcg(&part_ml[(base + s1) * 2 + 1]) : 0.f;
+    const float mm = warp_max(fmaxf(ma, mb));
+    const float fa = (mm == -CUDART_INF_F || s0 >= num_splits) ? 0.f : __expf(ma - mm);
+    const float fb = (mm == -CUDART_INF_F || s1 >= num_splits) ? 0.f : __expf(mb - mm);
+    if (s0 < num_splits) f_s[hh * 64 + s0] = fa;
+    if (s1 < num_splits) f_s[hh * 64 + s1] = fb;
+    const float ll = warp_sum(la * fa + lb * fb);  // a butterfly: the same order whichever block merges
+    if (lane == 0) inv_s[hh] = ll > 0.f ? 1.f / ll : 0.f;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < n_heads * (HD / 4); idx += kThreads) {
+    const int row = idx / (HD / 4), d = 4 * (idx - row * (HD / 4));
+    const size_t base = ((size_t)r * nq + h0 + row) * num_splits;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int s = 0; s < num_splits; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(&part_acc[(base + s) * HD + d]));
+      const float f = f_s[row * 64 + s];
+      a.x += v.x * f; a.y += v.y * f; a.z += v.z * f; a.w += v.w * f;
+    }
+    const float inv = inv_s[row];
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * inv, a.y * inv), hi = __floats2bfloat162_rn(a.z * inv, a.w * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(&out[((size_t)t * nq + h0 + row) * HD + d]) = pk;
+  }
 }
 
 __global__ void attention_merge_bf16_kernel2(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_acc,
@@ -298,7 +351,7 @@ template <int HD>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_acc, float* part_ml,
            const int* positions, const int* entry_of_token, const int* block_table, int bt_stride, int n_entries,
            int row0, int n_rows, int nq, int nkv, int page_size, int num_pages, int window, float scale,
-           int num_splits, int* status, cudaStream_t stream) {
+           int num_splits, int* counters, int* status, cudaStream_t stream) {
   const int G = nq / nkv, gchunks = (G + 15) / 16;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -318,9 +371,9 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
   dim3 grid(n_rows, nkv * gchunks, num_splits);
   ccb_launch(attention_decode_tma_kernel<HD>, grid, kThreads, smem, stream, tmK, tmV, (const __nv_bfloat16*)q,
              (__nv_bfloat16*)out, part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries,
-             row0, nq, nkv, page_size, page_shift, num_pages, window, scale, num_splits, status);
+             row0, nq, nkv, page_size, page_shift, num_pages, window, scale, num_splits, counters, status);
   int rc = ccb_launch_status();
-  if (rc != 0 || num_splits == 1) return rc;
+  if (rc != 0 || num_splits == 1 || counters != nullptr) return rc;
   ccb_launch(attention_merge_bf16_kernel2, dim3(n_rows, nq), 128, 0, stream, (__nv_bfloat16*)out, part_acc, part_ml,
              row0, nq, HD, num_splits);
   return ccb_launch_status();
@@ -329,12 +382,15 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
 }  // namespace
 
 // As ccb_attention_decode_mma, for page sizes that are a power of two from 8 to 64 (others: CCB_REFUSE_SIZE).
+// `counters` (optional): n_rows * kv_heads * ceil(group / 16) ints that are zero before the first launch and
+// are left zero; with them the splits are merged by the attention kernel itself, without them by a second
+// kernel.
 CCB_API int ccb_attention_decode_tma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                      float* part_acc, float* part_ml, const int* positions,
                                      const int* entry_of_token, const int* block_table, int bt_stride,
                                      int n_entries, int row0, int n_rows, int nq, int nkv, int hd, int page_size,
-                                     int num_pages, int window, float scale, int num_splits, int* status,
-                                     cudaStream_t stream) {
+                                     int num_pages, int window, float scale, int num_splits, int* counters,
+                                     int* status, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || bt_stride <= 0 || num_splits <= 0 || num_splits > 64 ||
       page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0 ||
@@ -344,10 +400,10 @@ CCB_API int ccb_attention_decode_tma(const void* q, const void* k_cache, const v
   if (hd == 128)
     return launch<128>(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
                        bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale, num_splits,
-                       status, stream);
+                       counters, status, stream);
   if (hd == 64)
     return launch<64>(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
                       bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale, num_splits,
-                      status, stream);
+                      counters, status, stream);
   return CCB_REFUSE_SIZE;
 }

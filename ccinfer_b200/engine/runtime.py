@@ -57,6 +57,7 @@ class Runtime:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.cublas = kernels.CublasHandle(self.device) if dtype == torch.bfloat16 else None
         self.tc_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)  # split-K tile counters
+        self.merge_counters = torch.zeros(8192, dtype=torch.int32, device=self.device)  # attention split counters
 
     def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """out[M, N] = x[M, K] @ w[N, K]^T; out may be float for bfloat16 operands (the logits)."""

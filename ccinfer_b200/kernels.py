@@ -55,7 +55,7 @@ _SIGNATURES = {
                                  c_float, c_int, c_void_p, c_void_p],
     "ccb_attention_decode_tma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_float, c_int, c_void_p, c_void_p],
+                                 c_float, c_int, c_void_p, c_void_p, c_void_p],
     "ccb_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                   c_void_p],
@@ -340,10 +340,13 @@ def attention_decode_tma_fits(hd: int, page_size: int) -> bool:
 
 def attention_decode_tma(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
                          n_entries: int, row0: int, n_rows: int, window: int, scale: float, num_splits: int,
-                         status=None) -> None:
+                         status=None, merge_counters=None) -> None:
     """As attention_decode_mma, with keys and values loaded page by page through TMA boxes by a producer warp
-    (page size a power of two from 8 to 64)."""
-    _cuda(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status)
+    (page size a power of two from 8 to 64).
+
+    ``merge_counters`` (int32 zeros, left zero): with them the block that finishes last merges the splits
+    of its row and head group; without them (or where they are too few) a second kernel does."""
+    _cuda(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status, merge_counters)
     T, nq, hd = q.shape
     num_pages, nkv, page_size, hd2 = k_cache.shape
     assert hd2 == hd and out.shape == q.shape
@@ -352,12 +355,18 @@ def attention_decode_tma(q, k_cache, v_cache, out, part_acc, part_ml, positions,
     if num_splits > 1:
         assert part_acc.dtype == part_ml.dtype == torch.float32
         assert part_acc.numel() >= n_rows * nq * num_splits * hd and part_ml.numel() >= n_rows * nq * num_splits * 2
+    if merge_counters is not None:
+        groups = nkv * -(-(nq // nkv) // DECODE_MMA_HEADS_PER_BLOCK)
+        if num_splits == 1 or merge_counters.numel() < n_rows * groups:
+            merge_counters = None
+        else:
+            assert merge_counters.dtype == torch.int32
     _check(lib().ccb_attention_decode_tma(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml),
                                           _p(positions), _p(entry_of_token), _p(block_table),
                                           block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
-                                          num_pages, int(window), float(scale), num_splits, _p(status),
-                                          _stream()), "attention_decode_tma")
-    if num_splits > 1:
+                                          num_pages, int(window), float(scale), num_splits, _p(merge_counters),
+                                          _p(status), _stream()), "attention_decode_tma")
+    if num_splits > 1 and merge_counters is None:
         counters.own += 1  # the merge kernel
 
 

@@ -85,12 +85,17 @@ class GroupedQueryAttention(Mixer):
             splits, n_acc, n_ml = kernels.attention_split_plan(n_rows, self.nq, self.nkv, self.hd, per_block)
             part_acc = rt.scratch.get("attn_part_acc", (n_acc,), torch.float32)
             part_ml = rt.scratch.get("attn_part_ml", (n_ml,), torch.float32)
+            args = (q, cache.k, cache.v, o, part_acc, part_ml, step.positions, step.entry_of_token, g.block_table,
+                    step.n_entries, 0, n_rows, self.window or 0, self.scale, splits)
             if mma and kernels.attention_decode_tma_fits(self.hd, g.page_size):
-                fn = kernels.attention_decode_tma     # pages arrive as TMA boxes
+                # pages arrive as TMA boxes.  Many splits (few rows, long contexts): the last block of a row
+                # and head group merges them; few splits: a second small kernel does, during which the
+                # output projection already loads its first weights (measured: 2 us a layer either way)
+                kernels.attention_decode_tma(*args, status=rt.status,
+                                             merge_counters=rt.merge_counters if splits >= 8 else None)
             else:
                 fn = kernels.attention_decode_mma if mma else kernels.attention_split
-            fn(q, cache.k, cache.v, o, part_acc, part_ml, step.positions, step.entry_of_token, g.block_table,
-               step.n_entries, 0, n_rows, self.window or 0, self.scale, splits, status=rt.status)
+                fn(*args, status=rt.status)
         if mma and step.n_entries > step.n_single:
             # long portions: 128-token tiles on tcgen05 with the accumulators in tensor memory; short ones
             # (and page sizes a TMA box cannot take): 64-token tiles on mma.sync

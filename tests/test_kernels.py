@@ -383,6 +383,27 @@ def test_attention_decode_tma(case, splits):
         assert torch.equal(part[1:-1], out[1:-1]) and float(part[0].abs().max()) == 0 == float(part[-1].abs().max())
 
 
+@pytest.mark.parametrize("splits", [2, 5, 64])
+@pytest.mark.parametrize("case", [c for c in MMA_CASES if c[5] >= 8])
+def test_attention_decode_tma_merges_in_the_last_block(case, splits):
+    """With counters the attention kernel merges its own splits: same numbers as the second kernel's, twice
+    in a row (the counters are left at zero)."""
+    import functools
+    ctx, new, nq, nkv, hd, P, window = case
+    q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", ctx, new, nq, nkv, hd, P, seed=hd + len(ctx),
+                                               window=window)
+    two = _run_split(q, kc, vc, pos, eot, bt, len(ctx), window, hd, splits, fn=_k().attention_decode_tma)
+    counters = torch.zeros(q.shape[0] * nq, dtype=torch.int32, device="cuda")
+    own0 = _k().counters.own
+    for _ in range(2):
+        one = _run_split(q, kc, vc, pos, eot, bt, len(ctx), window, hd, splits,
+                         fn=functools.partial(_k().attention_decode_tma, merge_counters=counters))
+        assert _rel(one, ref) <= 1.5e-2
+        assert _rel(one, two.double()) <= 1e-2   # the merge's arithmetic differs only in its rounding
+        assert int(counters.abs().sum().item()) == 0
+    assert _k().counters.own - own0 == 2  # one launch each
+
+
 @pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 257, 511, 598])
 def test_attention_decode_tma_reads_far_key(far_key):
     nq, nkv, hd, P = 8, 2, 128, 16
