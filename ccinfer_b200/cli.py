@@ -50,6 +50,8 @@ def main(argv=None) -> int:
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--kv-tokens", type=int, default=None, help="tokens the cache pool holds (default 16384)")
+    ap.add_argument("--kv-memory-fraction", type=float, default=None,
+                    help="instead of --kv-tokens: share of the free device memory that goes to the cache pool")
     ap.add_argument("--max-requests", type=int, default=64)
     ap.add_argument("--max-running", type=int, default=16)
     ap.add_argument("--max-tokens-per-step", type=int, default=4096)
@@ -84,7 +86,8 @@ def main(argv=None) -> int:
         from .engine.scheduler import SamplingParams
         from .llm import LLM
         llm = LLM(args.model_path, dtype=args.dtype, prefill_chunk_size=args.prefill_chunk_size,
-                  page_size=args.page_size, kv_tokens=args.kv_tokens, max_requests=args.max_requests,
+                  page_size=args.page_size, kv_tokens=args.kv_tokens,
+                  kv_memory_fraction=args.kv_memory_fraction, max_requests=args.max_requests,
                   max_tokens_per_step=args.max_tokens_per_step, max_context=args.max_context,
                   max_running=args.max_running, eos_token_id=args.eos_token_id)
         sp = SamplingParams(max_tokens=args.max_tokens, top_k=args.top_k, top_p=args.top_p,

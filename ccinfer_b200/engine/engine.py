@@ -60,6 +60,8 @@ class EngineOptions:
     device: str = "cuda:0"
     page_size: int = 16              # tokens per cache page (the reference's constant, src/cache/block.h:9)
     kv_tokens: Optional[int] = None  # tokens the cache pool of each group holds; default 1024 pages as the reference
+    kv_memory_fraction: Optional[float] = None  # instead of kv_tokens: this share of the memory that is free once
+                                                # the weights are on the device goes to the cache pools
     max_requests: int = 64           # live requests = state slots (src/worker/worker.h:102)
     max_tokens_per_step: int = 4096  # the reference's compute budget (src/scheduler/scheduler.cpp:25)
     max_context: Optional[int] = None  # longest request; default min(model limit, pool)
@@ -87,8 +89,22 @@ class Engine:
 
         # ---- cache groups, storage and state ----
         P = opt.page_size
-        kv_tokens = opt.kv_tokens if opt.kv_tokens is not None else 1024 * P
-        num_pages = max(1, -(-kv_tokens // P))
+        if opt.kv_tokens is not None and opt.kv_memory_fraction is not None:
+            raise InvalidArgument("give kv_tokens or kv_memory_fraction, not both")
+        if opt.kv_memory_fraction is not None:
+            if not (0.0 < opt.kv_memory_fraction <= 1.0):
+                raise InvalidArgument("kv_memory_fraction lies in (0, 1]")
+            elt = torch.empty((), dtype=self.dtype).element_size()
+            page_bytes = 0   # of one page in every pool: keys and values of every entry that keeps its own
+            for e in plan.order:
+                need = plan.layers[e.layer].mixer.cache_need()
+                if e.cache_of is None and need is not None:
+                    page_bytes += 2 * need.kv_heads * P * need.head_dim * elt
+            free_bytes = torch.cuda.mem_get_info(rt.device)[0]
+            num_pages = max(1, int(free_bytes * opt.kv_memory_fraction) // max(page_bytes, 1))
+        else:
+            kv_tokens = opt.kv_tokens if opt.kv_tokens is not None else 1024 * P
+            num_pages = max(1, -(-kv_tokens // P))
         limit = num_pages * P
         if plan.max_position is not None:
             limit = min(limit, plan.max_position)

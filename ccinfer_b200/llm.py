@@ -17,7 +17,8 @@ from .engine.scheduler import SamplingParams, Scheduler
 
 class LLM:
     def __init__(self, model_path: Optional[str] = None, dtype: str = "bfloat16", prefill_chunk_size: int = 512,
-                 page_size: int = 16, kv_tokens: Optional[int] = None, max_requests: int = 64,
+                 page_size: int = 16, kv_tokens: Optional[int] = None, kv_memory_fraction: Optional[float] = None,
+                 max_requests: int = 64,
                  max_tokens_per_step: int = 4096, max_context: Optional[int] = None, max_running: int = 16,
                  eos_token_id: Optional[int] = None, device: str = "cuda:0", use_graphs: bool = True,
                  engine: Optional[Engine] = None):
@@ -28,7 +29,8 @@ class LLM:
             if model_path is None:
                 raise ValueError("model_path (or an engine) is required")
             engine = Engine.from_model_dir(model_path, EngineOptions(
-                dtype=dtype, device=device, page_size=page_size, kv_tokens=kv_tokens, max_requests=max_requests,
+                dtype=dtype, device=device, page_size=page_size, kv_tokens=kv_tokens,
+                kv_memory_fraction=kv_memory_fraction, max_requests=max_requests,
                 max_tokens_per_step=max_tokens_per_step, max_context=max_context, use_graphs=use_graphs))
         self.engine = engine
         self.scheduler = Scheduler(engine, prefill_chunk_size=prefill_chunk_size,

@@ -27,6 +27,57 @@ from ..parts.base import TensorSpec
 from .safetensors_io import SafetensorsFile, write_safetensors
 
 WEIGHTS_FILE = "model.safetensors"
+INDEX_FILE = "model.safetensors.index.json"   # large checkpoints: {"weight_map": {tensor name: shard file}}
+
+
+class _Shards:
+    """Several safetensors files behind the interface of one (``entries``, ``tensor``, ``close``).
+
+    What the index promises is not trusted: the tensors are those the shard files really hold, so a name
+    the index lists but no shard has shows up as missing in the one error."""
+
+    def __init__(self, model_dir: str, index_path: str):
+        try:
+            with open(index_path) as f:
+                weight_map = json.load(f)["weight_map"]
+            shard_names = sorted(set(weight_map.values()))
+        except (OSError, ValueError, KeyError, AttributeError, TypeError) as e:
+            raise ModelLoadFailed(f"{index_path} is not a safetensors index (a JSON object with a weight_map): {e}")
+        self.files = []
+        self.entries: Dict[str, tuple] = {}
+        self._owner: Dict[str, SafetensorsFile] = {}
+        for shard in shard_names:
+            path = os.path.join(model_dir, shard)
+            if os.path.basename(shard) != shard or not os.path.isfile(path):
+                self.close()
+                raise ModelLoadFailed(f"{index_path} names the shard '{shard}', which is not a file of {model_dir}")
+            f = SafetensorsFile(path)
+            self.files.append(f)
+            for name, entry in f.entries.items():
+                if name in self._owner:
+                    self.close()
+                    raise ModelLoadFailed(f"tensor '{name}' is stored in more than one shard of {model_dir}")
+                self.entries[name] = entry
+                self._owner[name] = f
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self._owner[name].tensor(name)
+
+    def close(self) -> None:
+        for f in self.files:
+            f.close()
+
+
+def open_checkpoint(model_dir: str):
+    """The folder's weights: ``model.safetensors``, or the shards that ``model.safetensors.index.json`` names."""
+    path = os.path.join(model_dir, WEIGHTS_FILE)
+    if os.path.isfile(path):
+        return SafetensorsFile(path), path
+    index = os.path.join(model_dir, INDEX_FILE)
+    if os.path.isfile(index):
+        return _Shards(model_dir, index), index
+    raise ModelLoadFailed(f"{path} does not exist (the model folder holds config.json and {WEIGHTS_FILE}, "
+                          f"or {INDEX_FILE} with its shards)")
 
 
 def check_tensors(specs: List[TensorSpec], entries: Dict[str, tuple], where: str) -> None:
@@ -74,11 +125,12 @@ def open_weights(model_dir: str, specs: List[TensorSpec], device, compute_dtype,
     Names in ``shared`` (wanted by more than one part, like a tied head) are
     copied once and handed out again; every other call makes a fresh copy that
     the asking part owns."""
-    path = os.path.join(model_dir, WEIGHTS_FILE)
-    if not os.path.isfile(path):
-        raise ModelLoadFailed(f"{path} does not exist (the model folder holds config.json and {WEIGHTS_FILE})")
-    f = SafetensorsFile(path)
-    check_tensors(specs, f.entries, path)
+    f, path = open_checkpoint(model_dir)
+    try:
+        check_tensors(specs, f.entries, path)
+    except ModelLoadFailed:
+        f.close()
+        raise
     by_name = {s.name: s for s in specs}
     cache: Dict[str, torch.Tensor] = {}
 

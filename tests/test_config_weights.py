@@ -181,6 +181,42 @@ def test_loader_types_on_load(tmp_path):
     assert fetch("model.norm.weight") is not fetch("model.norm.weight")
 
 
+def test_sharded_checkpoint(tmp_path):
+    """Large checkpoints come as shards named by model.safetensors.index.json: same tensors, same one error."""
+    import json
+    cfg = tiny_configs.TINY_B
+    specs = _specs(cfg)
+    g = torch.Generator().manual_seed(1)
+    tensors = {s.name: torch.randn(s.shape, generator=g).bfloat16() for s in specs}
+    names = sorted(tensors)
+    d = tmp_path / "sharded"
+    d.mkdir()
+    shards = {"model-00001-of-00003.safetensors": names[0::3], "model-00002-of-00003.safetensors": names[1::3],
+              "model-00003-of-00003.safetensors": names[2::3]}
+    for fn, ns in shards.items():
+        write_safetensors(str(d / fn), {n: tensors[n] for n in ns})
+    index = {"metadata": {}, "weight_map": {n: fn for fn, ns in shards.items() for n in ns}}
+    (d / "model.safetensors.index.json").write_text(json.dumps(index))
+    fetch = open_weights(str(d), specs, "cpu", torch.bfloat16)
+    for n in names[:5] + names[-5:]:
+        spec = next(s for s in specs if s.name == n)
+        want = tensors[n].float() if spec.role == "vector" else tensors[n]
+        assert torch.equal(fetch(n), want)
+    fetch.close()
+    # a tensor that the index lists but no shard holds is missing; a shard that is not there is named
+    lost = names[4]
+    write_safetensors(str(d / "model-00002-of-00003.safetensors"), {n: tensors[n] for n in names[1::3] if n != lost})
+    with pytest.raises(ModelLoadFailed, match="missing tensors \\(1\\)") as ei:
+        open_weights(str(d), specs, "cpu", torch.bfloat16)
+    assert lost in str(ei.value)
+    (d / "model-00003-of-00003.safetensors").unlink()
+    with pytest.raises(ModelLoadFailed, match="model-00003-of-00003"):
+        open_weights(str(d), specs, "cpu", torch.bfloat16)
+    (d / "model.safetensors.index.json").write_text("[1, 2]")
+    with pytest.raises(ModelLoadFailed, match="weight_map"):
+        open_weights(str(d), specs, "cpu", torch.bfloat16)
+
+
 @pytest.mark.parametrize("damage", ["short", "header_len", "json", "offsets", "dtype", "missing_file"])
 def test_damaged_files(tmp_path, damage):
     d = tmp_path / "m"

@@ -119,6 +119,21 @@ def test_running_ahead_reads_tokens_a_step_late_and_changes_none(model_b):
     eng.check()
 
 
+def test_cache_pool_sized_from_free_memory(model_a):
+    """kv_memory_fraction: the pools take that share of what is free once the weights are loaded."""
+    from ccinfer_b200.engine.engine import Engine, EngineOptions
+    from ccinfer_b200.errors import InvalidArgument
+    d, cfg, w, page = model_a
+    free = torch.cuda.mem_get_info()[0]
+    eng = Engine.from_model_dir(d, EngineOptions(dtype="float32", page_size=page, kv_memory_fraction=0.01,
+                                                 max_requests=2, max_tokens_per_step=32, max_context=64))
+    per_page = cfg["num_hidden_layers"] * 2 * cfg["num_key_value_heads"] * page * cfg["head_dim"] * 4
+    pages = eng.cache.groups[0].num_pages
+    assert 0.8 * 0.01 * free / per_page <= pages <= 0.01 * free / per_page
+    with pytest.raises(InvalidArgument):
+        Engine.from_model_dir(d, EngineOptions(dtype="float32", kv_tokens=64, kv_memory_fraction=0.5))
+
+
 def test_long_decoding_and_first_tokens(model_b):
     """A one-token prompt decoded far, every position compared; and the first tokens of a sequence."""
     from ccinfer_b200.engine.engine import Engine, EngineOptions
