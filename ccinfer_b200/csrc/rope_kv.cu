@@ -214,6 +214,122 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
   }
 }
 
+// bfloat16 with 16-byte accesses: LPH lanes share a head (8 elements of each half per lane), so a warp works
+// on 32 / LPH heads at once.  Head sizes 16 * LPH with LPH a power of two (128 -> 8 lanes).
+template <int LPH>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
+                                    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                                    __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ positions,
+                                    const int* __restrict__ slot_map, const float* __restrict__ inv_freq,
+                                    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps, int nq,
+                                    int nkv, int page_size, int num_slots, int heads_per_block, int* status) {
+  ccb::pdl_begin();
+  constexpr int HD = 16 * LPH, HALF = 8 * LPH, HPW = 32 / LPH;
+  __shared__ float2 cs_table[HALF];  // (cos, sin) of this token's angles, shared by all heads of the block
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (inv_freq != nullptr) {
+    const float fpos_t = (float)positions[t];
+    for (int i = threadIdx.x; i < HALF; i += blockDim.x) {
+      float sn, cs;
+      sincosf(fpos_t * inv_freq[i], &sn, &cs);
+      cs_table[i] = make_float2(cs, sn);
+    }
+  }
+  __syncthreads();
+  const int sub = lane % LPH, i0 = 8 * sub;
+  const int head_end = min(nq + 2 * nkv, (int)(blockIdx.y + 1) * heads_per_block);
+  for (int head = blockIdx.y * heads_per_block + warp * HPW + lane / LPH; head < head_end; head += 4 * HPW) {
+    const __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)head * HD;
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    __nv_bfloat16* dst;
+    bool live = true;
+    if (is_q) {
+      dst = q_out + ((size_t)t * nq + head) * HD;
+    } else {
+      const int slot = slot_map[t];
+      live = slot >= 0 && slot < num_slots;
+      if (slot >= num_slots && sub == 0) set_status(status, CCB_ST_BAD_SLOT);
+      const int kvh = is_k ? head - nq : head - nq - nkv;
+      const int page = live ? slot / page_size : 0, off = live ? slot - page * page_size : 0;
+      dst = (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + off) * HD;
+    }
+    uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
+    if (live) {
+      ra = *reinterpret_cast<const uint4*>(src + i0);
+      rb = *reinterpret_cast<const uint4*>(src + i0 + HALF);
+    }
+    if (!is_q && !is_k) {
+      if (live) {
+        *reinterpret_cast<uint4*>(dst + i0) = ra;
+        *reinterpret_cast<uint4*>(dst + i0 + HALF) = rb;
+      }
+      continue;  // the lanes of a head take this branch together; the shuffles below name their lanes
+    }
+    float a[8], b[8];
+    {
+      const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&rb);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = __bfloat1622float2(pa[e]), fb = __bfloat1622float2(pb[e]);
+        a[2 * e] = fa.x; a[2 * e + 1] = fa.y;
+        b[2 * e] = fb.x; b[2 * e + 1] = fb.y;
+      }
+    }
+    const float* w = is_q ? q_w : k_w;
+    float inv = 1.f;
+    if (w != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += a[e] * a[e] + b[e] * b[e];
+      // the lanes of one head: a butterfly inside their group (other groups may be elsewhere in the loop)
+      const unsigned group_mask = LPH == 32 ? 0xffffffffu : (((1u << LPH) - 1u) << (lane - sub));
+#pragma unroll
+      for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(group_mask, ss, o);
+      inv = 1.0f / sqrtf(ss / (float)HD + eps);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (w != nullptr) {
+        a[e] = a[e] * inv * w[i0 + e];
+        b[e] = b[e] * inv * w[i0 + e + HALF];
+      }
+      if (inv_freq != nullptr) {
+        const float2 c = cs_table[i0 + e];
+        const float xa = a[e] * c.x - b[e] * c.y;
+        const float xb = b[e] * c.x + a[e] * c.y;
+        a[e] = xa;
+        b[e] = xb;
+      }
+    }
+    if (live) {
+      uint4 oa, ob;
+      __nv_bfloat162* qa = reinterpret_cast<__nv_bfloat162*>(&oa);
+      __nv_bfloat162* qb = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        qa[e] = __floats2bfloat162_rn(a[2 * e], a[2 * e + 1]);
+        qb[e] = __floats2bfloat162_rn(b[2 * e], b[2 * e + 1]);
+      }
+      *reinterpret_cast<uint4*>(dst + i0) = oa;
+      *reinterpret_cast<uint4*>(dst + i0 + HALF) = ob;
+    }
+  }
+}
+
+template <int LPH>
+static void launch_x8(dim3 grid, cudaStream_t stream, const void* qkv, int row_stride, void* q_out, void* k_cache,
+                      void* v_cache, const int* positions, const int* slot_map, const float* inv_freq,
+                      const float* q_w, const float* k_w, float eps, int nq, int nkv, int page_size, int num_slots,
+                      int hpb, int* status) {
+  ccb_launch(qk_norm_rope_kv_write_bf16x8_kernel<LPH>, grid, 128, 0, stream, (const __nv_bfloat16*)qkv, row_stride,
+             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, positions, slot_map, inv_freq,
+             q_w, k_w, eps, nq, nkv, page_size, num_slots, hpb, status);
+}
+
 CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_out, void* k_cache, void* v_cache,
                                       const int* positions, const int* slot_map, const float* inv_freq,
                                       const float* q_w, const float* k_w, float eps, int T_, int nq, int nkv,
@@ -232,6 +348,26 @@ CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_o
   // few tokens: many small blocks; many tokens: 16 heads a block, so the angles are computed 16x less often
   const int hpb = T_ <= 64 ? 4 : 16;
   dim3 vgrid(T_, (heads + hpb - 1) / hpb);
+  // bfloat16, many tokens, head sizes 32 .. 256 that are 16 x a power of two: 16-byte accesses
+  const bool x8 = dtype == CCB_BF16 && T_ > 64 && (hd == 32 || hd == 64 || hd == 128 || hd == 256) &&
+                  (row_stride % 8 == 0) &&
+                  ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                    reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+  if (x8) {
+    const int lph = hd / 16;
+    const int per_pass = 4 * (32 / lph);              // heads a block of four warps takes at once
+    const int hpb8 = per_pass * ((16 + per_pass - 1) / per_pass);
+    dim3 g8(T_, (heads + hpb8 - 1) / hpb8);
+#define CCB_X8(L)                                                                                                  \
+  launch_x8<L>(g8, stream, qkv, row_stride, q_out, k_cache, v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, \
+               nq, nkv, page_size, num_slots, hpb8, status)
+    if (lph == 2) CCB_X8(2);
+    else if (lph == 4) CCB_X8(4);
+    else if (lph == 8) CCB_X8(8);
+    else CCB_X8(16);
+#undef CCB_X8
+    return ccb_launch_status();
+  }
   if (vec && dtype == CCB_F32) {
     ccb_launch(qk_norm_rope_kv_write_vec_kernel<float>, vgrid, 128, 0, stream, (const float*)qkv, row_stride,
                (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, nq, nkv,

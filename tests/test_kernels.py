@@ -632,17 +632,22 @@ def test_attention_window_edge(dtype, edge):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T", [11, 150])   # many tokens: the 16-byte variant of the bfloat16 kernel
 @pytest.mark.parametrize("nq,nkv,hd,P,theta", [(4, 2, 16, 4, 1e4), (6, 3, 48, 8, 5e4), (8, 2, 128, 16, 1e6),
-                                                 (3, 1, 256, 16, 1e6)])
-def test_qk_norm_rope_kv_write(dtype, nq, nkv, hd, P, theta):
+                                                 (3, 1, 256, 16, 1e6), (5, 5, 64, 8, 1e4), (9, 3, 32, 16, 1e6),
+                                                 (32, 8, 128, 16, 1e6)])
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, hd, P, theta, T):
     k = _k()
-    T, eps = 11, 1e-6
-    pages = 9
+    eps = 1e-6
+    pages = max(9, T // P + 3)
     qkv, ref = _rand((T, (nq + 2 * nkv) * hd), DT[dtype], 12)
     qw, qw_ref = _rand((hd,), torch.float32, 13)
     kw, kw_ref = _rand((hd,), torch.float32, 14)
     qw, kw, qw_ref, kw_ref = qw + 1, kw + 1, qw_ref + 1, kw_ref + 1
     positions = torch.tensor([0, 1, 2, 3, 900, 901, 17, 4000, 5, 6, 7], dtype=torch.int32)
+    if T > 11:
+        more = torch.randint(0, 5000, (T - 11,), generator=torch.Generator().manual_seed(16), dtype=torch.int32)
+        positions = torch.cat([positions, more])
     slots = torch.randperm(pages * P, generator=torch.Generator().manual_seed(15))[:T].to(torch.int32)
     slots[3] = -1  # a padded row: nothing is cached for it
     inv_freq = plain.rope_inv_freq(hd, theta)
