@@ -20,6 +20,12 @@ prompts.  It prints ONE JSON line:
 
 Every timed decode step reads 15 GB of weights, far more than the 126 MB L2, so no flush is needed
 between iterations.  With --gpus N > 1 it prints one line that says so and exits with 2.
+
+    python bench.py --workload mix14b | long32b [--layers L]
+
+runs one of the two other workloads of the reference's benchmark record through the scheduler (a mixed
+continuous batch at the Qwen3-14B shape; four 16,384-token prompts at the Qwen3-32B shape) and prints a
+line of its own: output tokens a second, the distribution of the step calls, the pages' high water.
 """
 import argparse
 import json
@@ -38,6 +44,11 @@ QWEN3_8B = {
     "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
     "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "max_position_embeddings": 40960, "torch_dtype": "bfloat16",
+}
+# The two other workloads that the reference's benchmark record names, at their own layer shapes
+SHAPES = {
+    "mix14b": dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408),
+    "long32b": dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
@@ -114,6 +125,93 @@ def model_numbers(cfg, layers):
     return weight_bytes, kv_bytes_per_token, prefill_flops
 
 
+def run_workload(args) -> int:
+    """--workload mix14b: 32 requests, prompts of 64..4,096 tokens in 512-token portions beside running
+    decodes, 128 new tokens each, half greedy and half at temperature 0.7 (Qwen3-14B shape).
+    --workload long32b: 4 requests of 16,384 tokens, then 128 greedy tokens each (Qwen3-32B shape).
+    Through the Python entry point's scheduler; prints one JSON line of its own."""
+    import numpy as np
+    import torch
+    from ccinfer_b200.config import Qwen3Config
+    from ccinfer_b200.engine.engine import Engine, EngineOptions
+    from ccinfer_b200.engine.scheduler import Scheduler
+    from ccinfer_b200.sampling import SamplingParams
+
+    cfg_json = dict(SHAPES[args.workload])
+    layers_full = cfg_json["num_hidden_layers"]
+    layers = args.layers or layers_full
+    cfg_json["num_hidden_layers"] = layers
+    cfg = Qwen3Config.from_json(cfg_json)
+    rng = np.random.RandomState(1)
+    V, new = cfg.vocab_size, 128
+    if args.workload == "mix14b":
+        lens = rng.randint(64, 4097, size=32).tolist()
+        params = [SamplingParams(max_tokens=new, temperature=0.0 if i % 2 == 0 else 0.7, seed=i) for i in range(32)]
+        seed = 43
+    else:
+        lens = [16384] * 4
+        params = [SamplingParams(max_tokens=new) for _ in lens]
+        seed = 44
+    n = len(lens)
+    page = 16
+    per_req = [-(-(L + new + 1) // page) * page for L in lens]
+    opt = EngineOptions(dtype="bfloat16", page_size=page, kv_tokens=sum(per_req), max_requests=n,
+                        max_tokens_per_step=4096, max_context=max(per_req))
+    t0 = time.time()
+    engine = Engine.from_random(cfg, seed=seed, std=0.02, options=opt)
+    torch.cuda.synchronize()
+    print(f"[bench] {args.workload}: model on the device in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    sched = Scheduler(engine, prefill_chunk_size=512, max_tokens_per_step=4096, max_running=n, run_ahead=True)
+    for i, L in enumerate(lens):
+        sched.submit(i, rng.randint(0, V, size=L).tolist(), params[i])
+    sampler = ClockSampler()
+    sampler.start()
+    torch.cuda.synchronize()
+    produced, calls = 0, []
+    t_start = time.perf_counter()
+    t_first_decode_only = None
+    while sched.has_work():
+        t = time.perf_counter()
+        events = sched.step()
+        calls.append((time.perf_counter() - t) * 1e3)
+        produced += sum(1 for ev in events if ev.token is not None)
+        if t_first_decode_only is None and all(r.prefill_done for r in sched.active.values()) and not sched.waiting:
+            torch.cuda.synchronize()
+            t_first_decode_only = (time.perf_counter(), produced)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t_start
+    sampler.stop()
+    engine.check()
+    assert produced == n * new and all(p.used_pages == 0 for p in engine.cache.pools)
+    calls.sort()
+    decode_tail = None
+    if t_first_decode_only is not None and produced > t_first_decode_only[1]:
+        decode_tail = (produced - t_first_decode_only[1]) / (t_start + wall - t_first_decode_only[0])
+    prompt_tokens = int(sum(lens))
+    line = {
+        "metric": f"output tokens/s ({args.workload}: {n} requests, {prompt_tokens:,} prompt tokens in 512-token "
+                  f"portions beside decodes, {new} new tokens each)",
+        "value": round(produced / wall, 1), "unit": "tokens/s", "n_gpus": 1, "workload": args.workload,
+        "higher_is_better": True, "dtype": "bf16", "wall_s": round(wall, 3), "output_tokens": produced,
+        "prompt_tokens": prompt_tokens, "all_tokens_per_s": round((produced + prompt_tokens) / wall, 1),
+        "decode_only_tokens_per_s": None if decode_tail is None else round(decode_tail, 1),
+        "steps": sched.steps, "step_call_ms": {"p50": round(calls[len(calls) // 2], 3),
+                                               "p90": round(calls[int(len(calls) * 0.9)], 3),
+                                               "max": round(calls[-1], 3)},
+        "pages_high_water": max(p.high_water for p in engine.cache.pools), "pages": engine.cache.groups[0].num_pages,
+        "preemptions": sched.preemptions, "graph_replays": engine.graph_replays,
+        "data": f"synthetic: uniform random token ids, random weights (seed {seed}, N(0, 0.02))",
+        "config": {"model": {"mix14b": "Qwen3-14B shape", "long32b": "Qwen3-32B shape"}[args.workload],
+                   "layers": layers, "layers_full": layers_full, "hidden": cfg.hidden_size,
+                   "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "requests": n,
+                   "page_size": page, "prefill_chunk": 512, "max_tokens_per_step": 4096},
+        "clocks": sampler.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -127,6 +225,8 @@ def main() -> int:
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="0 off, 1 products start early, 2 every kernel")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mix14b", "long32b"],
+                    help="decode (the default line) or one of the two other workloads of the benchmark record")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -140,6 +240,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload != "decode":
+        return run_workload(args)
 
     import numpy as np
     import torch
