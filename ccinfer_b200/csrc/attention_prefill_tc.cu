@@ -19,7 +19,9 @@
 //   buffers, so the softmax of a tile does not wait for the previous tile's P V unless it must rescale O.
 //   Measured per 128-key tile on B200 (clock64 of one block, 2,048-token prompt): 3,740 cycles with one
 //   producer warp and one stage barrier for keys and values, 2,190 as it is now, of which the softmax
-//   threads are busy 1,900 (128 exponentials a thread; the special-function unit alone needs 1,024).
+//   threads are busy 1,900 (tcgen05.ld and maximum 345, exponentials, sum, conversion and store 1,385).
+//   Measured and dropped: two threads a row (eight softmax warps) and a share of the exponentials as a cubic
+//   on the FMA pipe: neither made a tile faster.
 //
 // Key tiles are aligned to absolute positions, so a row's result depends on its position and its request's
 // keys only.  Every mbarrier wait is bounded (CCB_ST_WAIT_TIMEOUT, then the block tears down and returns).
@@ -71,10 +73,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   const int b = entry0 + blockIdx.z;
-  const int h = blockIdx.y;
+  const int h = blockIdx.x;
   const int row_begin = cu_q[b], n_new = cu_q[b + 1] - row_begin;
   const int n_qtiles = (n_new + kTQ - 1) / kTQ;
-  const int qt = n_qtiles - 1 - (int)blockIdx.x;   // long tiles first
+  // Blocks start in the order of their linear index, x fastest: with the heads in x, every head's longest
+  // query tile (the last one: it sees the most keys) starts first and the short ones fill in at the end.
+  // With the tiles in x the lengths came mixed and the SMs finished up to 2.6x apart.
+  const int qt = n_qtiles - 1 - (int)blockIdx.y;
   if (qt < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = h / (nq / nkv);
@@ -364,7 +369,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((max_new + kTQ - 1) / kTQ, nq, n_entries);
+  dim3 grid(nq, (max_new + kTQ - 1) / kTQ, n_entries);
   ccb_launch(attention_prefill_tc_kernel<NH>, grid, kTcThreads, smem, stream, tmQ, tmK, tmV, (__nv_bfloat16*)out, cu_q,
              pos0, block_table, bt_stride, entry0, nq, nkv, page_size, page_shift, num_pages, window,
              scale * 1.4426950408889634f, status);
