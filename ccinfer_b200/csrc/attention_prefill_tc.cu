@@ -8,20 +8,23 @@
 //     S = Q K^T          tcgen05.mma  M=128 N=128 K=head   -> TMEM, two buffers: the product of tile i+1 runs
 //                        while the softmax warps work on tile i
 //     P = softmax part   four warps, one query row per thread: tcgen05.ld S, mask, running max and sum in
-//                        float (base-2 exponentials), P as bfloat16 into shared memory in the 128-byte
-//                        swizzle; the running output in TMEM is rescaled when the maximum moved
-//     O += P V           tcgen05.mma  M=128 N=head K=128  (V is the MN-major operand) -> TMEM
+//                        float (base-2 exponentials), P as bfloat16 pairs into tensor memory (tcgen05.st);
+//                        the running output in TMEM is rescaled when the maximum moved
+//     O += P V           tcgen05.mma  M=128 N=head K=128, P the A operand in tensor memory, V the MN-major
+//                        B operand in shared memory -> TMEM
 //   Q, K and V tiles arrive by TMA: Q as two boxes of 128 rows x 64 columns, K and V page by page (a box is
 //   one page of one kv head: page_size rows x 64 columns), two stages each.  Warp 0 issues the key copies,
 //   warp 6 the value copies (one warp for both set the pace of the block: every box is an instruction of its
 //   own), warp 1 the products, warps 2..5 do the softmax, the rescaling and the final division and store.
 //   A key stage is handed back as soon as its product Q K^T has run, a value stage after its P V; P has two
 //   buffers, so the softmax of a tile does not wait for the previous tile's P V unless it must rescale O.
+//   Tensor memory: S at columns 0 and 128, O at 256, P at 384 and 448.
 //   Measured per 128-key tile on B200 (clock64 of one block, 2,048-token prompt): 3,740 cycles with one
-//   producer warp and one stage barrier for keys and values, 2,190 as it is now, of which the softmax
-//   threads are busy 1,900 (tcgen05.ld and maximum 345, exponentials, sum, conversion and store 1,385).
-//   Measured and dropped: two threads a row (eight softmax warps) and a share of the exponentials as a cubic
-//   on the FMA pipe: neither made a tile faster.
+//   producer warp and one stage barrier for keys and values, 2,190 with P in shared memory, 2,060 as it
+//   is now, of which the softmax threads are busy 1,800 (tcgen05.ld and maximum 345, exponentials, sum,
+//   conversion and store 1,270).  Measured and dropped, because none made a tile faster: two threads a row
+//   (eight softmax warps); a share of the exponentials as a cubic on the FMA pipe; two groups of softmax warps
+//   on alternating tiles with three S buffers and P written over its own S; four producer warps.
 //
 // Key tiles are aligned to absolute positions, so a row's result depends on its position and its request's
 // keys only.  Every mbarrier wait is bounded (CCB_ST_WAIT_TIMEOUT, then the block tears down and returns).
@@ -37,7 +40,7 @@ namespace {
 constexpr int kTQ = 128;     // query rows per block = TMEM lanes
 constexpr int kTK = 128;     // keys per tile
 constexpr int kTcThreads = 224;  // warps: 0 key loads, 1 products, 2..5 softmax, 6 value loads
-constexpr int kKvStages = 2;
+constexpr int kKvStages = 2;   // a third stage (the shared memory is there since P left it) measured no faster
 
 // 2^x by the special-function unit alone (one instruction; 2^-inf = 0)
 __device__ __forceinline__ float ex2(float x) {
@@ -58,19 +61,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   constexpr int HD = 64 * NH;
   constexpr int HALF_BYTES = 128 * 128;            // 128 rows x 128 bytes: one 64-column half of a tile
   constexpr int TILE_BYTES = NH * HALF_BYTES;      // Q, K or V tile
-  constexpr int P_BYTES = 2 * HALF_BYTES;          // 128 rows x 128 keys
-  constexpr int TMEM_COLS = 512;                   // S: two buffers of 128 columns, O: HD columns
+  constexpr int TMEM_COLS = 512;                   // S: two buffers of 128 columns, O: HD columns, P: two of 64
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE_BYTES;                   // [stages]
   uint8_t* sV = sK + kKvStages * TILE_BYTES;       // [stages]
-  uint8_t* sP = sV + kKvStages * TILE_BYTES;       // [2]: tile i writes buffer i & 1
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * P_BYTES);
-  // barriers: q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_ready, pv_done[2]
-  const uint32_t b_q = s32(bars), b_kf = s32(bars + 1), b_vf = s32(bars + 3), b_ke = s32(bars + 5),
-                 b_ve = s32(bars + 7), b_sf = s32(bars + 9), b_pr = s32(bars + 11), b_pv = s32(bars + 12);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kKvStages * TILE_BYTES);
+  // barriers: q_full, k_full[3], v_full[3], k_empty[3], v_empty[3], s_full[2], p_ready, pv_done[2]
+  const uint32_t b_q = s32(bars), b_kf = s32(bars + 1), b_vf = s32(bars + 4), b_ke = s32(bars + 7),
+                 b_ve = s32(bars + 10), b_sf = s32(bars + 13), b_pr = s32(bars + 15), b_pv = s32(bars + 16);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
 
   const int b = entry0 + blockIdx.z;
   const int h = blockIdx.x;
@@ -117,6 +118,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_s = *tmem_slot, tmem_o = tmem_s + 256;  // S buffers at columns 0 and 128
+  const uint32_t tmem_p = tmem_s + 384;                       // P: two buffers of 64 columns (bfloat16 pairs)
 
   if (warp == 0 || warp == 6) {
     // ---- TMA producers: whole warps, one lane per page of a tile, so that the page look-ups (dependent
@@ -205,10 +207,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kTK / 16; ++ks) {
-          const uint64_t da = smem_desc(s32(sP + (i & 1) * P_BYTES + (ks >> 2) * HALF_BYTES)) + 2 * (ks & 3);
-          // 16 keys further = 16 rows of 128 bytes; 64 head columns further = the next half; 8 keys = 1024 bytes
+          // P is the A operand in tensor memory (lane = query row, a column = two consecutive keys: 16 keys
+          // = 8 columns).  V: 16 keys further = 16 rows of 128 bytes; 64 head columns further = the next half;
+          // 8 keys = 1024 bytes
           const uint64_t db = smem_desc_mn(s32(sV + s * TILE_BYTES) + ks * 2048, HALF_BYTES, 1024);
-          tc_mma(tmem_o, da, db, idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+          tc_mma_ts(tmem_o, tmem_p + (i & 1) * 64 + ks * 8, db, idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
         }
         tc_commit(b_ve + 8 * s);  // the value stage may be refilled
         tc_commit(b_pv + 8 * (i & 1));  // this P buffer may be overwritten, O may be rescaled
@@ -256,7 +259,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
       const float corr = m_new == -CUDART_INF_F ? 1.f : ex2(m - m_new);
       const float sub = m_new == -CUDART_INF_F ? 0.f : m_new;
       m = m_new;
-      // P has two buffers: this tile's was last read by the product P V of tile i - 2, which is long over;
+      // P has two buffers (in tensor memory): this tile's was last read by P V of tile i - 2, long over;
       // the previous tile's P V only has to be complete when O is rescaled, which is rare
       if (i >= 2) {
         alive = mbar_wait(b_pv + 8 * (i & 1), ((i - 2) >> 1) & 1);
@@ -279,15 +282,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
           tc_wait_st();
         }
       }
-      // probabilities -> bfloat16 -> shared memory (K-major rows of 128 bytes, 16-byte chunks XOR-swizzled by
-      // the row, two halves of 64 keys), and the row sum
+      // probabilities -> bfloat16 pairs -> tensor memory, where P is the A operand of P V: no shared memory for
+      // it, no generic-to-async fence, and the product reads one operand less through the shared-memory port
       float ps2[2] = {0.f, 0.f};
       const float nsub = -sub;
 #pragma unroll
-      for (int c0 = 0; c0 < kTK; c0 += 32) {
-        uint32_t packed[16];
+      for (int c0 = 0; c0 < kTK; c0 += 64) {
+        uint32_t packed[32];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
+        for (int e = 0; e < 64; e += 2) {
           const float a = ex2(fmaf(__uint_as_float(v[c0 + e]), scale_log2, nsub));
           const float c = ex2(fmaf(__uint_as_float(v[c0 + e + 1]), scale_log2, nsub));
           ps2[0] += a;
@@ -295,18 +298,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
           const __nv_bfloat162 hh = __floats2bfloat162_rn(a, c);
           packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
         }
-        uint8_t* prow = sP + (i & 1) * P_BYTES + (c0 >> 6) * HALF_BYTES + row * 128;
-        const int chunk0 = (c0 & 63) >> 3;  // first 16-byte chunk of these 32 keys inside the half
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          const int chunk = (chunk0 + cc) ^ (row & 7);
-          *reinterpret_cast<uint4*>(prow + chunk * 16) =
-              make_uint4(packed[4 * cc], packed[4 * cc + 1], packed[4 * cc + 2], packed[4 * cc + 3]);
-        }
+        tc_st32(tmem_p + (i & 1) * 64 + lane_addr + (c0 >> 1), packed);
       }
+      tc_wait_st();
       l = l * corr + (ps2[0] + ps2[1]);
-      fence_async_smem();   // P (generic writes) before the tensor core's reads
-      tc_fence_before();    // S reads and O writes before the next products
+      tc_fence_before();    // S reads, P and O writes before the next products
       mbar_arrive(b_pr);
     }
     if (alive) {
@@ -361,7 +357,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
       !ccb_tensor_map_2d(k_cache, cache_rows, HD, HD, 64, page_size, &tmK) ||
       !ccb_tensor_map_2d(v_cache, cache_rows, HD, HD, 64, page_size, &tmV))
     return CCB_REFUSE_ARG;
-  const size_t smem = (size_t)(1 + 2 * kKvStages) * NH * 128 * 128 + 2 * 2 * 128 * 128 + 16 * 8 + 1024;
+  const size_t smem = (size_t)(1 + 2 * kKvStages) * NH * 128 * 128 + 20 * 8 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<NH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
