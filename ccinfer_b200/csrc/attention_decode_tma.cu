@@ -31,10 +31,36 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int row, int chunk)
   return tile + (chunk >> 3) * kHalfBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
-template <int HD>
+// What the fused form takes instead of finished queries: the rows of the q|k|v product as they left it.  The
+// kernel then does what qk_norm_rope_kv_write does for these single-token rows (7QiC/ccInfer:
+// src/model/qwen3/qwen3_model.cpp:189-244): per-head RMSNorm and rotate-half rotation of the group's queries
+// in every block; in the block whose key range ends at the row's position also the new key and value, which
+// it writes to their page and adds to the attention as one more partial result (the copy of that page in
+// shared memory was made before the write, so the position is masked there).
+struct FusedQkv {
+  const __nv_bfloat16* qkv;   // [rows, (nq + 2 nkv) * HD]: q heads, k heads, v heads
+  int stride;                 // elements between rows
+  const float* q_w;           // [HD] weights of the per-head norms, or null
+  const float* k_w;
+  float eps;
+  const float* inv_freq;      // [HD / 2] rotation frequencies, or null
+  __nv_bfloat16* k_cache;     // where the new key and value go; null when the cache belongs to another layer
+  __nv_bfloat16* v_cache;     // (that layer has written this position already)
+};
+
+// (cos, sin) of position * inv_freq[i], or (1, 0) without rotation
+__device__ __forceinline__ float2 angle_cs(const float* inv_freq, float fpos, int i) {
+  if (inv_freq == nullptr) return make_float2(1.f, 0.f);
+  float sn, cs;
+  sincosf(fpos * inv_freq[i], &sn, &cs);
+  return make_float2(cs, sn);
+}
+
+template <int HD, bool FUSED>
 __global__ void __launch_bounds__(kThreads)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                            const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                            const __nv_bfloat16* __restrict__ q, const FusedQkv fq,
+                            __nv_bfloat16* __restrict__ out,
                             float* __restrict__ part_acc, float* __restrict__ part_ml,
                             const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                             const int* __restrict__ block_table, int bt_stride, int n_entries, int row0, int nq,
@@ -52,6 +78,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   uint8_t* v_sm = k_sm + kStages * TILE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + kStages * TILE_BYTES);
   const uint32_t bar0 = s32(bars);
+  __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(bars + 4);   // [16][HD]: the group's queries (fused form)
+  float2* cs_sm = reinterpret_cast<float2*>(q_sm + 16 * HD);          // [HD / 2]: (cos, sin) of the row's angles
 
   const int G = nq / nkv;
   const int gchunks = (G + 15) / 16;
@@ -70,17 +98,19 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (FUSED && !padded && tid < HD / 2) cs_sm[tid] = angle_cs(fq.inv_freq, (float)p, tid);   // one angle a thread
   __syncthreads();
 
   float o[2 * KS][4];
 #pragma unroll
   for (int i = 0; i < 2 * KS; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+  bool owner = false;   // fused form: this block's key range ends at the row's own position
 
   if (!padded) {
     // q as A fragments: rows = heads of the group (zero beyond n_heads); the producer warp has none
     uint32_t qa[KS][4];
-    if (warp < 4) {
+    if (warp < 4 && !FUSED) {
       const __nv_bfloat16* q0 = q + ((size_t)t * nq + h0 + gid) * HD;
       const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
       const bool v0 = gid < n_heads, v1 = gid + 8 < n_heads;
@@ -93,6 +123,69 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
       }
     }
+    if (warp < 4 && FUSED) {
+      // Raw queries -> norm -> rotation -> fragments.  A lane holds, of rows gid and gid + 8, the columns
+      // 16 ks + 2 tig (+ 0, 1, 8, 9): the four lanes of a quad hold a whole head between them, and the
+      // partners of a rotation (columns i and i + HD / 2) sit in the same lane, KS / 2 steps apart.
+#pragma unroll
+      for (int rh = 0; rh < 2; ++rh) {
+        const bool valid = gid + 8 * rh < n_heads;
+        const __nv_bfloat16* src = fq.qkv + (size_t)t * fq.stride + (size_t)(h0 + gid + 8 * rh) * HD;
+        float x[KS][4];
+        float ss = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int c = ks * 16 + 2 * tig;
+          const float2 lo = valid ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + c))
+                                  : make_float2(0.f, 0.f);
+          const float2 hi = valid ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + c + 8))
+                                  : make_float2(0.f, 0.f);
+          x[ks][0] = lo.x; x[ks][1] = lo.y; x[ks][2] = hi.x; x[ks][3] = hi.y;
+          ss += lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+        }
+        if (fq.q_w != nullptr) {
+          ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+          ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+          const float inv = 1.0f / sqrtf(ss / (float)HD + fq.eps);
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 16 + 2 * tig;
+            x[ks][0] *= inv * fq.q_w[c];
+            x[ks][1] *= inv * fq.q_w[c + 1];
+            x[ks][2] *= inv * fq.q_w[c + 8];
+            x[ks][3] *= inv * fq.q_w[c + 9];
+          }
+        }
+        if (valid || rh == 0) {   // (the angles are only worth computing for rows that exist)
+#pragma unroll
+          for (int ks = 0; ks < KS / 2; ++ks) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = ks * 16 + 2 * tig + (j & 1) + 8 * (j >> 1);
+              const float2 cs = cs_sm[i];
+              const float a = x[ks][j], bb = x[ks + KS / 2][j];
+              x[ks][j] = a * cs.x - bb * cs.y;
+              x[ks + KS / 2][j] = bb * cs.x + a * cs.y;
+            }
+          }
+        }
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          qa[ks][rh] = pack_bf16(x[ks][0], x[ks][1]);
+          qa[ks][2 + rh] = pack_bf16(x[ks][2], x[ks][3]);
+        }
+      }
+      if (warp == 0) {   // the same queries for the warp that adds the new key at the end
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int c = ks * 16 + 2 * tig;
+          *reinterpret_cast<uint32_t*>(q_sm + gid * HD + c) = qa[ks][0];
+          *reinterpret_cast<uint32_t*>(q_sm + (gid + 8) * HD + c) = qa[ks][1];
+          *reinterpret_cast<uint32_t*>(q_sm + gid * HD + c + 8) = qa[ks][2];
+          *reinterpret_cast<uint32_t*>(q_sm + (gid + 8) * HD + c + 8) = qa[ks][3];
+        }
+      }
+    }
     const int* bt = block_table + (size_t)b * bt_stride;
     const int j0 = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int first_tile = j0 / kTileKeys, last_tile = p / kTileKeys;
@@ -102,6 +195,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     const int my_tiles = min(my_first + per_split, last_tile + 1) - my_first;
     const int pages_per_tile = kTileKeys >> page_shift;
     const int lp_last = p >> page_shift;
+    // the fused form adds position p itself from the product's row, not from the (stale) copy of its page
+    const int p_seen = (FUSED && fq.k_cache != nullptr) ? p - 1 : p;
+    owner = FUSED && fq.k_cache != nullptr && last_tile >= my_first && last_tile < my_first + my_tiles;
 
     // producer warp: lane pg copies page pg of the tile (NH boxes of K, NH of V); lane 0 arms the barrier
     auto issue = [&](int tile, int stage) {
@@ -167,7 +263,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int j = jbase + nb * 8 + e;
-          const bool vis = j >= j0 && j <= p;
+          const bool vis = j >= j0 && j <= p_seen;
           s[nb][e] = vis ? s[nb][e] * scale : -CUDART_INF_F;
           s[nb][2 + e] = vis ? s[nb][2 + e] * scale : -CUDART_INF_F;
           mx0 = fmaxf(mx0, s[nb][e]);
@@ -226,9 +322,70 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   }
   __syncthreads();  // every copy has landed and every warp is done with the tiles: reuse the memory
 
-  float* o_s = reinterpret_cast<float*>(smem);  // [4 warps][16 rows][HD]
-  float* m_s = o_s + 4 * 16 * HD;                   // [4][16]
-  float* l_s = m_s + 64;
+  float* o_s = reinterpret_cast<float*>(smem);  // [4 warps + the new key][16 rows][HD]
+  float* m_s = o_s + 5 * 16 * HD;                   // [5][16]
+  float* l_s = m_s + 80;
+  const int n_part = owner ? 5 : 4;
+  if (FUSED && warp == 4 && owner) {
+    // The row's own key and value, from the product's row: norm, rotation, rounding as the cache holds them;
+    // into their page for the steps to come, and into the result as a fifth partial (one key: its score is
+    // the maximum, its weight 1, its output the value).  A lane has HD / 32 consecutive columns; the partner
+    // of a rotation is 16 lanes away.
+    constexpr int CPL = HD / 32;
+    const int col0 = lane * CPL;
+    const __nv_bfloat16* krow = fq.qkv + (size_t)t * fq.stride + (size_t)(nq + kvh) * HD;
+    const __nv_bfloat16* vrow = krow + (size_t)nkv * HD;
+    float kx[CPL];
+    __nv_bfloat16 vb[CPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) {
+      kx[c] = __bfloat162float(krow[col0 + c]);
+      vb[c] = vrow[col0 + c];
+      ss += kx[c] * kx[c];
+    }
+    if (fq.k_w != nullptr) {
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)HD + fq.eps);
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) kx[c] *= inv * fq.k_w[col0 + c];
+    }
+    const bool first_half = lane < 16;
+    __nv_bfloat16 kb[CPL];
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) {
+      const float other = __shfl_xor_sync(0xffffffffu, kx[c], 16);
+      const int i = (col0 + c) & (HD / 2 - 1);
+      const float2 cs = cs_sm[i];
+      const float a = first_half ? kx[c] : other, bb = first_half ? other : kx[c];
+      kb[c] = __float2bfloat16_rn(first_half ? a * cs.x - bb * cs.y : bb * cs.x + a * cs.y);
+    }
+    const int* bt = block_table + (size_t)b * bt_stride;
+    const int lp = p >> page_shift;
+    const int page = lp < bt_stride ? bt[lp] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (lane == 0) set_status(status, CCB_ST_BAD_PAGE);
+    } else if (gc == 0) {   // one block per kv head writes
+      const size_t dst = (((size_t)page * nkv + kvh) * page_size + (p & (page_size - 1))) * HD + col0;
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) {
+        fq.k_cache[dst + c] = kb[c];
+        fq.v_cache[dst + c] = vb[c];
+      }
+    }
+    for (int hh = 0; hh < n_heads; ++hh) {
+      float dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) dot += __bfloat162float(q_sm[hh * HD + col0 + c]) * __bfloat162float(kb[c]);
+      dot = warp_sum(dot);
+      if (lane == 0) {
+        m_s[4 * 16 + hh] = dot * scale;
+        l_s[4 * 16 + hh] = 1.f;
+      }
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) o_s[(size_t)(4 * 16 + hh) * HD + col0 + c] = __bfloat162float(vb[c]);
+    }
+  }
   if (warp < 4) {
 #pragma unroll
   for (int i = 0; i < 2 * KS; ++i) {
@@ -249,12 +406,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   for (int idx = tid; idx < n_heads * HD; idx += kThreads) {
     const int row = idx / HD, d = idx - row * HD;
     float mm = -CUDART_INF_F;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, m_s[w * 16 + row]);
+    for (int w = 0; w < n_part; ++w) mm = fmaxf(mm, m_s[w * 16 + row]);
     float a = 0.f, ll = 0.f;
     if (mm != -CUDART_INF_F) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < n_part; ++w) {
         const float f = __expf(m_s[w * 16 + row] - mm);
         a += o_s[(size_t)(w * 16 + row) * HD + d] * f;
         ll += l_s[w * 16 + row] * f;
@@ -347,8 +502,9 @@ __global__ void attention_merge_bf16_kernel2(__nv_bfloat16* __restrict__ out, co
   }
 }
 
-template <int HD>
-int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_acc, float* part_ml,
+template <int HD, bool FUSED>
+int launch(const void* q, const FusedQkv& fq, const void* k_cache, const void* v_cache, void* out, float* part_acc,
+           float* part_ml,
            const int* positions, const int* entry_of_token, const int* block_table, int bt_stride, int n_entries,
            int row0, int n_rows, int nq, int nkv, int page_size, int num_pages, int window, float scale,
            int num_splits, int* counters, int* status, cudaStream_t stream) {
@@ -360,17 +516,17 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
   if (!ccb_tensor_map_2d(k_cache, cache_rows, HD, HD, 64, page_size, &tmK) ||
       !ccb_tensor_map_2d(v_cache, cache_rows, HD, HD, 64, page_size, &tmV))
     return CCB_REFUSE_ARG;
-  const size_t smem = (size_t)2 * kStages * (HD / 64) * kHalfBytes + kStages * 8 + 1024;
+  const size_t smem = (size_t)2 * kStages * (HD / 64) * kHalfBytes + 32 + 16 * HD * 2 + (HD / 2) * 8 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, FUSED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(n_rows, nkv * gchunks, num_splits);
-  ccb_launch(attention_decode_tma_kernel<HD>, grid, kThreads, smem, stream, tmK, tmV, (const __nv_bfloat16*)q,
-             (__nv_bfloat16*)out, part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries,
+  ccb_launch(attention_decode_tma_kernel<HD, FUSED>, grid, kThreads, smem, stream, tmK, tmV, (const __nv_bfloat16*)q,
+             fq, (__nv_bfloat16*)out, part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries,
              row0, nq, nkv, page_size, page_shift, num_pages, window, scale, num_splits, counters, status);
   int rc = ccb_launch_status();
   if (rc != 0 || num_splits == 1 || counters != nullptr) return rc;
@@ -397,13 +553,55 @@ CCB_API int ccb_attention_decode_tma(const void* q, const void* k_cache, const v
       ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) != 0)
     return CCB_REFUSE_SIZE;
   if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return CCB_REFUSE_ARG;
+  const FusedQkv none = {};
   if (hd == 128)
-    return launch<128>(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
-                       bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale, num_splits,
-                       counters, status, stream);
+    return launch<128, false>(q, none, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
+                              block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,
+                              scale, num_splits, counters, status, stream);
   if (hd == 64)
-    return launch<64>(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
-                      bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale, num_splits,
-                      counters, status, stream);
+    return launch<64, false>(q, none, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
+                             block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,
+                             scale, num_splits, counters, status, stream);
+  return CCB_REFUSE_SIZE;
+}
+
+// The same attention for rows that bring ONE new token each, straight from the q|k|v product: qkv[t, :] holds
+// nq query heads, then nkv key heads, then nkv value heads (row stride qkv_stride).  The kernel applies the
+// per-head norms (q_w, k_w: [hd] floats or null) and the rotate-half rotation (inv_freq: [hd / 2] or null)
+// at positions[t], writes the row's key and value to their page (write_kv != 0; with 0 the cache belongs to
+// another layer that has written the position already) and attends over positions <= positions[t].
+// qk_norm_rope_kv_write is not needed for such rows.
+CCB_API int ccb_attention_decode_tma_fused(const void* qkv, int qkv_stride, void* k_cache, void* v_cache, void* out,
+                                           float* part_acc, float* part_ml, const int* positions,
+                                           const int* entry_of_token, const int* block_table, int bt_stride,
+                                           int n_entries, int row0, int n_rows, int nq, int nkv, int hd,
+                                           int page_size, int num_pages, int window, float scale, int num_splits,
+                                           const float* q_w, const float* k_w, float eps, const float* inv_freq,
+                                           int write_kv, int* counters, int* status, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || bt_stride <= 0 || num_splits <= 0 || num_splits > 64 ||
+      page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0 || (qkv_stride & 1) ||
+      qkv_stride < (nq + (write_kv ? 2 * nkv : 0)) * hd ||
+      ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(qkv) & 3) != 0)
+    return CCB_REFUSE_SIZE;
+  if (qkv == nullptr || (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr))) return CCB_REFUSE_ARG;
+  FusedQkv fq;
+  fq.qkv = (const __nv_bfloat16*)qkv;
+  fq.stride = qkv_stride;
+  fq.q_w = q_w;
+  fq.k_w = k_w;
+  fq.eps = eps;
+  fq.inv_freq = inv_freq;
+  fq.k_cache = write_kv ? (__nv_bfloat16*)k_cache : nullptr;
+  fq.v_cache = write_kv ? (__nv_bfloat16*)v_cache : nullptr;
+  if (hd == 128)
+    return launch<128, true>(nullptr, fq, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
+                             block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,
+                             scale, num_splits, counters, status, stream);
+  if (hd == 64)
+    return launch<64, true>(nullptr, fq, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
+                            block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,
+                            scale, num_splits, counters, status, stream);
   return CCB_REFUSE_SIZE;
 }

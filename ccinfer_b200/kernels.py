@@ -56,6 +56,10 @@ _SIGNATURES = {
     "ccb_attention_decode_tma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_int, c_void_p, c_void_p, c_void_p],
+    "ccb_attention_decode_tma_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_void_p],
     "ccb_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                   c_void_p],
@@ -385,6 +389,39 @@ def attention_prefill_mma(q, k_cache, v_cache, out, cu_q, pos0, block_table, ent
                                            _p(block_table), block_table.stride(0), entry0, n_entries, max_new,
                                            nq, nkv, hd, page_size, num_pages, int(window), float(scale),
                                            _p(status), _stream()), "attention_prefill_mma")
+
+
+def attention_decode_tma_fused(qkv, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
+                               block_table, n_entries: int, row0: int, n_rows: int, nq: int, window: int,
+                               scale: float, num_splits: int, q_norm_w, k_norm_w, eps: float, inv_freq,
+                               write_kv: bool = True, status=None, merge_counters=None) -> None:
+    """attention_decode_tma for rows of ONE new token each, straight from the q|k|v product ``qkv``
+    [T, (nq + 2 nkv) * hd] (only the nq query heads when ``write_kv`` is false): the kernel norms and rotates
+    the queries itself and, with ``write_kv``, also the row's key, which it writes with the value to their
+    page and attends to.  qk_norm_rope_kv_write is not needed for these rows."""
+    _cuda(qkv, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status,
+          merge_counters, q_norm_w, k_norm_w, inv_freq)
+    T = qkv.shape[0]
+    num_pages, nkv, page_size, hd = k_cache.shape
+    assert out.shape == (T, nq, hd) and qkv.stride(1) == 1
+    assert qkv.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16
+    assert all(w is None or (w.dtype == torch.float32 and w.numel() >= n) for w, n in
+               ((q_norm_w, hd), (k_norm_w, hd), (inv_freq, hd // 2)))
+    assert 0 <= row0 and row0 + n_rows <= T
+    if num_splits > 1:
+        assert part_acc.dtype == part_ml.dtype == torch.float32
+        assert part_acc.numel() >= n_rows * nq * num_splits * hd and part_ml.numel() >= n_rows * nq * num_splits * 2
+    if merge_counters is not None:
+        groups = nkv * -(-(nq // nkv) // DECODE_MMA_HEADS_PER_BLOCK)
+        if num_splits == 1 or merge_counters.numel() < n_rows * groups:
+            merge_counters = None
+    _check(lib().ccb_attention_decode_tma_fused(
+        _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml), _p(positions),
+        _p(entry_of_token), _p(block_table), block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
+        num_pages, int(window), float(scale), num_splits, _p(q_norm_w), _p(k_norm_w), float(eps), _p(inv_freq),
+        1 if write_kv else 0, _p(merge_counters), _p(status), _stream()), "attention_decode_tma_fused")
+    if num_splits > 1 and merge_counters is None:
+        counters.own += 1  # the merge kernel
 
 
 def attention_prefill_tc_fits(hd: int, page_size: int) -> bool:

@@ -404,6 +404,83 @@ def test_attention_decode_tma_merges_in_the_last_block(case, splits):
     assert _k().counters.own - own0 == 2  # one launch each
 
 
+FUSED_CASES = [
+    # cached tokens per row (the new token's position), nq, nkv, hd, page, window, entries that are padding
+    ([0, 1, 15, 16, 63, 64, 65, 700], 32, 8, 128, 16, None, ()),
+    ([5, 127, 128, 300], 8, 8, 64, 8, None, (2,)),          # groups of one head, page 8, a padded row
+    ([511, 512, 40], 16, 2, 128, 32, None, ()),             # groups of 8
+    ([200, 64, 0], 40, 2, 128, 64, 70, ()),                 # groups of 20 (two head chunks), a window
+    ([90, 31], 6, 3, 64, 16, 50, ()),
+]
+
+
+@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("plain_keys", [False, True])
+@pytest.mark.parametrize("case", FUSED_CASES)
+def test_attention_decode_tma_fused(case, splits, plain_keys):
+    """The decode attention fed with the rows of the q|k|v product does what qk_norm_rope_kv_write followed
+    by the attention does: same output, same key and value in the same place of the cache, nothing else
+    touched.  plain_keys: without norm weights and rotation."""
+    k = _k()
+    ctx, nq, nkv, hd, P, window, padding = case
+    B = len(ctx)
+    g = torch.Generator().manual_seed(hd + B + splits)
+    pages_per = [c // P + 1 for c in ctx]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g)
+    stride = max(pages_per)
+    bt = torch.full((B, stride), -1, dtype=torch.int32)
+    at = 0
+    for b in range(B):
+        bt[b, :pages_per[b]] = perm[at:at + pages_per[b]].to(torch.int32)
+        at += pages_per[b]
+    kc0 = (torch.randn((num_pages, nkv, P, hd), generator=g) * 0.7).bfloat16().cuda()
+    vc0 = torch.randn((num_pages, nkv, P, hd), generator=g).bfloat16().cuda()
+    qkv = torch.randn((B, (nq + 2 * nkv) * hd), generator=g).bfloat16().cuda()
+    qw = None if plain_keys else (1 + 0.1 * torch.randn(hd, generator=g)).cuda()
+    kw = None if plain_keys else (1 + 0.1 * torch.randn(hd, generator=g)).cuda()
+    inv_freq = None if plain_keys else plain.rope_inv_freq(hd, 1e6).float().cuda()
+    eps = 1e-6
+    pos = torch.tensor(ctx, dtype=torch.int32)
+    eot = torch.arange(B, dtype=torch.int32)
+    slots = torch.tensor([int(bt[b, ctx[b] // P]) * P + ctx[b] % P for b in range(B)], dtype=torch.int32)
+    for b in padding:
+        eot[b] = -1
+        slots[b] = -1
+    pos, eot, slots, btd = pos.cuda(), eot.cuda(), slots.cuda(), bt.cuda()
+    scale = 1 / math.sqrt(hd)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    acc = torch.empty(B * nq * splits * hd, dtype=torch.float32, device="cuda")
+    ml = torch.empty(B * nq * splits * 2, dtype=torch.float32, device="cuda")
+    # two kernels
+    kc2, vc2 = kc0.clone(), vc0.clone()
+    q = torch.zeros((B, nq, hd), dtype=torch.bfloat16, device="cuda")
+    k.qk_norm_rope_kv_write(qkv, q, kc2, vc2, pos, slots, inv_freq, qw, kw, eps, nq, nkv, hd, P, status)
+    want = torch.zeros_like(q)
+    k.attention_decode_tma(q, kc2, vc2, want, acc, ml, pos, eot, btd, B, 0, B, window or 0, scale, splits, status)
+    # one kernel
+    kc1, vc1 = kc0.clone(), vc0.clone()
+    got = torch.zeros_like(q)
+    counters = torch.zeros(B * nq, dtype=torch.int32, device="cuda")
+    k.attention_decode_tma_fused(qkv, kc1, vc1, got, acc, ml, pos, eot, btd, B, 0, B, nq, window or 0, scale, splits,
+                                 qw, kw, eps, inv_freq, status=status,
+                                 merge_counters=counters if splits == 16 else None)
+    assert int(status.item()) == 0 and int(counters.abs().sum().item()) == 0
+    live = [b for b in range(B) if b not in padding]
+    assert _rel(got[live], want[live].double().cpu()) <= 1e-2
+    assert float(got[list(padding)].abs().max()) == 0 if padding else True
+    assert torch.equal(vc1, vc2)                                  # values are copied
+    assert _rel(kc1, kc2.double().cpu()) <= 8e-3                   # keys: the same up to the rounding of the norm
+    changed = (kc1 != kc0).any(dim=-1)
+    assert int(changed.sum().item()) <= len(live) * nkv           # only the new tokens' rows
+    # a layer that reads another layer's cache: queries only, the position is already there
+    got2 = torch.zeros_like(q)
+    k.attention_decode_tma_fused(qkv, kc2, vc2, got2, acc, ml, pos, eot, btd, B, 0, B, nq, window or 0, scale,
+                                 splits, qw, None, eps, inv_freq, write_kv=False, status=status)
+    assert int(status.item()) == 0
+    assert _rel(got2[live], want[live].double().cpu()) <= 1e-2
+
+
 @pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 257, 511, 598])
 def test_attention_decode_tma_reads_far_key(far_key):
     nq, nkv, hd, P = 8, 2, 128, 16
