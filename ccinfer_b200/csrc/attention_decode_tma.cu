@@ -486,19 +486,36 @@ __global__ void attention_merge_bf16_kernel2(__nv_bfloat16* __restrict__ out, co
   ccb::pdl_begin();
   const int r = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)r * nq + h) * num_splits;
-  float mm = -CUDART_INF_F;
-  for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
   __nv_bfloat16* o = out + ((size_t)(row0 + r) * nq + h) * hd;
-  if (mm == -CUDART_INF_F) {
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
-    return;
-  }
-  float ll = 0.f;
-  for (int s = 0; s < num_splits; ++s) ll += part_ml[(base + s) * 2 + 1] * __expf(part_ml[(base + s) * 2] - mm);
+  // Eight splits at a time: their maxima, sums and outputs are all asked for before any is used, and are
+  // folded in ascending order into a running (maximum, sum, output), as the attention kernels do with keys.
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < num_splits; ++s) a += part_acc[(base + s) * hd + d] * __expf(part_ml[(base + s) * 2] - mm);
-    o[d] = __float2bfloat16_rn(a / ll);
+    float mm = -CUDART_INF_F, ll = 0.f, a = 0.f;
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {
+      float mv[8], lv[8], av[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const bool in = s0 + s < num_splits;
+        mv[s] = in ? part_ml[(base + s0 + s) * 2] : -CUDART_INF_F;
+        lv[s] = in ? part_ml[(base + s0 + s) * 2 + 1] : 0.f;
+        av[s] = in ? part_acc[(base + s0 + s) * hd + d] : 0.f;
+      }
+      float mx = mm;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) mx = fmaxf(mx, mv[s]);
+      if (mx == -CUDART_INF_F) continue;
+      const float keep = __expf(mm - mx);   // 0 while nothing has been seen
+      ll *= keep;
+      a *= keep;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const float f = __expf(mv[s] - mx);   // exp(-inf) = 0 for splits that saw no key or do not exist
+        ll += lv[s] * f;
+        a += av[s] * f;
+      }
+      mm = mx;
+    }
+    o[d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
   }
 }
 

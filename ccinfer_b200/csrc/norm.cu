@@ -93,8 +93,13 @@ residual_rmsnorm_vec_kernel(T* __restrict__ y, float* __restrict__ h, const T* _
   }
   float* hr = h + (size_t)src * D;
   const T* dr = delta ? delta + (size_t)src * D : nullptr;
-  float4 v[kNormVecs];
+  float4 v[kNormVecs], g[kNormVecs];
   float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kNormVecs; ++j) {   // the weights are asked for with the row, not after the sum
+    const int i = threadIdx.x + j * kNormThreads;
+    if (i < nvec) g[j] = Vec4<float>::load(w + 4 * i);
+  }
 #pragma unroll
   for (int j = 0; j < kNormVecs; ++j) {
     const int i = threadIdx.x + j * kNormThreads;
@@ -114,11 +119,9 @@ residual_rmsnorm_vec_kernel(T* __restrict__ y, float* __restrict__ h, const T* _
 #pragma unroll
   for (int j = 0; j < kNormVecs; ++j) {
     const int i = threadIdx.x + j * kNormThreads;
-    if (i < nvec) {
-      const float4 g = Vec4<float>::load(w + 4 * i);
-      Vec4<T>::store(yr + 4 * i, make_float4(v[j].x * inv * g.x, v[j].y * inv * g.y, v[j].z * inv * g.z,
-                                             v[j].w * inv * g.w));
-    }
+    if (i < nvec)
+      Vec4<T>::store(yr + 4 * i, make_float4(v[j].x * inv * g[j].x, v[j].y * inv * g[j].y, v[j].z * inv * g[j].z,
+                                             v[j].w * inv * g[j].w));
   }
 }
 
