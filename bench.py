@@ -167,26 +167,29 @@ def run_workload(args) -> int:
     sampler = ClockSampler()
     sampler.start()
     torch.cuda.synchronize()
-    produced, calls = 0, []
+    produced, calls, decode_calls = 0, [], []
     t_start = time.perf_counter()
-    t_first_decode_only = None
     while sched.has_work():
+        decode_only = all(r.prefill_done for r in sched.active.values()) and not sched.waiting
         t = time.perf_counter()
         events = sched.step()
-        calls.append((time.perf_counter() - t) * 1e3)
-        produced += sum(1 for ev in events if ev.token is not None)
-        if t_first_decode_only is None and all(r.prefill_done for r in sched.active.values()) and not sched.waiting:
-            torch.cuda.synchronize()
-            t_first_decode_only = (time.perf_counter(), produced)
+        ms = (time.perf_counter() - t) * 1e3
+        n_out = sum(1 for ev in events if ev.token is not None)
+        calls.append(ms)
+        if decode_only:
+            decode_calls.append((ms, n_out))
+        produced += n_out
     torch.cuda.synchronize()
     wall = time.perf_counter() - t_start
     sampler.stop()
     engine.check()
     assert produced == n * new and all(p.used_pages == 0 for p in engine.cache.pools)
     calls.sort()
+    # steps that hold decoding requests only, without the first three (a CUDA graph is captured there)
     decode_tail = None
-    if t_first_decode_only is not None and produced > t_first_decode_only[1]:
-        decode_tail = (produced - t_first_decode_only[1]) / (t_start + wall - t_first_decode_only[0])
+    steady = decode_calls[3:]
+    if steady and sum(ms for ms, _ in steady) > 0:
+        decode_tail = sum(n for _, n in steady) / (sum(ms for ms, _ in steady) * 1e-3)
     prompt_tokens = int(sum(lens))
     line = {
         "metric": f"output tokens/s ({args.workload}: {n} requests, {prompt_tokens:,} prompt tokens in 512-token "
