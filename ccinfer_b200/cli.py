@@ -57,6 +57,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens-per-step", type=int, default=4096)
     ap.add_argument("--max-context", type=int, default=None)
     ap.add_argument("--eos-token-id", type=int, default=None)
+    ap.add_argument("--warm-up", action="store_true", help="capture the decode graphs before the first request")
     ap.add_argument("--stats", action="store_true", help="print cache and scheduler figures to stderr")
     ap.add_argument("--write-random-model", metavar="CONFIG_JSON",
                     help="write a random model folder to --model-path from this config.json and exit")
@@ -89,7 +90,7 @@ def main(argv=None) -> int:
                   page_size=args.page_size, kv_tokens=args.kv_tokens,
                   kv_memory_fraction=args.kv_memory_fraction, max_requests=args.max_requests,
                   max_tokens_per_step=args.max_tokens_per_step, max_context=args.max_context,
-                  max_running=args.max_running, eos_token_id=args.eos_token_id)
+                  max_running=args.max_running, eos_token_id=args.eos_token_id, warm_up=args.warm_up)
         sp = SamplingParams(max_tokens=args.max_tokens, top_k=args.top_k, top_p=args.top_p,
                             temperature=args.temperature, seed=args.seed)
         for i, toks in enumerate(llm.generate(prompts, sp)):

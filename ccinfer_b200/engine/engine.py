@@ -387,10 +387,7 @@ class Engine:
         for e in entries:
             if len(e.tokens) != 1 or list(e.want) != [0]:
                 return 0
-        b = 1
-        while b < len(entries):
-            b *= 2
-        return b if b <= self.options.max_requests else 0
+        return self._bucket_of(len(entries))
 
     def _replay_decode(self, entries: List[StepEntry], bucket: int) -> torch.Tensor:
         """A decode step of up to ``bucket`` requests: the step arrays are copied, the kernels replayed.
@@ -412,6 +409,44 @@ class Engine:
         kernels.counters.library += n_lib
         self.graph_replays += 1
         return out[:len(entries)]
+
+    def warm_up(self, batch_sizes: Sequence[int] = ()) -> List[int]:
+        """Captures the decode graphs of the given batch sizes (default: every power of two up to
+        max_requests) before the first request needs them, with throw-away requests of one token; returns
+        the sizes captured.  A capture costs a fraction of a second per size at 36 layers, which the first
+        decode step of that size would otherwise pay."""
+        if not (self.options.use_graphs and self.graph_safe):
+            return []
+        sizes = sorted({self._bucket_of(b) for b in (batch_sizes or self._all_buckets())} - {0})
+        done = []
+        for b in sizes:
+            if b in self._graphs or self.cache.slots.free_slots < b or min(p.free_pages for p in self.cache.pools) < b:
+                continue
+            ids = [("__warm_up__", i) for i in range(b)]
+            try:
+                for rid in ids:
+                    self.open_request(rid)
+                self.step([StepEntry(rid, [0], [0]) for rid in ids])
+                done.append(b)
+            finally:
+                for rid in ids:
+                    if rid in self.cache.requests:
+                        self.close_request(rid)
+        torch.cuda.synchronize(self.rt.device)
+        return done
+
+    def _bucket_of(self, n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return b if b <= self.options.max_requests else 0
+
+    def _all_buckets(self) -> List[int]:
+        out, b = [], 1
+        while b <= self.options.max_requests:
+            out.append(b)
+            b *= 2
+        return out
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the tokens given, as one batch, from the cache; returns float logits [wanted, vocab].

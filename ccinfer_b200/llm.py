@@ -21,10 +21,12 @@ class LLM:
                  max_requests: int = 64,
                  max_tokens_per_step: int = 4096, max_context: Optional[int] = None, max_running: int = 16,
                  eos_token_id: Optional[int] = None, device: str = "cuda:0", use_graphs: bool = True,
-                 engine: Optional[Engine] = None):
+                 warm_up: bool = False, engine: Optional[Engine] = None):
         """``model_path``: a folder with config.json and model.safetensors (the model class is chosen by
         config.json).  ``prefill_chunk_size``: most prompt tokens of one request in a step, 0 = whole prompts.
-        An ``engine`` built elsewhere (for instance ``Engine.from_random``) may be passed instead of a path."""
+        ``warm_up``: capture the decode graphs of every batch size up to ``max_running`` now, not at the first
+        step that needs one.  An ``engine`` built elsewhere (for instance ``Engine.from_random``) may be passed
+        instead of a path."""
         if engine is None:
             if model_path is None:
                 raise ValueError("model_path (or an engine) is required")
@@ -33,6 +35,8 @@ class LLM:
                 kv_memory_fraction=kv_memory_fraction, max_requests=max_requests,
                 max_tokens_per_step=max_tokens_per_step, max_context=max_context, use_graphs=use_graphs))
         self.engine = engine
+        if warm_up:
+            engine.warm_up(range(1, max_running + 1))
         self.scheduler = Scheduler(engine, prefill_chunk_size=prefill_chunk_size,
                                    max_tokens_per_step=min(max_tokens_per_step, engine.options.max_tokens_per_step),
                                    max_running=max_running, eos_token_id=eos_token_id,

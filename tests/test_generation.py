@@ -134,6 +134,25 @@ def test_cache_pool_sized_from_free_memory(model_a):
         Engine.from_model_dir(d, EngineOptions(dtype="float32", kv_tokens=64, kv_memory_fraction=0.5))
 
 
+def test_warm_up_captures_graphs_and_changes_nothing(model_a):
+    """The decode graphs captured ahead of the first request, with throw-away requests: everything they
+    held is given back, and generation afterwards replays them and gives the plain tokens."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, page = model_a
+    llm = LLM(d, dtype="bfloat16", page_size=page, kv_tokens=128, max_requests=4, max_tokens_per_step=64,
+              max_running=4, warm_up=True)
+    eng = llm.engine
+    assert sorted(eng._graphs) == [1, 2, 4]
+    assert all(p.used_pages == 0 for p in eng.cache.pools) and eng.cache.slots.free_slots == 4
+    eng.cache.check_consistency()
+    assert eng.warm_up() == []                       # nothing left to capture
+    replays = eng.graph_replays
+    prompts = _prompts(cfg, [5, 11, 17], 0)
+    got = llm.generate(prompts, SamplingParams(max_tokens=8))
+    assert got == [plain.generate(cfg, w, p, 8) for p in prompts]
+    assert eng.graph_replays > replays and sorted(eng._graphs) == [1, 2, 4]
+
+
 def test_long_decoding_and_first_tokens(model_b):
     """A one-token prompt decoded far, every position compared; and the first tokens of a sequence."""
     from ccinfer_b200.engine.engine import Engine, EngineOptions
