@@ -4,11 +4,11 @@
 // softmax, split key range merged afterwards; 7QiC/ccInfer: src/kernel/attention/decode_attn.cu:417-473).
 //
 // What differs is how keys and values reach shared memory.  There a tile costs 2,048 16-byte cp.async copies
-// issued by all threads, and the load/store path is what holds the kernel (mio / lg throttle stalls).  Here a
-// fifth warp is the producer: one lane per page issues cp.async.bulk.tensor boxes of one page of one kv head
-// (page_size rows x 64 columns, 128-byte swizzle) - 16 copies a tile at page size 16 - signalled by one
-// mbarrier per stage; pages a tile reaches but the request does not hold are replaced by its last page (their
-// keys are masked).  Every mbarrier wait is bounded.
+// issued by all threads, and the load/store path is what holds the kernel (mio / lg throttle stalls).  Here
+// two more warps are the producers, one for keys and one for values: one lane per page issues
+// cp.async.bulk.tensor boxes of one page of one kv head (page_size rows x 64 columns, 128-byte swizzle) - 16
+// copies a tile at page size 16 - signalled by one mbarrier per stage; pages a tile reaches but the request
+// does not hold are replaced by its last page (their keys are masked).  Every mbarrier wait is bounded.
 #include "common.cuh"
 #include "mma_common.cuh"
 #include "tc_common.cuh"
@@ -22,7 +22,7 @@ namespace {
 constexpr int kTileKeys = 64;
 constexpr int kStages = 3;
 constexpr int kComputeThreads = 128;
-constexpr int kThreads = 160;  // four compute warps and the producer warp
+constexpr int kThreads = 192;  // four compute warps and two producer warps (keys, values)
 constexpr int kHalfBytes = kTileKeys * 128;  // 64 rows x 64 columns of bfloat16
 
 // byte address of 16-byte chunk `chunk` (of the whole head) of row `row`: halves of 64 columns, rows 128 bytes
@@ -95,7 +95,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   const int p = positions[t];
   const bool padded = b < 0 || b >= n_entries || p < 0;
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+    for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 2);   // the two producer warps
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (FUSED && !padded && tid < HD / 2) cs_sm[tid] = angle_cs(fq.inv_freq, (float)p, tid);   // one angle a thread
@@ -199,9 +199,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     const int p_seen = (FUSED && fq.k_cache != nullptr) ? p - 1 : p;
     owner = FUSED && fq.k_cache != nullptr && last_tile >= my_first && last_tile < my_first + my_tiles;
 
-    // producer warp: lane pg copies page pg of the tile (NH boxes of K, NH of V); lane 0 arms the barrier
+    // producer warps (4: keys, 5: values): lane pg copies page pg of the tile (NH boxes); lane 0 arrives at the
+    // stage's barrier with the warp's share of the bytes.  Every box is an instruction of its own that costs
+    // its warp about 130 cycles: one warp for both operands was close to setting the pace at full bandwidth.
     auto issue = [&](int tile, int stage) {
-      if (lane == 0) mbar_expect_tx(bar0 + 8 * stage, 2 * TILE_BYTES);
+      if (lane == 0) mbar_expect_tx(bar0 + 8 * stage, TILE_BYTES);
       __syncwarp();
       if (lane < pages_per_tile) {
         const int lp = ((tile * kTileKeys) >> page_shift) + lane;
@@ -213,15 +215,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         }
         const int grow = (page * nkv + kvh) * page_size;
         const uint32_t off = (uint32_t)(lane * page_size) * 128u;
+        uint8_t* dst = (warp == 4 ? k_sm : v_sm) + stage * TILE_BYTES;
+        const CUtensorMap* tm = warp == 4 ? &tmK : &tmV;
 #pragma unroll
-        for (int hf = 0; hf < NH; ++hf) {
-          tma_load_2d(s32(k_sm + stage * TILE_BYTES + hf * kHalfBytes) + off, &tmK, hf * 64, grow, bar0 + 8 * stage);
-          tma_load_2d(s32(v_sm + stage * TILE_BYTES + hf * kHalfBytes) + off, &tmV, hf * 64, grow, bar0 + 8 * stage);
-        }
+        for (int hf = 0; hf < NH; ++hf) tma_load_2d(s32(dst + hf * kHalfBytes) + off, tm, hf * 64, grow, bar0 + 8 * stage);
       }
     };
 
-    if (warp == 4) {
+    if (warp >= 4) {
 #pragma unroll
       for (int s = 0; s < kStages - 1; ++s)
         if (s < my_tiles) issue(my_first + s, s);
@@ -235,7 +236,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         if (tid == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
         break;
       }
-      if (warp == 4) {
+      if (warp >= 4) {
         if (it + kStages - 1 < my_tiles) issue(my_first + it + kStages - 1, (it + kStages - 1) % kStages);
         continue;
       }
