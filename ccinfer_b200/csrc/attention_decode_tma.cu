@@ -77,8 +77,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   uint8_t* k_sm = smem;                               // [stages][tile]
   uint8_t* v_sm = k_sm + kStages * TILE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + kStages * TILE_BYTES);
-  const uint32_t bar0 = s32(bars);
-  __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(bars + 4);   // [16][HD]: the group's queries (fused form)
+  const uint32_t bar0 = s32(bars), empty0 = s32(bars + kStages);   // per stage: "has landed", "has been read"
+  __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(bars + 8);   // [16][HD]: the group's queries (fused form)
   float2* cs_sm = reinterpret_cast<float2*>(q_sm + 16 * HD);          // [HD / 2]: (cos, sin) of the row's angles
 
   const int G = nq / nkv;
@@ -95,7 +95,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   const int p = positions[t];
   const bool padded = b < 0 || b >= n_entries || p < 0;
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 2);   // the two producer warps
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar0 + 8 * s, 2);     // the two producer warps
+      mbar_init(empty0 + 8 * s, 4);   // the four compute warps
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (FUSED && !padded && tid < HD / 2) cs_sm[tid] = angle_cs(fq.inv_freq, (float)p, tid);   // one angle a thread
@@ -222,23 +225,26 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
       }
     };
 
+    // The producers run ahead of the compute warps, held back only by the stages; nobody meets at a block-wide
+    // barrier inside the loop: a compute warp waits for its tile to land and, when it has read it, says so.
     if (warp >= 4) {
-#pragma unroll
-      for (int s = 0; s < kStages - 1; ++s)
-        if (s < my_tiles) issue(my_first + s, s);
-    }
-    for (int it = 0; it < my_tiles; ++it) {
-      const int st = it % kStages;
-      bool alive = mbar_wait(bar0 + 8 * st, (it / kStages) & 1);
-      // the tile has landed for everybody, and everybody has left the stage that is refilled below
-      alive = __syncthreads_and(alive);
-      if (!alive) {
-        if (tid == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
-        break;
+      for (int j = 0; j < my_tiles; ++j) {
+        const int st = j % kStages;
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(empty0 + 8 * st, ((j / kStages) & 1) ^ 1) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          if (lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
+          break;
+        }
+        issue(my_first + j, st);
       }
-      if (warp >= 4) {
-        if (it + kStages - 1 < my_tiles) issue(my_first + it + kStages - 1, (it + kStages - 1) % kStages);
-        continue;
+    }
+    for (int it = 0; warp < 4 && it < my_tiles; ++it) {
+      const int st = it % kStages;
+      if (!mbar_wait(bar0 + 8 * st, (it / kStages) & 1)) {
+        if (lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
+        break;
       }
       const uint32_t ks_ = s32(k_sm + st * TILE_BYTES);
       const uint32_t vs_ = s32(v_sm + st * TILE_BYTES);
@@ -315,6 +321,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
           mma_bf16_16816(o[2 * nn + 1], pa, b10, b11);
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * st);   // this warp has read the stage
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -534,7 +542,7 @@ int launch(const void* q, const FusedQkv& fq, const void* k_cache, const void* v
   if (!ccb_tensor_map_2d(k_cache, cache_rows, HD, HD, 64, page_size, &tmK) ||
       !ccb_tensor_map_2d(v_cache, cache_rows, HD, HD, 64, page_size, &tmV))
     return CCB_REFUSE_ARG;
-  const size_t smem = (size_t)2 * kStages * (HD / 64) * kHalfBytes + 32 + 16 * HD * 2 + (HD / 2) * 8 + 1024;
+  const size_t smem = (size_t)2 * kStages * (HD / 64) * kHalfBytes + 64 + 16 * HD * 2 + (HD / 2) * 8 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, FUSED>,
