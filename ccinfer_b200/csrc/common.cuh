@@ -85,28 +85,6 @@ __device__ __forceinline__ void set_status(int* status, int bit) {
 
 }  // namespace ccb
 
-// What a product may do besides C = A W^T, so that the RMSNorm between two products needs no kernel of its own.
-// The norm y = x * rstd(x) * w is split: the product BEFORE it adds its result to the residual stream h and
-// writes xw = bfloat16(h * w) and, per block, the sum of squares of its columns of h (kResidualPrenorm); the
-// product AFTER it takes xw as its operand and multiplies its result by rstd = 1 / sqrt(sum / K + eps), the
-// sum added up from those partial sums in a fixed order (kScaledRows): (xw rstd) W^T = rstd (xw W^T).
-enum { kPlain = 0, kScaledRows = 1, kResidualPrenorm = 2 };
-
-struct NormFusion {
-  // kScaledRows: where the partial sums of squares lie ([n_part][16] floats, row = token) and the norm's eps
-  const float* ssq_in;
-  int n_part;
-  float eps;
-  // kResidualPrenorm: the residual stream (float [M, N], row stride ldh), the following norm's weights [N],
-  // where xw goes (bfloat16, row stride ldx) and where this launch's partial sums go ([blocks][16])
-  float* h;
-  int ldh;
-  const float* norm_w;
-  __nv_bfloat16* xw;
-  int ldx;
-  float* ssq_out;
-};
-
 // Host side: every launcher returns the CUDA error code of its launch (0 = ok)
 // or a negative number for an argument it refuses.
 #define CCB_REFUSE_SIZE (-2)

@@ -30,12 +30,11 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 }
 
 // NB: number of 8-token tiles (M <= 8 * NB).  TOut: float or bfloat16.
-template <int NB, typename TOut, int MODE>
+template <int NB, typename TOut>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
-                   int M, int N, int K, int lda, int ldw, int ldc, const NormFusion nf) {
+                   int M, int N, int K, int lda, int ldw, int ldc) {
   __shared__ float red[kSkinnyWarps][16][8 * NB + 1];
-  __shared__ float rstd_s[8 * NB];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int n0 = blockIdx.x * 16;
@@ -73,19 +72,6 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
   }
   pdl_wait();
   pdl_trigger();
-  // kScaledRows: warp w owns the tokens w, w + 8, ...; a lane asks for its share of their partial sums of
-  // squares now and adds them after the main loop, so that the loop does not wait for them
-  constexpr int kOwn = (8 * NB + kSkinnyWarps - 1) / kSkinnyWarps, kPer = 8;   // 8 * 32 = 256 partial sums
-  float part[kOwn][kPer];
-  if (MODE == kScaledRows) {
-#pragma unroll
-    for (int o = 0; o < kOwn; ++o)
-#pragma unroll
-      for (int j = 0; j < kPer; ++j) {
-        const int t = warp + o * kSkinnyWarps, i = lane + 32 * j;
-        part[o][j] = (t < M && i < nf.n_part) ? nf.ssq_in[(size_t)i * 16 + t] : 0.f;
-      }
-  }
   for (; kb + U <= kb1; kb += U) {
     uint4 x[U][NB];
 #pragma unroll
@@ -122,18 +108,6 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
       mma_bf16_16816(c[nb], fb, x.z, x.w);
     }
   }
-  if (MODE == kScaledRows) {
-#pragma unroll
-    for (int o = 0; o < kOwn; ++o) {
-      const int t = warp + o * kSkinnyWarps;
-      float sum = 0.f;
-#pragma unroll
-      for (int j = 0; j < kPer; ++j) sum += part[o][j];
-      for (int i = lane + 32 * kPer; i < nf.n_part && t < M; i += 32) sum += nf.ssq_in[(size_t)i * 16 + t];
-      sum = warp_sum(sum);   // a fixed split and a butterfly: the same sum in every block
-      if (lane == 0 && t < 8 * NB) rstd_s[t] = 1.0f / sqrtf(sum / (float)K + nf.eps);
-    }
-  }
   // c[nb]: (feature gid, tokens 8 nb + 2 tig, + 1), (feature gid + 8, same tokens)
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {
@@ -145,51 +119,26 @@ gemm_skinny_kernel(TOut* __restrict__ C, const __nv_bfloat16* __restrict__ A, co
   __syncthreads();
   for (int idx = threadIdx.x; idx < 16 * 8 * NB; idx += kSkinnyWarps * 32) {
     const int tok = idx >> 4, f = idx & 15;  // consecutive threads write consecutive features of a token
-    const bool live = tok < M && n0 + f < N;
-    float s = 0.f;
-    if (live) {
+    if (tok < M && n0 + f < N) {
+      float s = 0.f;
 #pragma unroll
       for (int w = 0; w < kSkinnyWarps; ++w) s += red[w][f][tok];
-    }
-    if (MODE == kResidualPrenorm) {
-      // h += the product; xw = h * (the next norm's weight); the block's share of sum(h^2) per token
-      float hv = 0.f;
-      if (live) {
-        float* hp = nf.h + (size_t)tok * nf.ldh + n0 + f;
-        hv = *hp + s;
-        *hp = hv;
-        nf.xw[(size_t)tok * nf.ldx + n0 + f] = __float2bfloat16_rn(hv * nf.norm_w[n0 + f]);
-      }
-      float sq = hv * hv;   // the 16 features of a token sit in 16 consecutive lanes
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-      if (f == 0) nf.ssq_out[(size_t)blockIdx.x * 16 + tok] = sq;   // tokens beyond M: zeros
-    } else if (live) {
-      if (MODE == kScaledRows) s *= rstd_s[tok];
       C[(size_t)tok * ldc + n0 + f] = from_f32<TOut>(s);
     }
   }
 }
 
-template <int NB, int MODE>
+template <int NB>
 int launch_skinny(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
-                  int out_dtype, const NormFusion& nf, cudaStream_t stream) {
+                  int out_dtype, cudaStream_t stream) {
   const int blocks = (N + 15) / 16;
   if (out_dtype == CCB_F32)
-    ccb_launch_ex(true, gemm_skinny_kernel<NB, float, MODE>, blocks, kSkinnyWarps * 32, 0, stream,
-        (float*)C, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc, nf);
+    ccb_launch_ex(true, gemm_skinny_kernel<NB, float>, blocks, kSkinnyWarps * 32, 0, stream, 
+        (float*)C, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
   else
-    ccb_launch_ex(true, gemm_skinny_kernel<NB, __nv_bfloat16, MODE>, blocks, kSkinnyWarps * 32, 0, stream,
-        (__nv_bfloat16*)C, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc, nf);
+    ccb_launch_ex(true, gemm_skinny_kernel<NB, __nv_bfloat16>, blocks, kSkinnyWarps * 32, 0, stream, 
+        (__nv_bfloat16*)C, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
   return ccb_launch_status();
-}
-
-template <int MODE>
-int dispatch_skinny(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
-                    int out_dtype, const NormFusion& nf, cudaStream_t stream) {
-  if (M <= 8) return launch_skinny<1, MODE>(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, nf, stream);
-  if (M <= 16) return launch_skinny<2, MODE>(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, nf, stream);
-  return launch_skinny<4, MODE>(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, nf, stream);
 }
 
 }  // namespace
@@ -203,43 +152,7 @@ CCB_API int ccb_gemm_skinny_bf16(void* C, const void* A, const void* W, int M, i
   if (M > 32 || K <= 0 || (K & 31) || lda < K || ldw < K || ldc < N || (lda & 7) || (ldw & 7) ||
       (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return CCB_REFUSE_SIZE;
-  return dispatch_skinny<kPlain>(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, NormFusion{}, stream);
-}
-
-// C = rstd[token] * (A W^T) for M <= 16 tokens: A is the xw a product with residual_prenorm wrote, ssq its
-// partial sums of squares ([n_part][16]), K also the width the norm runs over.
-CCB_API int ccb_gemm_skinny_scaled_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
-                                        int ldc, int out_dtype, const float* ssq, int n_part, float eps,
-                                        cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (out_dtype != CCB_F32 && out_dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
-  if (M > 16 || K <= 0 || (K & 31) || lda < K || ldw < K || ldc < N || (lda & 7) || (ldw & 7) || n_part <= 0 ||
-      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
-    return CCB_REFUSE_SIZE;
-  if (ssq == nullptr) return CCB_REFUSE_ARG;
-  NormFusion nf = {};
-  nf.ssq_in = ssq;
-  nf.n_part = n_part;
-  nf.eps = eps;
-  return dispatch_skinny<kScaledRows>(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, nf, stream);
-}
-
-// h[M, N] += A W^T (float, in place); xw = bfloat16(h * norm_w); ssq_out[block][token] = the block's share of
-// sum(h^2) (ceil(N / 16) blocks of 16 floats; tokens beyond M get zeros).  M <= 16.
-CCB_API int ccb_gemm_skinny_residual_prenorm_bf16(float* h, int ldh, const void* A, const void* W, int M, int N, int K,
-                                                  int lda, int ldw, const float* norm_w, void* xw, int ldx,
-                                                  float* ssq_out, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 16 || K <= 0 || (K & 31) || lda < K || ldw < K || ldh < N || ldx < N || (lda & 7) || (ldw & 7) ||
-      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
-    return CCB_REFUSE_SIZE;
-  if (h == nullptr || norm_w == nullptr || xw == nullptr || ssq_out == nullptr) return CCB_REFUSE_ARG;
-  NormFusion nf = {};
-  nf.h = h;
-  nf.ldh = ldh;
-  nf.norm_w = norm_w;
-  nf.xw = (__nv_bfloat16*)xw;
-  nf.ldx = ldx;
-  nf.ssq_out = ssq_out;
-  return dispatch_skinny<kResidualPrenorm>(nullptr, A, W, M, N, K, lda, ldw, N, CCB_BF16, nf, stream);
+  if (M <= 8) return launch_skinny<1>(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, stream);
+  if (M <= 16) return launch_skinny<2>(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, stream);
+  return launch_skinny<4>(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, stream);
 }

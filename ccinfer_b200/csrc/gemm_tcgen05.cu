@@ -76,7 +76,7 @@ template <int BN, int STAGES, bool SWAP, typename TOut>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TOut* __restrict__ C,
                int ldc, int rowsA, int rowsB, int K, int splits, float* __restrict__ partial,
-               int* __restrict__ counters, int swiglu, const NormFusion nf, int* status) {
+               int* __restrict__ counters, int swiglu, int* status) {
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   extern __shared__ uint8_t smem_raw[];
@@ -113,7 +113,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  float* rstd_s = reinterpret_cast<float*>(last_flag + 1);   // [16]: kScaledRows (few tokens only)
 
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer ----
@@ -168,19 +167,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {  // ---- epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31 ----
     const int q = warp & 3;
     const int row = q * 32 + lane;
-    if (SWAP && BN == 16 && nf.ssq_in != nullptr) {
-      // kScaledRows: the tokens' rstd from the partial sums of squares that the product before the norm left
-      // (eight threads a token, a fixed split and a butterfly); these warps have nothing else to do yet
-      pdl_wait();
-      const int e = threadIdx.x - 64, t = e >> 3, sub = e & 7;   // 128 threads: 16 tokens x 8
-      float sum = 0.f;
-      if (t < rowsB)
-        for (int i = sub; i < nf.n_part; i += 8) sum += nf.ssq_in[(size_t)i * 16 + t];
-#pragma unroll
-      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      if (sub == 0) rstd_s[t] = 1.0f / sqrtf(sum / (float)K + nf.eps);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-    }
     const bool ok = mbar_wait(tfull, 0);
     if (!ok && lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
     tc_fence_after();
@@ -215,8 +201,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (j < rowsB) {
-              const float r = nf.ssq_in != nullptr ? rstd_s[j] : 1.f;
-              const float g = __uint_as_float(v[j]) * r, u = xch[row * 17 + j] * r;
+              const float g = __uint_as_float(v[j]), u = xch[row * 17 + j];
               C[(size_t)j * ldc + ch] = from_f32<TOut>(g / (1.f + __expf(-g)) * u);
             }
           }
@@ -286,35 +271,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     acc.w += v[s].w;
                   }
                 }
-                if (nf.h != nullptr) {
-                  // kResidualPrenorm (the launcher takes it only where rowsA % 128 == 0, so every lane of the
-                  // warp is here): h += the product; xw = h * (the next norm's weight); this tile's share of
-                  // sum(h^2) for the token - the warp holds the tile's 128 features of it
-                  float4* hp = reinterpret_cast<float4*>(nf.h + (size_t)t * nf.ldh + f);
-                  float4 hv = *hp;
-                  hv.x += acc.x; hv.y += acc.y; hv.z += acc.z; hv.w += acc.w;
-                  *hp = hv;
-                  const float4 w4 = *reinterpret_cast<const float4*>(nf.norm_w + f);
-                  const __nv_bfloat162 lo = __floats2bfloat162_rn(hv.x * w4.x, hv.y * w4.y);
-                  const __nv_bfloat162 hi = __floats2bfloat162_rn(hv.z * w4.z, hv.w * w4.w);
+                TOut* dst = C + (size_t)t * ldc + f;
+                if constexpr (sizeof(TOut) == 4) {
+                  *reinterpret_cast<float4*>(dst) = acc;
+                } else {
+                  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+                  const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
                   uint2 pk;
                   pk.x = *reinterpret_cast<const uint32_t*>(&lo);
                   pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-                  *reinterpret_cast<uint2*>(nf.xw + (size_t)t * nf.ldx + f) = pk;
-                  const float sq = warp_sum(hv.x * hv.x + hv.y * hv.y + hv.z * hv.z + hv.w * hv.w);
-                  if (lane == 0) nf.ssq_out[(size_t)tileA * 16 + (t - t_begin)] = sq;
-                } else {
-                  TOut* dst = C + (size_t)t * ldc + f;
-                  if constexpr (sizeof(TOut) == 4) {
-                    *reinterpret_cast<float4*>(dst) = acc;
-                  } else {
-                    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
-                    const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
-                    uint2 pk;
-                    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
-                    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-                    *reinterpret_cast<uint2*>(dst) = pk;
-                  }
+                  *reinterpret_cast<uint2*>(dst) = pk;
                 }
               }
             }
@@ -397,9 +363,8 @@ bool tensor_map(const void* ptr, int rows, int K, int ld, int box_rows, CUtensor
 
 template <int BN, int STAGES, bool SWAP, typename TOut>
 int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, int rowsA, int rowsB, int K,
-              int splits, float* partial, int* counters, int* status, cudaStream_t stream, int swiglu = 0,
-              const NormFusion& nf = NormFusion{}) {
-  constexpr size_t smem = (size_t)STAGES * (A_STAGE_BYTES + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 64 + 1024;
+              int splits, float* partial, int* counters, int* status, cudaStream_t stream, int swiglu = 0) {
+  constexpr size_t smem = (size_t)STAGES * (A_STAGE_BYTES + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TOut>,
@@ -409,7 +374,7 @@ int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, 
   }
   dim3 grid((rowsA + BM - 1) / BM, (rowsB + BN - 1) / BN, splits);
   ccb_launch_ex(true, gemm_tc_kernel<BN, STAGES, SWAP, TOut>, grid, kThreadsTc, smem, stream, 
-      tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, swiglu, nf, status);
+      tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, swiglu, status);
   return ccb_launch_status();
 }
 
@@ -460,12 +425,8 @@ CCB_API int ccb_gemm_tc_bf16(void* C, const void* A, const void* W, int M, int N
 // tile of the tensor-core product owns matching gate and up channels.  The products are accumulated in
 // float and the activation is rounded once (7QiC/ccInfer rounds gate and up to bfloat16 first:
 // src/model/qwen3/qwen3_model.cpp:325-370, src/kernel/mlp/silu_mul.cu:24-28).
-// With ssq (partial sums of squares [n_part][16] left by a product with residual_prenorm) A is that product's
-// xw and the products are multiplied by the tokens' rstd before the activation: the RMSNorm before this
-// product, without a kernel of its own.
 CCB_API int ccb_gemm_tc_swiglu_bf16(void* act, const void* A, const void* W, int M, int F, int K, int lda, int ldw,
-                                    int ld_act, const float* ssq, int n_part, float eps, int* status,
-                                    cudaStream_t stream) {
+                                    int ld_act, int* status, cudaStream_t stream) {
   if (M <= 0 || F <= 0) return 0;
   if (M > 16 || (F & 63)) return CCB_REFUSE_SIZE;
   if (K <= 0 || (K & 7) || lda < K || ldw < K || ld_act < F || (lda & 7) || (ldw & 7) ||
@@ -473,45 +434,5 @@ CCB_API int ccb_gemm_tc_swiglu_bf16(void* act, const void* A, const void* W, int
     return CCB_REFUSE_SIZE;
   CUtensorMap tmW, tmX;
   if (!tensor_map(W, 2 * F, K, ldw, BM, &tmW) || !tensor_map(A, M, K, lda, 16, &tmX)) return CCB_REFUSE_ARG;
-  NormFusion nf = {};
-  if (ssq != nullptr) {
-    if (n_part <= 0) return CCB_REFUSE_ARG;
-    nf.ssq_in = ssq;
-    nf.n_part = n_part;
-    nf.eps = eps;
-  }
-  return launch_tc<16, 6, true, __nv_bfloat16>(tmW, tmX, act, ld_act, 2 * F, M, K, 1, nullptr, nullptr, status, stream, 1,
-                                               nf);
-}
-
-// h[M, N] += A W^T (float, in place) with K cut into `splits` >= 2 slices; xw = bfloat16(h * norm_w);
-// ssq_out[tile][token] = the share of sum(h^2) of each tile of 128 columns (N / 128 tiles of 16 floats).
-// M <= 16, N a multiple of 128.  partial / counters as for ccb_gemm_tc_bf16.
-CCB_API int ccb_gemm_tc_residual_prenorm_bf16(float* h, int ldh, const void* A, const void* W, int M, int N, int K,
-                                              int lda, int ldw, int splits, float* partial, int* counters,
-                                              const float* norm_w, void* xw, int ldx, float* ssq_out, int* status,
-                                              cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 16 || (N & 127) || K <= 0 || (K & 7) || lda < K || ldw < K || ldh < N || ldx < N || (lda & 7) || (ldw & 7) ||
-      (ldh & 3) || (ldx & 3) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
-      (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(xw) & 7) ||
-      (reinterpret_cast<uintptr_t>(norm_w) & 15))
-    return CCB_REFUSE_SIZE;
-  const int kb_total = (K + BK - 1) / BK;
-  if (splits < 2 || splits > 16 || splits > kb_total || partial == nullptr || counters == nullptr || h == nullptr ||
-      norm_w == nullptr || xw == nullptr || ssq_out == nullptr)
-    return CCB_REFUSE_ARG;
-  const int per = (kb_total + splits - 1) / splits;
-  if ((splits - 1) * per >= kb_total) return CCB_REFUSE_ARG;
-  CUtensorMap tmW, tmX;
-  if (!tensor_map(W, N, K, ldw, BM, &tmW) || !tensor_map(A, M, K, lda, 16, &tmX)) return CCB_REFUSE_ARG;
-  NormFusion nf = {};
-  nf.h = h;
-  nf.ldh = ldh;
-  nf.norm_w = norm_w;
-  nf.xw = (__nv_bfloat16*)xw;
-  nf.ldx = ldx;
-  nf.ssq_out = ssq_out;
-  // C and ldc stand for h here: the tail's 16-byte path is taken when ldc % 4 == 0
-  return launch_tc<16, 6, true, float>(tmW, tmX, h, ldh, N, M, K, splits, partial, counters, status, stream, 0, nf);
+  return launch_tc<16, 6, true, __nv_bfloat16>(tmW, tmX, act, ld_act, 2 * F, M, K, 1, nullptr, nullptr, status, stream, 1);
 }

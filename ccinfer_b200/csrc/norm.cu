@@ -185,35 +185,3 @@ CCB_API int ccb_rmsnorm(void* y, const void* x, const float* w, int rows, int D,
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
 }
-
-// The second half of a split RMSNorm on its own: y = xw * rstd with rstd = 1 / sqrt(sum / D + eps), the sum
-// added up from the partial sums of squares [n_part][16] that a product with residual_prenorm left (the same
-// fixed order as the products that take xw directly use).  For consumers that need the normalised rows
-// themselves.  Up to 16 rows.
-__global__ void __launch_bounds__(256)
-prenorm_finish_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ xw, int ldx,
-                      const float* __restrict__ ssq, int n_part, int D, float eps) {
-  ccb::pdl_begin();
-  __shared__ float rstd;
-  const int t = blockIdx.x;
-  if (threadIdx.x < 32) {
-    float sum = 0.f;
-    for (int i = threadIdx.x; i < n_part; i += 32) sum += ssq[(size_t)i * 16 + t];
-    sum = ccb::warp_sum(sum);
-    if (threadIdx.x == 0) rstd = 1.0f / sqrtf(sum / (float)D + eps);
-  }
-  __syncthreads();
-  const float r = rstd;
-  for (int d = threadIdx.x; d < D; d += blockDim.x)
-    y[(size_t)t * D + d] = __float2bfloat16_rn(__bfloat162float(xw[(size_t)t * ldx + d]) * r);
-}
-
-CCB_API int ccb_prenorm_finish(void* y, const void* xw, int ldx, const float* ssq, int n_part, int rows, int D,
-                               float eps, cudaStream_t stream) {
-  if (rows <= 0) return 0;
-  if (rows > 16 || D <= 0 || ldx < D || n_part <= 0) return CCB_REFUSE_SIZE;
-  if (y == nullptr || xw == nullptr || ssq == nullptr) return CCB_REFUSE_ARG;
-  ccb_launch(prenorm_finish_kernel, rows, 256, 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)xw, ldx, ssq,
-             n_part, D, eps);
-  return ccb_launch_status();
-}

@@ -37,15 +37,7 @@ _SIGNATURES = {
                          c_void_p],
     "ccb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_gemm_tc_swiglu_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                c_int, c_float, c_void_p, c_void_p],
-    "ccb_gemm_tc_residual_prenorm_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                          c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                          c_void_p],
-    "ccb_gemm_skinny_scaled_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                    c_void_p, c_int, c_float, c_void_p],
-    "ccb_gemm_skinny_residual_prenorm_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                              c_void_p, c_void_p, c_int, c_void_p, c_void_p],
-    "ccb_prenorm_finish": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+                                c_void_p],
     "ccb_residual_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                              c_int, c_void_p, c_void_p],
     "ccb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -202,73 +194,16 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int) -> torc
     return torch.cat([gate.view(F // block, block, D), up.view(F // block, block, D)], dim=1).reshape(2 * F, D).contiguous()
 
 
-def gemm_tc_swiglu_bf16(act, a, w, status=None, ssq=None, n_part: int = 0, eps: float = 0.0) -> None:
+def gemm_tc_swiglu_bf16(act, a, w, status=None) -> None:
     """act[M, F] = silu(a Wg^T) * (a Wu^T) in one tensor-core kernel; w [2F, K] interleaved in blocks of
-    SWIGLU_BLOCK rows (interleave_gate_up), M <= 16, F a multiple of 64.
-
-    With ``ssq`` (see gemm_residual_prenorm) ``a`` is an xw and the products are scaled by the rows' rstd
-    before the activation."""
-    _cuda(act, a, w, status, ssq)
+    SWIGLU_BLOCK rows (interleave_gate_up), M <= 16, F a multiple of 64."""
+    _cuda(act, a, w, status)
     assert act.dtype == a.dtype == w.dtype == torch.bfloat16
     M, K = a.shape
     F = w.shape[0] // 2
     assert w.shape == (2 * F, K) and act.shape == (M, F) and a.stride(1) == w.stride(1) == act.stride(1) == 1
     _check(lib().ccb_gemm_tc_swiglu_bf16(_p(act), _p(a), _p(w), M, F, K, a.stride(0), w.stride(0), act.stride(0),
-                                         _p(ssq), int(n_part), float(eps), _p(status), _stream()),
-           "gemm_tc_swiglu_bf16")
-
-
-# The RMSNorm between two products of a few rows, without a kernel of its own (csrc/common.cuh, NormFusion):
-# the product before it adds itself to the residual stream and leaves xw = h * norm_weight with partial sums
-# of squares; the product after it takes xw and scales its result by the rows' rstd.
-PRENORM_ROWS = 16     # rows of a partial-sum table (and the most rows these kernels take)
-
-
-def gemm_residual_prenorm(h, a, w, norm_w, xw, ssq, splits: int = 1, partial=None, counters=None,
-                          status=None) -> int:
-    """h[M, N] += a[M, K] @ w[N, K]^T (float, in place); xw[M, N] = bfloat16(h * norm_w); returns n_part, the
-    number of partial-sum rows written to ssq ([n_part, 16] floats).  splits >= 2: the tensor-core kernel with
-    K cut into slices (N a multiple of 128); splits == 1: the register-streaming kernel (K a multiple of 32)."""
-    _cuda(h, a, w, norm_w, xw, ssq, partial, counters, status)
-    M, K = a.shape
-    N = w.shape[0]
-    assert h.dtype == norm_w.dtype == ssq.dtype == torch.float32 and a.dtype == w.dtype == xw.dtype == torch.bfloat16
-    assert h.shape == (M, N) and xw.shape == (M, N) and w.shape[1] == K and norm_w.numel() == N
-    assert a.stride(1) == w.stride(1) == h.stride(1) == xw.stride(1) == 1 and M <= PRENORM_ROWS
-    if splits >= 2:
-        n_part = N // 128
-        assert ssq.numel() >= n_part * PRENORM_ROWS and partial.numel() >= splits * M * N
-        _check(lib().ccb_gemm_tc_residual_prenorm_bf16(
-            _p(h), h.stride(0), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), splits, _p(partial), _p(counters),
-            _p(norm_w), _p(xw), xw.stride(0), _p(ssq), _p(status), _stream()), "gemm_tc_residual_prenorm_bf16")
-    else:
-        n_part = -(-N // 16)
-        assert ssq.numel() >= n_part * PRENORM_ROWS
-        _check(lib().ccb_gemm_skinny_residual_prenorm_bf16(
-            _p(h), h.stride(0), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), _p(norm_w), _p(xw), xw.stride(0),
-            _p(ssq), _stream()), "gemm_skinny_residual_prenorm_bf16")
-    return n_part
-
-
-def gemm_skinny_scaled_bf16(c, xw, w, ssq, n_part: int, eps: float) -> None:
-    """c[M, N] = rstd[row] * (xw[M, K] @ w[N, K]^T), rstd from the partial sums ssq [n_part, 16] over K columns."""
-    _cuda(c, xw, w, ssq)
-    M, K = xw.shape
-    N = w.shape[0]
-    assert xw.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT and ssq.dtype == torch.float32
-    assert w.shape[1] == K and c.shape == (M, N) and xw.stride(1) == w.stride(1) == c.stride(1) == 1
-    _check(lib().ccb_gemm_skinny_scaled_bf16(_p(c), _p(xw), _p(w), M, N, K, xw.stride(0), w.stride(0), c.stride(0),
-                                             _dt(c), _p(ssq), int(n_part), float(eps), _stream()),
-           "gemm_skinny_scaled_bf16")
-
-
-def prenorm_finish(y, xw, ssq, n_part: int, eps: float) -> None:
-    """y[M, D] = bfloat16(xw * rstd[row]): the normalised rows themselves, for who needs them."""
-    _cuda(y, xw, ssq)
-    M, D = xw.shape
-    assert y.shape == (M, D) and y.is_contiguous() and xw.stride(1) == 1 and y.dtype == xw.dtype == torch.bfloat16
-    _check(lib().ccb_prenorm_finish(_p(y), _p(xw), xw.stride(0), _p(ssq), int(n_part), M, D, float(eps), _stream()),
-           "prenorm_finish")
+                                         _p(status), _stream()), "gemm_tc_swiglu_bf16")
 
 
 def residual_rmsnorm(y, h, delta, w, eps: float, row_idx=None, n_rows=None, status=None) -> None:

@@ -129,54 +129,6 @@ def test_gemm_tc_swiglu(M, F, K):
                               torch.zeros((17, K), dtype=torch.bfloat16, device="cuda"), w, status)
 
 
-@pytest.mark.parametrize("M,N,K,splits", [(1, 128, 64, 1), (8, 4096, 4096, 1), (13, 80, 96, 1), (16, 256, 512, 1),
-                                          (8, 4096, 12288, 5), (3, 256, 512, 2), (16, 384, 4096, 4)])
-def test_norm_split_over_two_products(M, N, K, splits):
-    """h += a Wo^T and the RMSNorm after it without a norm kernel: the first product leaves xw = h * w_norm
-    and partial sums of squares; the second (plain, gated, or none: prenorm_finish) scales by the rows' rstd.
-    Against the plain formulas in double."""
-    k = _k()
-    eps = 1e-6
-    a, a_ref = _rand((M, K), torch.bfloat16, 40)
-    wo, wo_ref = _rand((N, K), torch.bfloat16, 41, 0.05)
-    h0, h_ref = _rand((M, N), torch.float32, 42)
-    nw, nw_ref = _rand((N,), torch.float32, 43, 0.1)
-    nw, nw_ref = nw + 1, nw_ref + 1
-    h = h0.clone()
-    xw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
-    n_rows = N // 128 if splits > 1 else -(-N // 16)
-    ssq = torch.full((n_rows, 16), float("nan"), dtype=torch.float32, device="cuda")
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    partial = torch.empty(max(1, splits * M * N), dtype=torch.float32, device="cuda")
-    counters = torch.zeros(64, dtype=torch.int32, device="cuda")
-    n_part = k.gemm_residual_prenorm(h, a, wo, nw, xw, ssq, splits, partial, counters, status)
-    assert n_part == n_rows and int(status.item()) == 0 and int(counters.abs().sum().item()) == 0
-    h_want = h_ref + a_ref @ wo_ref.T
-    assert _rel(h, h_want) <= 1e-5 * max(1.0, float(K) ** 0.5)
-    assert _rel(xw, h_want * nw_ref) <= 8e-3
-    assert _rel(ssq[:, :M].sum(0), (h_want ** 2).sum(1)) <= 1e-5
-    normed = h_want * torch.rsqrt((h_want ** 2).mean(1, keepdim=True) + eps) * nw_ref
-    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
-    k.prenorm_finish(y, xw, ssq, n_part, eps)
-    assert _rel(y, normed) <= 1e-2
-    # the next product takes xw and scales its result
-    if N % 32 == 0:
-        N2 = 96
-        w2, w2_ref = _rand((N2, N), torch.bfloat16, 44, 0.05)
-        c = torch.empty((M, N2), dtype=torch.bfloat16, device="cuda")
-        k.gemm_skinny_scaled_bf16(c, xw, w2, ssq, n_part, eps)
-        assert _rel(c, normed @ w2_ref.T) <= 1.2e-2
-    if N % 8 == 0:
-        F = 128
-        wg, wg_ref = _rand((F, N), torch.bfloat16, 45, 0.05)
-        wu, wu_ref = _rand((F, N), torch.bfloat16, 46, 0.05)
-        act = torch.empty((M, F), dtype=torch.bfloat16, device="cuda")
-        k.gemm_tc_swiglu_bf16(act, xw, k.interleave_gate_up(wg, wu, k.SWIGLU_BLOCK), status, ssq, n_part, eps)
-        g, u = normed @ wg_ref.T, normed @ wu_ref.T
-        assert int(status.item()) == 0
-        assert _rel(act, g / (1 + torch.exp(-g)) * u) <= 1.5e-2
-
-
 @pytest.mark.parametrize("M,N,K", [(1, 17, 33), (5, 301, 80), (33, 130, 257), (70, 64, 12), (130, 500, 96)])
 def test_gemm_f32(M, N, K):
     a, a_ref = _rand((M, K), torch.float32, 8)
