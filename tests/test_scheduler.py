@@ -285,3 +285,59 @@ def test_cancel_while_a_step_is_in_flight():
     assert [e.req_id for e in events if e.req_id == "a"] == ["a"]   # the token that was in flight, no more
     assert len([e for e in events if e.req_id == "b" and e.token is not None]) == 10
     assert all(p.used_pages == 0 for p in eng.cache.pools)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_workloads_with_and_without_running_ahead(seed):
+    """Random prompts, lengths, sampling parameters, pool sizes, portion sizes and arrival times: a scheduler
+    that runs ahead returns the same tokens and reasons as one that waits for every step, nothing is left in
+    the cache, and the manager's books stay consistent throughout (the fake engine checks after every step)."""
+    import random
+    rnd = random.Random(seed)
+    n = rnd.randint(3, 9)
+    page = rnd.choice([2, 4, 8])
+    max_context = rnd.choice([40, 64, 96])
+    reqs = []
+    for i in range(n):
+        L = rnd.randint(1, max_context - 8)
+        reqs.append((f"r{i}", _prompt(L, rnd.randint(0, 900)),
+                     SamplingParams(max_tokens=rnd.randint(0, 30), temperature=rnd.choice([0.0, 0.7]), seed=i),
+                     rnd.randint(0, 6)))
+    longest = max(len(p) + sp.max_tokens for _, p, sp, _ in reqs)
+    pages = max(-(-min(longest, max_context) // page) + 1, rnd.randint(6, 40))
+    chunk = rnd.choice([0, 3, 8, 16])
+    budget = rnd.choice([8, 24, 64])
+    window = rnd.choice([None, None, 6])
+
+    def run(ahead, eos_id):
+        eng = FakeEngine(pages=pages, page=page, slots=4, max_context=max_context, window=window)
+        s = Scheduler(eng, prefill_chunk_size=chunk, max_tokens_per_step=budget, max_running=rnd_running,
+                      run_ahead=ahead, eos_token_id=eos_id)
+        out, reasons, step_no = {}, {}, 0
+        todo = sorted(reqs, key=lambda r: r[3])
+        while todo or s.has_work():
+            while todo and todo[0][3] <= step_no:
+                rid, p, sp, _ = todo.pop(0)
+                s.submit(rid, p, sp)
+            for ev in s.step():
+                if ev.token is not None:
+                    out.setdefault(ev.req_id, []).append(ev.token)
+                if ev.finished:
+                    assert ev.req_id not in reasons
+                    reasons[ev.req_id] = ev.reason
+            step_no += 1
+            assert step_no < 5000
+        assert all(p.used_pages == 0 for p in eng.cache.pools) and eng.cache.slots.free_slots == 4
+        assert set(reasons) == {r[0] for r in reqs}
+        return out, reasons
+
+    rnd_running = rnd.randint(1, 4)
+    base, _ = run(False, None)
+    produced = [t for toks in base.values() for t in toks]
+    eos_id = rnd.choice(produced) if produced and rnd.random() < 0.5 else None
+    calm = run(False, eos_id)
+    ahead = run(True, eos_id)
+    assert ahead == calm
+    for rid, p, sp, _ in reqs:
+        toks = calm[0].get(rid, [])
+        assert len(toks) <= sp.max_tokens and len(p) + len(toks) <= max_context + 1
