@@ -237,6 +237,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
           if (lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
           break;
         }
+        // the compute warps read the stage through the generic proxy, the copies write it through the async
+        // proxy: the mbarrier orders the threads, this fence the proxies
+        fence_async_smem();
         issue(my_first + j, st);
       }
     }

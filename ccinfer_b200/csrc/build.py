@@ -42,6 +42,7 @@ GROUPS = {
         "gemm_cublas.cu",
         "gemm_skinny.cu",
         "gemm_tcgen05.cu",
+        "gemm_fewrows.cu",
         "sampling.cu",
     ],
 }

@@ -56,6 +56,7 @@ class Runtime:
         self.scratch = ScratchPool(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.cublas = kernels.CublasHandle(self.device) if dtype == torch.bfloat16 else None
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.tc_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)  # split-K tile counters
         self.merge_counters = torch.zeros(8192, dtype=torch.int32, device=self.device)  # attention split counters
 
@@ -68,20 +69,28 @@ class Runtime:
         N = w.shape[0]
         if M <= kernels.SKINNY_MAX_ROWS:
             # A few tokens: the product is a stream of the weights.  Measured on B200 (graph-timed, weights
-            # larger than L2): the TMA + tcgen05 kernel wins where one block per 128 features fills the
-            # machine or K is long enough to be cut into slices; the register-streaming kernel wins on the
-            # small square products.
-            tc = kernels.gemm_tc_fits(K, x, w) and (-(-N // 128) >= kernels.TC_TARGET_BLOCKS or K >= 8192)
-            if tc:
+            # larger than L2): the tcgen05 kernel wins where one block per 128 features fills the machine
+            # (gate|up, the vocabulary), the TMA-ring kernel with blocks of 16 features on everything
+            # smaller from K = 2048 on (q|k|v, o, down), the register-streaming kernel on short K and, for
+            # one or two tokens, where the ring kernel's blocks would not all be resident with deep rings.
+            fits_tc = kernels.gemm_tc_fits(K, x, w)
+            if fits_tc and -(-N // 128) >= kernels.TC_TARGET_BLOCKS:
+                kernels.gemm_tc_bf16(out, x, w, 1, None, None, self.status)
+                return out
+            if (K >= kernels.FEWROWS_MIN_K and kernels.gemm_fewrows_fits(M, K, x, w)
+                    and (M > 2 or -(-N // 16) <= 2 * self.sm_count)):
+                kernels.gemm_fewrows_bf16(out, x, w, status=self.status)
+                return out
+            if kernels.gemm_skinny_fits(M, K, x, w):
+                kernels.gemm_skinny_bf16(out, x, w)
+                return out
+            if fits_tc:
                 splits = kernels.gemm_tc_splits(M, N, K)
                 partial = counters = None
                 if splits > 1:
                     partial = self.scratch.get("tc_partial", (splits * kernels.SKINNY_MAX_ROWS * N,), torch.float32)
                     counters = self.tc_counters
                 kernels.gemm_tc_bf16(out, x, w, splits, partial, counters, self.status)
-                return out
-            if kernels.gemm_skinny_fits(M, K, x, w):
-                kernels.gemm_skinny_bf16(out, x, w)
                 return out
         self.cublas.gemm_bf16(out, x, w)
         return out
@@ -97,6 +106,11 @@ class Runtime:
                 and kernels.gemm_tc_fits(K, x, w) and -(-N // 128) >= kernels.TC_TARGET_BLOCKS
                 and kernels.gemm_tc_splits(M, N, K) == 1):
             kernels.gemm_tc_swiglu_bf16(act, x, w, self.status)
+            return act
+        if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M <= kernels.FEWROWS_MAX_ROWS
+                and K >= kernels.FEWROWS_MIN_K and N % 128 == 0 and kernels.gemm_fewrows_fits(M, K, x, w)
+                and -(-N // 128) < kernels.TC_TARGET_BLOCKS):
+            kernels.gemm_fewrows_bf16(act, x, w, swiglu=True, status=self.status)
             return act
         gu = self.scratch.get("ffn_gate_up", (self.max_tokens, N), self.dtype)[:M]
         self.linear(gu, x, w)

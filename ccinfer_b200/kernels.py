@@ -38,6 +38,9 @@ _SIGNATURES = {
     "ccb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_gemm_tc_swiglu_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p],
+    "ccb_gemm_fewrows_set_stages": [c_int],
+    "ccb_gemm_fewrows_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_void_p, c_void_p],
     "ccb_residual_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                              c_int, c_void_p, c_void_p],
     "ccb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -508,6 +511,29 @@ def gemm_tc_bf16(c, a, w, splits: int = 1, partial=None, counters=None, status=N
         assert counters.dtype == torch.int32 and counters.numel() >= -(-N // 128)
     _check(lib().ccb_gemm_tc_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _dt(c),
                                   splits, _p(partial), _p(counters), _p(status), _stream()), "gemm_tc_bf16")
+
+
+FEWROWS_MAX_ROWS = 16
+FEWROWS_MIN_K = 2048      # below, the register-streaming kernel starts up faster
+
+
+def gemm_fewrows_fits(M: int, K: int, a, w) -> bool:
+    return (M <= FEWROWS_MAX_ROWS and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_fewrows_bf16(c, a, w, swiglu: bool = False, status=None) -> None:
+    """c[M, N] (bfloat16 or float) = a[M, K] @ w[N, K]^T for M <= 16: blocks of 16 features over the whole K
+    range, weights and tokens through a TMA ring, mma.sync; with ``swiglu`` w [2F, K] is interleaved in blocks
+    of SWIGLU_BLOCK rows (interleave_gate_up) and c[M, F] = silu(a Wg^T) * (a Wu^T)."""
+    _cuda(w, status)
+    assert a.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT and c.is_cuda and a.is_cuda
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N // 2 if swiglu else N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    _check(lib().ccb_gemm_fewrows_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _dt(c),
+                                       1 if swiglu else 0, _p(status), _stream()), "gemm_fewrows_bf16")
 
 
 class CublasHandle:

@@ -212,6 +212,73 @@ def test_gemm_tc_swapped(out, M, N, K, splits):
     assert k.gemm_tc_splits(M, N, K) >= 1
 
 
+@pytest.mark.parametrize("out", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 16, 8), (1, 24, 64), (3, 301, 96), (8, 1000, 4096), (9, 500, 160), (16, 40, 12288),
+                                   (8, 4096, 4096), (16, 6144, 520), (5, 130, 2048 + 72)])
+def test_gemm_fewrows(out, M, N, K):
+    """The TMA-ring few-rows product: ragged edges of N (blocks of 16 features) and of K (stages of 256),
+    more stages than the ring holds, one to 16 tokens."""
+    k = _k()
+    a, a_ref = _rand((M, K), torch.bfloat16, 50)
+    w, w_ref = _rand((N, K), torch.bfloat16, 51)
+    c = torch.full((M, N), float("nan"), dtype=DT[out], device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.gemm_fewrows_bf16(c, a, w, status=status)
+    assert int(status.item()) == 0
+    assert _rel(c, a_ref @ w_ref.T) <= (2e-5 if out == "float32" else 8e-3)
+    # a row's result does not depend on the other rows of the batch
+    c1 = torch.empty((1, N), dtype=DT[out], device="cuda")
+    k.gemm_fewrows_bf16(c1, a[M - 1:M].contiguous(), w, status=status)
+    assert torch.equal(c1[0], c[M - 1])
+    # rows of a wider buffer (row stride > K, output stride > N) as the engine passes them
+    wide = torch.zeros((M, K + 64), dtype=torch.bfloat16, device="cuda")
+    wide[:, :K] = a
+    cw = torch.full((M, N + 24), float("nan"), dtype=DT[out], device="cuda")
+    k.gemm_fewrows_bf16(cw[:, :N], wide[:, :K], w, status=status)
+    assert torch.equal(cw[:, :N], c) and bool(torch.isnan(cw[:, N:].float()).all())
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 64, 64), (8, 192, 512), (8, 12288, 1024), (16, 64 * 75, 320), (5, 64 * 3, 4096 + 8)])
+def test_gemm_fewrows_swiglu(M, F, K):
+    """silu(a Wg^T) * (a Wu^T) as the epilogue: a block holds 8 gate rows and the 8 up rows of the same channels."""
+    from ccinfer_b200.errors import Unsupported
+    k = _k()
+    a, a_ref = _rand((M, K), torch.bfloat16, 54)
+    wg, wg_ref = _rand((F, K), torch.bfloat16, 55)
+    wu, wu_ref = _rand((F, K), torch.bfloat16, 56)
+    w = k.interleave_gate_up(wg, wu, k.SWIGLU_BLOCK)
+    act = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.gemm_fewrows_bf16(act, a, w, swiglu=True, status=status)
+    assert int(status.item()) == 0
+    g, u = a_ref @ wg_ref.T, a_ref @ wu_ref.T
+    assert _rel(act, g / (1 + torch.exp(-g)) * u) <= 8e-3
+    with pytest.raises(Unsupported):  # more rows than the kernel takes
+        k.gemm_fewrows_bf16(torch.empty((17, F), dtype=torch.bfloat16, device="cuda"),
+                            torch.zeros((17, K), dtype=torch.bfloat16, device="cuda"), w, swiglu=True, status=status)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 6144, 4096), (16, 6144, 4096), (3, 10240, 5120), (8, 16384, 2048), (12, 12288, 2560)])
+def test_gemm_fewrows_many_blocks_per_sm(M, N, K):
+    """Shapes with three to seven blocks resident per SM and more stages than the ring holds: the ring's
+    stages are rewritten by TMA under the eyes of many readers.  (Without the proxy fence before the
+    producer's copies these shapes gave wrong features in random blocks, a few hundred of 6,144.)"""
+    k = _k()
+    a, a_ref = _rand((M, K), torch.bfloat16, 57)
+    w, w_ref = _rand((N, K), torch.bfloat16, 58, scale=0.05)
+    want = a_ref @ w_ref.T
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    first = None
+    for rep in range(8):
+        c = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        k.gemm_fewrows_bf16(c, a, w, status=status)
+        assert _rel(c, want) <= 2e-5, rep
+        first = c if first is None else first
+        assert torch.equal(c, first), rep
+    assert int(status.item()) == 0
+
+
 def test_gemm_skinny_refuses():
     from ccinfer_b200.errors import Unsupported
     k = _k()
