@@ -68,7 +68,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             int num_splits, int* __restrict__ counters, int* status) {
   // The kernel after this one is let in only when this one ends: a product that came in while the last
   // blocks were still merging made the pair slower (measured), not faster.
-  ccb::pdl_wait();
+  // The fused form may itself come in early (programmatic dependent launch): the cached keys and values it
+  // copies were written by earlier steps and the step's tables long before, so the producer warps fill
+  // their stages while the q|k|v product before this kernel still runs; the compute warps wait for that
+  // product before they touch its rows.  Otherwise the key of the row's own position is in a page that
+  // the kernel before this one wrote: everybody waits first.
+  const bool early = FUSED && fq.k_cache != nullptr;
+  if (!early) ccb::pdl_wait();
   constexpr int NH = HD / 64;
   constexpr int KS = HD / 16;
   constexpr int TILE_BYTES = NH * kHalfBytes;        // one K or V tile
@@ -103,6 +109,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   }
   if (FUSED && !padded && tid < HD / 2) cs_sm[tid] = angle_cs(fq.inv_freq, (float)p, tid);   // one angle a thread
   __syncthreads();
+  if (early && warp < 4) ccb::pdl_wait();
 
   float o[2 * KS][4];
 #pragma unroll
@@ -554,8 +561,8 @@ int launch(const void* q, const FusedQkv& fq, const void* k_cache, const void* v
     configured = true;
   }
   dim3 grid(n_rows, nkv * gchunks, num_splits);
-  ccb_launch(attention_decode_tma_kernel<HD, FUSED>, grid, kThreads, smem, stream, tmK, tmV, (const __nv_bfloat16*)q,
-             fq, (__nv_bfloat16*)out, part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries,
+  ccb_launch_ex(FUSED && fq.k_cache != nullptr, attention_decode_tma_kernel<HD, FUSED>, grid, kThreads, smem, stream,
+                tmK, tmV, (const __nv_bfloat16*)q, fq, (__nv_bfloat16*)out, part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries,
              row0, nq, nkv, page_size, page_shift, num_pages, window, scale, num_splits, counters, status);
   int rc = ccb_launch_status();
   if (rc != 0 || num_splits == 1 || counters != nullptr) return rc;
