@@ -92,7 +92,7 @@ class GroupedQueryAttention(Mixer):
                 # and head group merges them; few splits: a second small kernel does, during which the
                 # output projection already loads its first weights (measured: 2 us a layer either way)
                 kernels.attention_decode_tma(*args, status=rt.status,
-                                             merge_counters=rt.merge_counters if splits >= 8 else None)
+                                             merge_counters=rt.merge_counters if splits >= self.MERGE_IN_KERNEL_MIN_SPLITS else None)
             else:
                 fn = kernels.attention_decode_mma if mma else kernels.attention_split
                 fn(*args, status=rt.status)
@@ -104,6 +104,7 @@ class GroupedQueryAttention(Mixer):
             fn(q, cache.k, cache.v, o, step.cu_q, step.pos0, g.block_table, step.n_single,
                step.n_entries - step.n_single, step.max_q_len, self.window or 0, self.scale, status=rt.status)
 
+    MERGE_IN_KERNEL_MIN_SPLITS = 8   # from here on the block that finishes last merges the splits itself
     FUSED_DECODE_MAX_ROWS = 48   # measured: 1.3-2.3 us a layer faster up to 32 rows, 1.6 us slower at 64
 
     def _fused_decode(self, step, g) -> bool:
@@ -136,7 +137,7 @@ class GroupedQueryAttention(Mixer):
                 g.block_table, step.n_entries, 0, T, self.nq, self.window or 0, self.scale, splits,
                 self.q_norm_w, self.k_norm_w, self.qk_norm_eps if self.qk_norm_eps is not None else 1.0,
                 self.position.rotary_table(), write_kv=self.own_kv, status=rt.status,
-                merge_counters=rt.merge_counters if splits >= 8 else None)
+                merge_counters=rt.merge_counters if splits >= self.MERGE_IN_KERNEL_MIN_SPLITS else None)
         else:
             q = rt.scratch.get("attn_q", (rt.max_tokens, self.nq, self.hd), rt.dtype)[:T]
             kernels.qk_norm_rope_kv_write(
