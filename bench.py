@@ -161,7 +161,8 @@ def run_workload(args) -> int:
     engine = Engine.from_random(cfg, seed=seed, std=0.02, options=opt)
     torch.cuda.synchronize()
     print(f"[bench] {args.workload}: model on the device in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
-    sched = Scheduler(engine, prefill_chunk_size=512, max_tokens_per_step=4096, max_running=n, run_ahead=True)
+    chunk = args.chunk or 512
+    sched = Scheduler(engine, prefill_chunk_size=chunk, max_tokens_per_step=4096, max_running=n, run_ahead=True)
     for i, L in enumerate(lens):
         sched.submit(i, rng.randint(0, V, size=L).tolist(), params[i])
     sampler = ClockSampler()
@@ -192,7 +193,7 @@ def run_workload(args) -> int:
         decode_tail = sum(n for _, n in steady) / (sum(ms for ms, _ in steady) * 1e-3)
     prompt_tokens = int(sum(lens))
     line = {
-        "metric": f"output tokens/s ({args.workload}: {n} requests, {prompt_tokens:,} prompt tokens in 512-token "
+        "metric": f"output tokens/s ({args.workload}: {n} requests, {prompt_tokens:,} prompt tokens in {chunk}-token "
                   f"portions beside decodes, {new} new tokens each)",
         "value": round(produced / wall, 1), "unit": "tokens/s", "n_gpus": 1, "workload": args.workload,
         "higher_is_better": True, "dtype": "bf16", "wall_s": round(wall, 3), "output_tokens": produced,
@@ -208,7 +209,7 @@ def run_workload(args) -> int:
                    "layers": layers, "layers_full": layers_full, "hidden": cfg.hidden_size,
                    "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "requests": n,
-                   "page_size": page, "prefill_chunk": 512, "max_tokens_per_step": 4096},
+                   "page_size": page, "prefill_chunk": chunk, "max_tokens_per_step": 4096},
         "clocks": sampler.summary(),
     }
     print(json.dumps(line))
@@ -228,6 +229,8 @@ def main() -> int:
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="0 off, 1 products start early, 2 every kernel")
+    ap.add_argument("--chunk", type=int, default=None,
+                    help="prompt portion of the two workloads (default 512, the entry point's own default)")
     ap.add_argument("--workload", default="decode", choices=["decode", "mix14b", "long32b"],
                     help="decode (the default line) or one of the two other workloads of the benchmark record")
     args = ap.parse_args()
