@@ -73,3 +73,46 @@ def test_cuttings_agree_at_the_8b_layer_shape():
     mixed16 = run("bfloat16", tail_only(helpers.trace_mixed(reqs, max_live=4, seed=4)))
     for name, rows in (("whole", whole16), ("decode32", dec16), ("mixed", mixed16)):
         assert _worst(rows, whole32) <= 3e-2, name
+
+
+MID_SHAPE = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 4, "head_dim": 64, "intermediate_size": 4096,
+    "vocab_size": 3000, "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 4096, "torch_dtype": "bfloat16",
+}
+
+
+def test_cuttings_agree_at_a_mid_size_shape_with_head_size_64():
+    """Hidden 2048, head size 64, groups of 8 q heads, 64 tiles of gate|up: the sizes at which the few-rows
+    products of a decode or mixed step go to the TMA-ring kernel (q|k|v, o, down and, with fewer tiles than
+    SMs, gate|up with the activation as its epilogue) while portions of more than 16 tokens go to the
+    library.  bfloat16 under three cuttings against the 32-bit path."""
+    from ccinfer_b200.config import Qwen3Config
+    from ccinfer_b200.engine.engine import Engine, EngineOptions
+    from ccinfer_b200 import kernels
+    rng = np.random.RandomState(3)
+    reqs = {f"r{i}": rng.randint(0, MID_SHAPE["vocab_size"], size=n).tolist() for i, n in enumerate([150, 41, 260, 77])}
+
+    def run(dtype, steps):
+        eng = Engine.from_random(Qwen3Config.from_json(MID_SHAPE), seed=5, std=0.03, options=EngineOptions(
+            dtype=dtype, page_size=16, kv_tokens=1024, max_requests=8, max_tokens_per_step=512, max_context=512))
+        before = kernels.counters.own
+        rows = helpers.replay(eng, steps)
+        eng.cache.check_consistency()
+        assert kernels.counters.own > before
+        del eng
+        torch.cuda.empty_cache()
+        return rows
+
+    whole32 = run("float32", helpers.trace_whole(reqs))
+    mixed32 = run("float32", helpers.trace_mixed(reqs, max_live=4, seed=6))
+    assert set(whole32) == set(mixed32)
+    assert _worst(mixed32, whole32) <= 2e-5
+    for name, steps in (("whole", helpers.trace_whole(reqs)),
+                        ("decode32", helpers.trace_prefill_then_decode(reqs, tail=32)),
+                        ("portions", helpers.trace_portions(reqs)),
+                        ("mixed", helpers.trace_mixed(reqs, max_live=4, seed=6))):
+        rows = run("bfloat16", steps)
+        assert set(rows) == set(whole32), name
+        assert _worst(rows, whole32) <= 3e-2, name
