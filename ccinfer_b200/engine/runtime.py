@@ -71,8 +71,9 @@ class Runtime:
             # A few tokens: the product is a stream of the weights.  Measured on B200 (graph-timed, weights
             # larger than L2): the tcgen05 kernel wins where one block per 128 features fills the machine
             # (gate|up, the vocabulary), the TMA-ring kernel with blocks of 16 features on everything
-            # smaller from K = 2048 on (q|k|v, o, down), the register-streaming kernel on short K and, for
-            # one or two tokens, where the ring kernel's blocks would not all be resident with deep rings.
+            # smaller from K = 2048 on (q|k|v, o, down); for one or two tokens only where its blocks fit two
+            # per SM, else the tcgen05 kernel with K cut into slices (K >= 8192) or the register-streaming
+            # kernel, which also has the short K.
             fits_tc = kernels.gemm_tc_fits(K, x, w)
             if fits_tc and -(-N // 128) >= kernels.TC_TARGET_BLOCKS:
                 kernels.gemm_tc_bf16(out, x, w, 1, None, None, self.status)
@@ -81,7 +82,7 @@ class Runtime:
                     and (M > 2 or -(-N // 16) <= 2 * self.sm_count)):
                 kernels.gemm_fewrows_bf16(out, x, w, status=self.status)
                 return out
-            if kernels.gemm_skinny_fits(M, K, x, w):
+            if kernels.gemm_skinny_fits(M, K, x, w) and not (fits_tc and K >= 8192):
                 kernels.gemm_skinny_bf16(out, x, w)
                 return out
             if fits_tc:
