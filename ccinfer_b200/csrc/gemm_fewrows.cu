@@ -7,10 +7,13 @@
 //     walks the WHOLE K range, so there are N / 16 blocks that the hardware deals out as SMs fall free, and
 //     nothing is added across blocks.
 //   * A producer warp brings W (box 16 rows x 256 k, 8 KB) and the tokens (box 8 or 16 rows x 256 k) into a
-//     ring of shared-memory stages by TMA, each stage with a full and an empty mbarrier; two or three blocks
-//     are resident per SM, so 100-190 KB of weights are in flight per SM from the first cycle.  The weight
-//     boxes of the first ring are requested before griddepcontrol.wait (programmatic dependent launch),
-//     the token boxes after it.
+//     ring of shared-memory stages by TMA, each stage with a full and an empty mbarrier.  The ring is as
+//     deep as it can be with all blocks of the launch resident at once (two blocks of eight stages to seven
+//     blocks of two stages per SM), so 100-130 KB of weights are in flight per SM from the first cycle and
+//     there is no second wave.  The weight boxes of the first ring are requested before
+//     griddepcontrol.wait (programmatic dependent launch), the token boxes after it.  Before the producer
+//     refills a stage that the consumers have handed back it executes fence.proxy.async: they read the
+//     stage through the generic proxy, the copy writes it through the async proxy.
 //   * Eight consumer warps split each stage along k (32 k each): lane (gid, tig) reads 8 consecutive k of
 //     weight rows gid and gid + 8 and of token gid with one 16-byte shared-memory load each and feeds two
 //     mma instructions (a tensor-core product does not care in which order k is walked as long as both
