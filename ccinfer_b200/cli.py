@@ -45,7 +45,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-seed", type=int, default=0)
     ap.add_argument("--max-tokens", type=int, default=256)
     ap.add_argument("--temperature", type=float, default=0.0)
-    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--top-k", type=int, default=0, help="0 = off; applies with a temperature above 0")
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--page-size", type=int, default=16)

@@ -1,4 +1,4 @@
-// Greedy and temperature sampling over float logits, one parameter set per row.
+// Greedy, temperature, top-k and top-p sampling over float logits, one parameter set per row.
 //
 // Greedy: argmax, ties to the lowest id (7QiC/ccInfer: src/kernel/sampling/sample.cu:32, 51-52).
 // Temperature (the reference carries temperature and seed in its SamplingParams,
@@ -8,6 +8,13 @@
 // Philox4x32-10 with counter (v, output index, 0, 0) and key (seed, 0), so a
 // request's draw depends on its seed and on how many tokens it has produced,
 // never on the batch it shares a step with.
+// top-k / top-p (named by the reference's SamplingParams and request fields, src/base/types.h:54-60,
+// src/http/http_server.cpp:529-555, which refuses them): the draw is restricted to the logits at or above a
+// threshold.  top-k: the k-th largest logit.  top-p, within the top-k set: the largest threshold whose set
+// still holds a share p of the set's probability at the row's temperature (the smallest set of most probable
+// tokens that reaches p; ties at the threshold are all kept).  Both thresholds are found exactly over the
+// order-preserving integer image of the floats, by a 256-way search of four levels, each one pass over the
+// row into integer bins (see Search below).
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -40,14 +47,176 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
   return v > bv || (v == bv && i < bi);
 }
 
+// order-preserving image of a float in the unsigned integers; NaN counts as the smallest value
+__device__ __forceinline__ uint32_t float_key(float f) {
+  if (f != f) return 0u;
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Thresholds of top-k and top-p: the largest key T such that the logits with key >= T number at least k
+// (top-k), or hold at least the wanted probability mass (top-p).  Found exactly by a 256-way search: the
+// range of keys that still holds T is cut into 256 equal bins, one pass over the row adds every logit of
+// the range to its bin (counts, or masses in 2^-40 fixed point: integer sums do not depend on the order
+// of the atomic additions, so the result is the same in every run), warp 0 walks the bins from the top
+// until the target is reached, and the search goes on inside that bin: four levels from 2^32 keys to one.
+// The first range is [smallest key, largest key], so the bins follow the spread of the row's logits and
+// few lanes of a warp meet at the same bin.
+// ---------------------------------------------------------------------------------------------
+constexpr int kBins = 256;
+
+struct Search {
+  uint32_t hist_lo[kBins], hist_hi[kBins];   // a bin's sum: 2^32 hist_hi + hist_lo
+  uint32_t lo;                  // keys [lo, lo + 2^wl) still hold the threshold
+  int wl;
+  unsigned long long above;     // count or mass of the keys above the range
+  unsigned long long target;
+  uint32_t ured[2 * (kSampleThreads / 32)];
+};
+
+// One level: `value(v, key)` is what logit v adds (0: nothing).  The range is cut into up to 256 bins of
+// 2^shift keys (a shift, not a division, per logit).  With share >= 0 the target is first set to that
+// share of everything added (the first level of top-p).  Afterwards the range is the bin in which
+// `above + bins from the top` reaches the target.
+template <typename F>
+__device__ void search_level(Search& S, const float* __restrict__ row, int V, double share, F value) {
+  for (int i = threadIdx.x; i < kBins; i += kSampleThreads) S.hist_lo[i] = S.hist_hi[i] = 0u;
+  __syncthreads();
+  const uint32_t lo = S.lo;
+  const int wl = S.wl, shift = wl > 8 ? wl - 8 : 0;
+  const unsigned long long width = 1ull << wl;
+  for (int v = threadIdx.x; v < V; v += kSampleThreads) {
+    const uint32_t key = float_key(row[v]);
+    const unsigned long long off = (unsigned long long)key - lo;
+    if (key >= lo && off < width) {
+      const unsigned long long q = value(v, key);
+      if (q) {
+        // two native 32-bit additions with the carry taken over by hand: integer sums, so the order in
+        // which the lanes arrive does not matter (64-bit shared-memory atomics are compare-and-swap loops)
+        const int b = (int)(off >> shift);
+        const uint32_t ql = (uint32_t)q, qh = (uint32_t)(q >> 32);
+        const uint32_t old = atomicAdd(&S.hist_lo[b], ql);
+        const uint32_t carry = old > 0xffffffffu - ql ? 1u : 0u;
+        if (qh + carry) atomicAdd(&S.hist_hi[b], qh + carry);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {  // warp 0: lane i owns bins 8 i .. 8 i + 7; walk from the top
+    const int lane = threadIdx.x;
+    constexpr int PER = kBins / 32;
+    auto bin_sum = [&](int b) { return ((unsigned long long)S.hist_hi[b] << 32) + S.hist_lo[b]; };
+    unsigned long long mine = 0ull;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) mine += bin_sum(lane * PER + j);
+    unsigned long long higher = 0ull, all = 0ull;  // the lanes above this one; every lane
+    for (int l = 31; l >= 0; --l) {
+      const unsigned long long x = __shfl_sync(0xffffffffu, mine, l);
+      all += x;
+      if (l > lane) higher += x;
+    }
+    unsigned long long tgt = S.target;
+    if (share >= 0.0) {
+      tgt = (unsigned long long)ceil(share * (double)(all + S.above));
+      if (tgt < 1ull) tgt = 1ull;
+    }
+    __syncwarp();
+    const unsigned long long acc0 = S.above + higher;
+    if (acc0 < tgt && acc0 + mine >= tgt) {  // the target is reached inside this lane's bins
+      unsigned long long acc = acc0;
+      int b = lane * PER + PER - 1;
+      for (; b > lane * PER; --b) {
+        if (acc + bin_sum(b) >= tgt) break;
+        acc += bin_sum(b);
+      }
+      S.above = acc;
+      S.lo = lo + ((uint32_t)b << shift);
+      S.wl = shift;
+      S.target = tgt;
+    }
+  }
+  __syncthreads();
+}
+
+// bits of the smallest power of two that holds n keys
+__device__ __forceinline__ int width_log2(unsigned long long n) {
+  int wl = 0;
+  while ((1ull << wl) < n) ++wl;
+  return wl;
+}
+
+// The smallest key that a logit must have to be drawn (0: every logit).
+__device__ uint32_t draw_threshold(const float* __restrict__ row, int V, int k, float p, float inv_t, Search& S) {
+  // the row's smallest and largest key
+  uint32_t kmin = 0xffffffffu, kmax = 0u;
+  for (int v = threadIdx.x; v < V; v += kSampleThreads) {
+    const uint32_t key = float_key(row[v]);
+    kmin = min(kmin, key);
+    kmax = max(kmax, key);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+    kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) {
+    S.ured[2 * (threadIdx.x >> 5)] = kmin;
+    S.ured[2 * (threadIdx.x >> 5) + 1] = kmax;
+  }
+  __syncthreads();
+  for (int w = 0; w < kSampleThreads / 32; ++w) {
+    kmin = min(kmin, S.ured[2 * w]);
+    kmax = max(kmax, S.ured[2 * w + 1]);
+  }
+  __syncthreads();
+  uint32_t thr = 0u;
+  if (k > 0 && k < V) {  // the k-th largest key
+    if (threadIdx.x == 0) {
+      S.lo = kmin;
+      S.wl = width_log2((unsigned long long)kmax - kmin + 1ull);
+      S.above = 0ull;
+      S.target = (unsigned long long)k;
+    }
+    __syncthreads();
+    for (int level = 0; level < 5 && S.wl > 0; ++level)   // at most four levels; the limit is a safeguard
+      search_level(S, row, V, -1.0, [](int, uint32_t) { return 1ull; });
+    thr = S.lo;
+    __syncthreads();
+  }
+  if (p < 1.f) {
+    const float m = __uint_as_float((kmax & 0x80000000u) ? (kmax & 0x7fffffffu) : ~kmax);  // the largest logit
+    const uint32_t floor_key = thr;  // masses are those of the top-k set
+    auto mass = [&](int v, uint32_t key) -> unsigned long long {
+      if (key < floor_key) return 0ull;
+      return (unsigned long long)(__expf((row[v] - m) * inv_t) * 1099511627776.0f);  // 2^40
+    };
+    if (threadIdx.x == 0) {
+      S.lo = max(kmin, floor_key);
+      S.wl = width_log2((unsigned long long)kmax - S.lo + 1ull);
+      S.above = 0ull;
+      S.target = 1ull;
+    }
+    __syncthreads();
+    for (int level = 0; level < 5 && (level == 0 || S.wl > 0); ++level)
+      search_level(S, row, V, level == 0 ? (double)p : -1.0, mass);
+    thr = max(S.lo, floor_key);
+    __syncthreads();
+  }
+  return thr;
+}
+
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, size_t ld, int* __restrict__ tokens,
                    const float* __restrict__ temperature, const unsigned* __restrict__ seed,
-                   const int* __restrict__ out_index, int V, const int* __restrict__ slot_of_row,
+                   const int* __restrict__ out_index, const int* __restrict__ top_k,
+                   const float* __restrict__ top_p, int V, const int* __restrict__ slot_of_row,
                    int* __restrict__ by_slot, int n_slots) {
   ccb::pdl_begin();
   __shared__ float sv[kSampleThreads];
   __shared__ int si[kSampleThreads];
+  __shared__ Search search;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
   const float temp = temperature ? temperature[r] : 0.f;
@@ -56,8 +225,13 @@ sample_rows_kernel(const float* __restrict__ logits, size_t ld, int* __restrict_
   if (temp > 0.f) {
     const float inv_t = 1.0f / temp;
     const uint32_t sd = seed[r], oi = (uint32_t)out_index[r];
+    const int k = top_k ? top_k[r] : 0;
+    const float p = top_p ? top_p[r] : 1.f;
+    const uint32_t thr = (k > 0 || p < 1.f) ? draw_threshold(row, V, k, p, inv_t, search) : 0u;
     for (int v = threadIdx.x; v < V; v += kSampleThreads) {
-      const float z = row[v] * inv_t + gumbel((uint32_t)v, oi, sd);
+      const float l = row[v];
+      if (thr != 0u && float_key(l) < thr) continue;
+      const float z = l * inv_t + gumbel((uint32_t)v, oi, sd);
       if (better(z, v, bv, bi)) { bv = z; bi = v; }
     }
   } else {
@@ -90,14 +264,17 @@ sample_rows_kernel(const float* __restrict__ logits, size_t ld, int* __restrict_
 
 }  // namespace
 
+// top_k (int [R], 0 = off) and top_p (float [R], >= 1 = off) may be null; they apply to rows with a
+// temperature above zero.
 CCB_API int ccb_sample_rows(const float* logits, long long ld, int* tokens, const float* temperature,
-                            const unsigned* seed, const int* out_index, int R, int V, const int* slot_of_row,
-                            int* by_slot, int n_slots, cudaStream_t stream) {
+                            const unsigned* seed, const int* out_index, const int* top_k, const float* top_p, int R,
+                            int V, const int* slot_of_row, int* by_slot, int n_slots, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) return CCB_REFUSE_SIZE;
   if (temperature != nullptr && (seed == nullptr || out_index == nullptr)) return CCB_REFUSE_ARG;
   if (slot_of_row != nullptr && (by_slot == nullptr || n_slots <= 0)) return CCB_REFUSE_ARG;
-  ccb_launch(sample_rows_kernel, R, kSampleThreads, 0, stream, logits, (size_t)ld, tokens, temperature, seed, out_index, V,
-             slot_of_row, by_slot, n_slots);
+  if ((top_k != nullptr || top_p != nullptr) && temperature == nullptr) return CCB_REFUSE_ARG;
+  ccb_launch(sample_rows_kernel, R, kSampleThreads, 0, stream, logits, (size_t)ld, tokens, temperature, seed, out_index,
+             top_k, top_p, V, slot_of_row, by_slot, n_slots);
   return ccb_launch_status();
 }

@@ -153,7 +153,7 @@ class Engine:
         self._dev_buf = torch.zeros(lay.size, dtype=torch.int32, device=rt.device)
         n_rows = max(opt.max_requests, 1)
         self._sample_tokens = torch.zeros(opt.max_tokens_per_step, dtype=torch.int32, device=rt.device)
-        self._sample_host = [torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32).pin_memory()
+        self._sample_host = [torch.zeros((5, opt.max_tokens_per_step), dtype=torch.int32).pin_memory()
                              for _ in range(2)]
         self._sample_out = [torch.zeros(opt.max_tokens_per_step, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._sample_events = [None, None]
@@ -162,7 +162,7 @@ class Engine:
         self._pending_tokens = torch.zeros(opt.max_requests, dtype=torch.int32, device=rt.device)
         self._pending_slots = set()   # slots whose pending token is valid
         self._last_row_slot = None    # (device view, host list) of the most recent step's logits rows
-        self._sample_dev = torch.zeros((3, opt.max_tokens_per_step), dtype=torch.int32, device=rt.device)
+        self._sample_dev = torch.zeros((5, opt.max_tokens_per_step), dtype=torch.int32, device=rt.device)
         self.steps_run = 0
         self.graph_replays = 0
         self._graphs: Dict[int, tuple] = {}
@@ -481,9 +481,10 @@ class Engine:
         return logits
 
     def sample(self, logits: torch.Tensor, params: Sequence, out_index: Sequence[int]) -> List[int]:
-        """One token per logits row: greedy where temperature <= 0, else a temperature draw.
+        """One token per logits row: greedy where temperature <= 0, else a temperature draw, restricted to
+        the top-k logits / the top-p share of the probability where the row's parameters say so.
 
-        ``params[r]`` has ``temperature`` and ``seed``; ``out_index[r]`` is how many tokens the
+        ``params[r]`` has ``temperature`` and ``seed`` (and may have ``top_k``, ``top_p``); ``out_index[r]`` is how many tokens the
         row's request has produced so far.  A draw depends on (seed, out_index) only, not on the
         batch.  Returns host integers (this waits for the step).
         """
@@ -516,10 +517,17 @@ class Engine:
             hp[0, :R] = torch.tensor([float(p.temperature) for p in params], dtype=torch.float32).view(torch.int32)
             hp[1, :R] = torch.tensor([int(p.seed) & 0xFFFFFFFF for p in params], dtype=torch.int64).to(torch.int32)
             hp[2, :R] = torch.tensor(list(out_index), dtype=torch.int32)
+            filtered = any(getattr(p, "top_k", 0) > 0 or getattr(p, "top_p", 1.0) < 1.0 for p in params)
+            if filtered:
+                hp[3, :R] = torch.tensor([int(getattr(p, "top_k", 0)) for p in params], dtype=torch.int32)
+                hp[4, :R] = torch.tensor([float(getattr(p, "top_p", 1.0)) for p in params],
+                                         dtype=torch.float32).view(torch.int32)
             self._sample_dev.copy_(hp, non_blocking=True)
             d = self._sample_dev
             kernels.sample_rows(logits, tokens, d[0, :R].view(torch.float32), d[1, :R], d[2, :R],
-                                slot_of_row=slot_dev, by_slot=self._pending_tokens)
+                                slot_of_row=slot_dev, by_slot=self._pending_tokens,
+                                top_k=d[3, :R] if filtered else None,
+                                top_p=d[4, :R].view(torch.float32) if filtered else None)
         if slots is not None:
             self._pending_slots.update(s for s in slots if s >= 0)
         out = self._sample_out[turn]

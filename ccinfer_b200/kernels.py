@@ -79,8 +79,8 @@ _SIGNATURES = {
                              c_void_p],
     "ccb_gemm_tc_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_void_p, c_void_p],
-    "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
-                        c_void_p, c_int, c_void_p],
+    "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                        c_int, c_void_p, c_void_p, c_int, c_void_p],
 }
 
 
@@ -562,21 +562,26 @@ class CublasHandle:
             self._h = c_void_p()
 
 
-def sample_rows(logits, tokens, temperature=None, seed=None, out_index=None, slot_of_row=None, by_slot=None) -> None:
+def sample_rows(logits, tokens, temperature=None, seed=None, out_index=None, slot_of_row=None, by_slot=None,
+                top_k=None, top_p=None) -> None:
     """tokens[r] = greedy or temperature draw of logits[r, :] (float), per-row parameters.
 
     temperature float [R] (<= 0 greedy), seed uint32-valued int32/int64 [R] taken
     as 32 bits, out_index int32 [R].  temperature None = greedy for all rows.
+    top_k int32 [R] (0 = off) and top_p float [R] (>= 1 = off) restrict a temperature draw to the k largest
+    logits and, within those, to the most probable tokens that hold a share p of the probability.
     With ``slot_of_row`` (int32 [R]) the token of row r is also stored in by_slot[slot_of_row[r]]
     (rows with a slot outside by_slot are skipped).
     """
-    _cuda(tokens, temperature, seed, out_index, slot_of_row, by_slot)
+    _cuda(tokens, temperature, seed, out_index, slot_of_row, by_slot, top_k, top_p)
     assert slot_of_row is None or (slot_of_row.dtype == torch.int32 and by_slot.dtype == torch.int32
                                    and slot_of_row.numel() >= logits.shape[0])
     R, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and tokens.dtype == torch.int32
     assert temperature is None or (temperature.dtype == torch.float32 and seed.dtype == torch.int32
                                    and out_index.dtype == torch.int32)
+    assert top_k is None or (top_k.dtype == torch.int32 and top_k.numel() >= R)
+    assert top_p is None or (top_p.dtype == torch.float32 and top_p.numel() >= R)
     _check(lib().ccb_sample_rows(_p(logits), logits.stride(0), _p(tokens), _p(temperature), _p(seed),
-                                 _p(out_index), R, V, _p(slot_of_row), _p(by_slot),
+                                 _p(out_index), _p(top_k), _p(top_p), R, V, _p(slot_of_row), _p(by_slot),
                                  0 if by_slot is None else by_slot.numel(), _stream()), "sample_rows")

@@ -264,6 +264,38 @@ def sample_temperature(logits_row: torch.Tensor, temperature: float, seed: int, 
     return greedy(z)
 
 
+def sample_filtered(logits_row: torch.Tensor, temperature: float, seed: int, out_index: int, top_k: int = 0,
+                    top_p: float = 1.0):
+    """A temperature draw restricted to the top-k logits and, within those, to the smallest set of most
+    probable tokens whose probabilities at this temperature add up to top_p (ties at either threshold are
+    kept).  The reference names both in its SamplingParams (src/base/types.h:54-60) and refuses them
+    (src/model/model_runner.h:96-100).  Returns (token, margin): margin is how far the cumulative
+    probability at the top-p cut is from top_p (a test skips rows where float rounding could move the cut).
+    """
+    if temperature <= 0:
+        return greedy(logits_row), 1.0
+    l = logits_row.to(F64)
+    allowed = torch.ones_like(l, dtype=torch.bool)
+    V = l.numel()
+    if 0 < top_k < V:
+        kth = torch.sort(l, descending=True).values[top_k - 1]
+        allowed &= l >= kth
+    margin = 1.0
+    if top_p < 1.0:
+        z = torch.where(allowed, torch.exp((l - l.max()) / temperature), torch.zeros_like(l))
+        order = torch.argsort(l, descending=True, stable=True)
+        cum = torch.cumsum(z[order], dim=0) / z.sum()
+        first = int((cum >= top_p).nonzero()[0])          # the prefix up to here reaches top_p
+        cut = l[order[first]]
+        allowed &= l >= cut
+        below = float(cum[first - 1]) if first > 0 else 0.0
+        margin = min(float(cum[first]) - top_p, top_p - below)
+    g = gumbel_noise(seed, out_index, V)
+    zz = l / temperature + torch.from_numpy(g)
+    zz = torch.where(allowed, zz, torch.full_like(zz, -float("inf")))
+    return greedy(zz), margin
+
+
 def generate(cfg, weights, prompt, max_tokens, temperature=0.0, seed=42, dtype=F64):
     """Whole-sequence recomputation per token; returns the new token ids."""
     toks = list(prompt)

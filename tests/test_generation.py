@@ -61,6 +61,31 @@ def test_temperature_generation_tiny_b_in_portions(model_b):
     assert got != [plain.generate(cfg, w, p, 12) for p in prompts]  # it is not greedy in disguise
 
 
+def test_top_k_and_top_p_generation(model_b):
+    """Requests with different filters in one batch: top_k = 1 is greedy whatever the temperature; a
+    request with top_k and top_p draws the tokens of the plain rule, step by step."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, page = model_b
+    prompts = _prompts(cfg, [9, 20, 5], 2)
+    llm = LLM(d, dtype="float32", page_size=page, kv_tokens=512, max_requests=4, max_tokens_per_step=64)
+    params = [SamplingParams(max_tokens=10, temperature=1.3, seed=3, top_k=1),
+              SamplingParams(max_tokens=10, temperature=0.9, seed=11, top_k=20, top_p=0.7),
+              SamplingParams(max_tokens=10, temperature=1.0, seed=5)]
+    got = llm.generate(prompts, params)
+    assert got[0] == plain.generate(cfg, w, prompts[0], 10)
+    assert got[2] == plain.generate(cfg, w, prompts[2], 10, temperature=1.0, seed=5)
+    toks, safe = list(prompts[1]), True
+    for i in range(10):
+        logits = plain.forward(cfg, w, toks, plain.F64)[-1]
+        want, margin = plain.sample_filtered(logits, 0.9, 11, i, 20, 0.7)
+        if margin < 1e-5:
+            safe = False   # a cut on a rounding edge: what follows may differ legitimately
+            break
+        assert got[1][i] == want, i
+        toks.append(want)
+    assert safe or i >= 3
+
+
 def test_pages_run_out_during_generation(model_b):
     """So few pages that a request is preempted and computed again: the tokens are those of a calm run."""
     from ccinfer_b200 import LLM, SamplingParams

@@ -843,6 +843,47 @@ def test_sampling(V):
     assert tokens.tolist() == want
 
 
+@pytest.mark.parametrize("V", [97, 5000, 151936])
+def test_sampling_top_k_top_p(V):
+    """The draw restricted to the k largest logits and to the top-p share: the same token as the plain
+    sort-based rule, never a token outside the allowed set, ties at the k-th logit kept."""
+    k = _k()
+    R = 12
+    g = torch.Generator().manual_seed(21)
+    logits = torch.randn((R, V), generator=g) * 2.0
+    logits[3, 5] = logits[3, 11] = torch.sort(logits[3], descending=True).values[3]   # a tie at the 4th place
+    temps = torch.tensor([0.7, 1.0, 1.3, 0.9, 0.0, 2.0, 0.5, 1.0, 1.0, 0.8, 1.1, 3.0])
+    top_k = torch.tensor([1, 5, 0, 4, 3, 50, 0, V, 7, 2, 0, 40], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 0.9, 1.0, 0.5, 0.8, 0.3, 0.95, 0.6, 1.0, 0.999, 0.05])
+    seeds = torch.arange(R, dtype=torch.int32) * 77 + 5
+    idx = torch.arange(R, dtype=torch.int32) * 3
+    tokens = torch.zeros(R, dtype=torch.int32, device="cuda")
+    k.sample_rows(logits.cuda(), tokens, temps.cuda(), seeds.cuda(), idx.cuda(), top_k=top_k.cuda(), top_p=top_p.cuda())
+    got = tokens.tolist()
+    checked = 0
+    for r in range(R):
+        want, margin = plain.sample_filtered(logits[r], float(temps[r]), int(seeds[r]), int(idx[r]), int(top_k[r]),
+                                             float(top_p[r]))
+        # With a large vocabulary the float sums may move the top-p cut by a few tokens of probability
+        # 1e-6 each (margin: how close the plain rule's cut is to top_p); such a token is practically
+        # never the winner, so the draw is the same unless the cut sits on a rounding edge.
+        assert got[r] == want or margin < 1e-5, (r, margin)
+        checked += got[r] == want
+    assert checked >= R - 1
+    assert got[0] == plain.greedy(logits[0])   # top_k = 1 is the argmax whatever the noise
+    assert got[4] == plain.greedy(logits[4])   # temperature 0: greedy, the filters do not apply
+    # many draws never leave the allowed set
+    n = 400
+    row = logits[1:2].expand(n, V).contiguous().cuda()
+    toks = torch.zeros(n, dtype=torch.int32, device="cuda")
+    k.sample_rows(row, toks, torch.full((n,), 1.5, device="cuda"), torch.full((n,), 3, dtype=torch.int32, device="cuda"),
+                  torch.arange(n, dtype=torch.int32, device="cuda"), top_k=torch.full((n,), 5, dtype=torch.int32, device="cuda"),
+                  top_p=torch.full((n,), 1.0, device="cuda"))
+    top5 = set(torch.topk(logits[1], 5).indices.tolist())
+    seen = set(toks.tolist())
+    assert seen <= top5 and len(seen) >= 3
+
+
 def test_sampling_distribution():
     """Temperature draws follow softmax(logits / T): chi-square over a 12-symbol vocabulary."""
     k = _k()

@@ -95,3 +95,30 @@ def test_tied_head_and_shapes():
     assert lg.shape == (3, cfg["vocab_size"])
     out = plain.generate(cfg, w, [5, 6, 7], 4)
     assert len(out) == 4 and out[0] == plain.greedy(plain.forward(cfg, w, [5, 6, 7])[-1])
+
+
+
+def test_filtered_draws_stay_in_their_set_and_follow_the_renormalised_distribution():
+    """top-k / top-p: every draw is one of the allowed tokens, top_k = 1 is the argmax, and the draws
+    follow softmax over the allowed set."""
+    import numpy as np
+    import torch
+    logits = torch.tensor([2.0, 1.5, 1.4, 0.2, -0.5, -1.0, -3.0, 0.9])
+    T = 0.8
+    assert all(plain.sample_filtered(logits, T, 1, i, top_k=1)[0] == 0 for i in range(20))
+    n = 6000
+    draws = [plain.sample_filtered(logits, T, 9, i, top_k=5, top_p=0.9)[0] for i in range(n)]
+    p_all = torch.softmax(logits.double() / T, dim=0)
+    top5 = torch.topk(logits, 5).indices.tolist()
+    p5 = p_all[top5] / p_all[top5].sum()
+    keep, acc = [], 0.0
+    for j, t in enumerate(top5):           # topk returns them in descending order
+        keep.append(t)
+        acc += float(p5[j])
+        if acc >= 0.9:
+            break
+    assert set(draws) <= set(keep)
+    pk = (p_all[keep] / p_all[keep].sum()).numpy()
+    counts = np.array([draws.count(t) for t in keep])
+    chi2 = float(((counts - n * pk) ** 2 / (n * pk)).sum())
+    assert chi2 < 30.0, chi2

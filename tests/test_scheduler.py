@@ -174,7 +174,9 @@ def test_max_tokens_context_limit_eos_and_cancel():
     with pytest.raises(InvalidArgument):
         s.submit("neg", [1, -2])
     with pytest.raises(Unsupported):
-        s.submit("topk", _prompt(3), SamplingParams(top_k=5))
+        s.submit("topk", _prompt(3), SamplingParams(top_k=-1))
+    with pytest.raises(Unsupported):
+        s.submit("topp", _prompt(3), SamplingParams(top_p=0.0))
     s.submit("x", _prompt(4), SamplingParams(max_tokens=30))
     s.step()
     with pytest.raises(InvalidArgument):
