@@ -87,6 +87,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   const uint32_t bar0 = s32(bars), empty0 = s32(bars + kStages);   // per stage: "has landed", "has been read"
   __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(bars + 8);   // [16][HD]: the group's queries (fused form)
   float2* cs_sm = reinterpret_cast<float2*>(q_sm + 16 * HD);          // [HD / 2]: (cos, sin) of the row's angles
+  float* qw_sm = reinterpret_cast<float*>(cs_sm + HD / 2);            // [HD]: the queries' norm weights
 
   const int G = nq / nkv;
   const int gchunks = (G + 15) / 16;
@@ -119,6 +120,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (FUSED && !padded && tid < HD / 2) cs_sm[tid] = angle_cs(fq.inv_freq, (float)p, tid);   // one angle a thread
+  // weights do not wait for the kernel before this one: they are in shared memory when the queries arrive
+  if (FUSED && !padded && fq.q_w != nullptr && tid < HD) qw_sm[tid] = fq.q_w[tid];
   __syncthreads();
   if (early && warp < 4) ccb::pdl_wait();
 
@@ -171,10 +174,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
 #pragma unroll
           for (int ks = 0; ks < KS; ++ks) {
             const int c = ks * 16 + 2 * tig;
-            x[ks][0] *= inv * fq.q_w[c];
-            x[ks][1] *= inv * fq.q_w[c + 1];
-            x[ks][2] *= inv * fq.q_w[c + 8];
-            x[ks][3] *= inv * fq.q_w[c + 9];
+            x[ks][0] *= inv * qw_sm[c];
+            x[ks][1] *= inv * qw_sm[c + 1];
+            x[ks][2] *= inv * qw_sm[c + 8];
+            x[ks][3] *= inv * qw_sm[c + 9];
           }
         }
         if (valid || rh == 0) {   // (the angles are only worth computing for rows that exist)
@@ -560,7 +563,7 @@ int launch(const void* q, const FusedQkv& fq, const void* k_cache, const void* v
   if (!ccb_tensor_map_2d(k_cache, cache_rows, HD, HD, 64, page_size, &tmK) ||
       !ccb_tensor_map_2d(v_cache, cache_rows, HD, HD, 64, page_size, &tmV))
     return CCB_REFUSE_ARG;
-  const size_t smem = (size_t)2 * kStages * (HD / 64) * kHalfBytes + 64 + 16 * HD * 2 + (HD / 2) * 8 + 1024;
+  const size_t smem = (size_t)2 * kStages * (HD / 64) * kHalfBytes + 64 + 16 * HD * 2 + (HD / 2) * 8 + HD * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, FUSED>,
