@@ -4,8 +4,8 @@
 // Temperature (the reference carries temperature and seed in its SamplingParams,
 // src/base/types.h:54-60, but samples greedily only): the Gumbel-max draw
 //   token = argmax_v( logit_v / T + G_v ),  G_v = -log(-log u_v),
-// which is an exact draw from softmax(logits / T).  u_v comes from
-// Philox4x32-10 with counter (v, output index, 0, 0) and key (seed, 0), so a
+// which is an exact draw from softmax(logits / T).  u_v is word v % 4 of
+// Philox4x32-10 with counter (v / 4, output index, 0, 0) and key (seed, 0), so a
 // request's draw depends on its seed and on how many tokens it has produced,
 // never on the batch it shares a step with.
 // top-k / top-p (named by the reference's SamplingParams and request fields, src/base/types.h:54-60,
@@ -22,7 +22,7 @@ namespace {
 
 constexpr int kSampleThreads = 512;
 
-__device__ __forceinline__ uint32_t philox_first_word(uint32_t c0, uint32_t c1, uint32_t k0) {
+__device__ __forceinline__ void philox4(uint32_t c0, uint32_t c1, uint32_t k0, uint32_t* out) {
   uint32_t c[4] = {c0, c1, 0u, 0u};
   uint32_t k[2] = {k0, 0u};
 #pragma unroll
@@ -34,11 +34,10 @@ __device__ __forceinline__ uint32_t philox_first_word(uint32_t c0, uint32_t c1, 
     k[0] += 0x9E3779B9u;
     k[1] += 0xBB67AE85u;
   }
-  return c[0];
+  out[0] = c[0]; out[1] = c[1]; out[2] = c[2]; out[3] = c[3];
 }
 
-__device__ __forceinline__ float gumbel(uint32_t v, uint32_t out_index, uint32_t seed) {
-  const uint32_t r = philox_first_word(v, out_index, seed);
+__device__ __forceinline__ float gumbel_of(uint32_t r) {
   const float u = ((float)(r >> 9) + 0.5f) * (1.0f / 8388608.0f);  // exact: 24 significant bits
   return -logf(-logf(u));
 }
@@ -328,11 +327,49 @@ sample_rows_kernel(const float* __restrict__ logits, size_t ld, int* __restrict_
     const int k = top_k ? top_k[r] : 0;
     const float p = top_p ? top_p[r] : 1.f;
     const uint32_t thr = (k > 0 || p < 1.f) ? draw_threshold(row, V, k, p, inv_t, search) : 0u;
-    for_each_logit(row, V, [&](int v, float l) {
-      if (thr != 0u && float_key(l) < thr) return;
-      const float z = l * inv_t + gumbel((uint32_t)v, oi, sd);
-      if (better(z, v, bv, bi)) { bv = z; bi = v; }
-    });
+    // four consecutive logits share one call of the generator
+    auto draw4 = [&](int g, const float* l, int n) {
+      bool any = thr == 0u;
+      for (int i = 0; i < n && !any; ++i) any = float_key(l[i]) >= thr;
+      if (!any) return;
+      uint32_t rnd[4];
+      philox4((uint32_t)g, oi, sd, rnd);
+      for (int i = 0; i < n; ++i) {
+        if (thr != 0u && float_key(l[i]) < thr) continue;
+        const float z = l[i] * inv_t + gumbel_of(rnd[i]);
+        if (better(z, 4 * g + i, bv, bi)) { bv = z; bi = 4 * g + i; }
+      }
+    };
+    const int groups = V >> 2;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      constexpr int U = 4;  // groups a thread asks for at once
+      int g = threadIdx.x;
+      for (; g + (U - 1) * kSampleThreads < groups; g += U * kSampleThreads) {
+        float4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) x[u] = reinterpret_cast<const float4*>(row)[g + u * kSampleThreads];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float l[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+          draw4(g + u * kSampleThreads, l, 4);
+        }
+      }
+      for (; g < groups; g += kSampleThreads) {
+        const float4 x = reinterpret_cast<const float4*>(row)[g];
+        const float l[4] = {x.x, x.y, x.z, x.w};
+        draw4(g, l, 4);
+      }
+    } else {
+      for (int g = threadIdx.x; g < groups; g += kSampleThreads) {
+        const float l[4] = {row[4 * g], row[4 * g + 1], row[4 * g + 2], row[4 * g + 3]};
+        draw4(g, l, 4);
+      }
+    }
+    if (threadIdx.x == 0 && (V & 3)) {  // the last, short group
+      float l[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int i = 0; i < (V & 3); ++i) l[i] = row[4 * groups + i];
+      draw4(groups, l, V & 3);
+    }
   } else {
     for_each_logit(row, V, [&](int v, float z) {
       if (better(z, v, bv, bi)) { bv = z; bi = v; }

@@ -239,15 +239,17 @@ def philox4x32(counter, key):
 
 
 def gumbel_noise(seed: int, out_index: int, vocab: int) -> np.ndarray:
-    """G_v = -log(-log u_v), u_v from Philox(counter=(v, out_index, 0, 0), key=(seed, 0)).
+    """G_v = -log(-log u_v), u_v from word v % 4 of Philox(counter=(v // 4, out_index, 0, 0), key=(seed, 0)):
+    one call of the generator serves four consecutive token ids.
 
-    u = (top 23 bits of the first output word + 0.5) / 2^23, so 0 < u < 1 and u
-    is exact in 32-bit floating point.
+    u = (top 23 bits of the word + 0.5) / 2^23, so 0 < u < 1 and u is exact in 32-bit floating point.
     """
-    v = np.arange(vocab, dtype=np.uint64)
-    z = np.zeros(vocab, dtype=np.uint64)
-    r = philox4x32([v, z + np.uint64(out_index), z, z], [z + np.uint64(seed & 0xFFFFFFFF), z])
-    u = ((r[0] >> np.uint64(9)).astype(np.float64) + 0.5) / float(1 << 23)
+    groups = (vocab + 3) // 4
+    g = np.arange(groups, dtype=np.uint64)
+    z = np.zeros(groups, dtype=np.uint64)
+    r = philox4x32([g, z + np.uint64(out_index), z, z], [z + np.uint64(seed & 0xFFFFFFFF), z])
+    words = np.stack(r, axis=1).reshape(-1)[:vocab]
+    u = ((words >> np.uint64(9)).astype(np.float64) + 0.5) / float(1 << 23)
     return -np.log(-np.log(u))
 
 
