@@ -67,32 +67,28 @@ class Runtime:
             return out
         M, K = x.shape
         N = w.shape[0]
-        if M <= kernels.SKINNY_MAX_ROWS:
-            # A few tokens: the product is a stream of the weights.  Measured on B200 (graph-timed, weights
-            # larger than L2): the tcgen05 kernel wins where one block per 128 features fills the machine
-            # (gate|up, the vocabulary), the TMA-ring kernel with blocks of 16 features on everything
-            # smaller from K = 2048 on (q|k|v, o, down); for one or two tokens only where its blocks fit two
-            # per SM, else the tcgen05 kernel with K cut into slices (K >= 8192) or the register-streaming
-            # kernel, which also has the short K.
-            fits_tc = kernels.gemm_tc_fits(K, x, w)
-            if fits_tc and -(-N // 128) >= kernels.TC_TARGET_BLOCKS:
-                kernels.gemm_tc_bf16(out, x, w, 1, None, None, self.status)
-                return out
-            if (K >= kernels.FEWROWS_MIN_K and kernels.gemm_fewrows_fits(M, K, x, w)
-                    and (M > 2 or -(-N // 16) <= 2 * self.sm_count)):
-                kernels.gemm_fewrows_bf16(out, x, w, status=self.status)
-                return out
-            if kernels.gemm_skinny_fits(M, K, x, w) and not (fits_tc and K >= 8192):
-                kernels.gemm_skinny_bf16(out, x, w)
-                return out
-            if fits_tc:
-                splits = kernels.gemm_tc_splits(M, N, K)
-                partial = counters = None
-                if splits > 1:
-                    partial = self.scratch.get("tc_partial", (splits * kernels.SKINNY_MAX_ROWS * N,), torch.float32)
-                    counters = self.tc_counters
-                kernels.gemm_tc_bf16(out, x, w, splits, partial, counters, self.status)
-                return out
+        choice = "library"
+        if M <= kernels.SKINNY_MAX_ROWS:  # a few tokens: the product is a stream of the weights
+            choice = kernels.few_rows_product_kernel(
+                M, N, K, self.sm_count, kernels.gemm_tc_fits(K, x, w), kernels.gemm_fewrows_fits(M, K, x, w),
+                kernels.gemm_skinny_fits(M, K, x, w))
+        if choice == "tc":
+            kernels.gemm_tc_bf16(out, x, w, 1, None, None, self.status)
+            return out
+        if choice == "fewrows":
+            kernels.gemm_fewrows_bf16(out, x, w, status=self.status)
+            return out
+        if choice == "skinny":
+            kernels.gemm_skinny_bf16(out, x, w)
+            return out
+        if choice == "tc_split":
+            splits = kernels.gemm_tc_splits(M, N, K)
+            partial = counters = None
+            if splits > 1:
+                partial = self.scratch.get("tc_partial", (splits * kernels.SKINNY_MAX_ROWS * N,), torch.float32)
+                counters = self.tc_counters
+            kernels.gemm_tc_bf16(out, x, w, splits, partial, counters, self.status)
+            return out
         self.cublas.gemm_bf16(out, x, w)
         return out
 

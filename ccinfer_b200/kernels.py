@@ -536,6 +536,28 @@ def gemm_fewrows_bf16(c, a, w, swiglu: bool = False, status=None) -> None:
                                        1 if swiglu else 0, _p(status), _stream()), "gemm_fewrows_bf16")
 
 
+def few_rows_product_kernel(M: int, N: int, K: int, sm_count: int, fits_tc: bool, fits_fewrows: bool,
+                            fits_skinny: bool) -> str:
+    """Which kernel takes out[M, N] = x[M, K] @ w[N, K]^T in bfloat16: "tc", "tc_split", "fewrows", "skinny" or
+    "library".  Measured on B200 (graph-timed, weights larger than L2): with up to 16 tokens the tcgen05 kernel
+    wins where one block per 128 features fills the machine (gate|up, the vocabulary), the TMA-ring kernel
+    with blocks of 16 features on everything smaller from K = 2048 on (q|k|v, o, down); for one or two
+    tokens only where its blocks fit two per SM, else the tcgen05 kernel with K cut into slices (K >= 8192:
+    inside a step the register-streaming kernel was 40 us a layer slower there than alone) or the
+    register-streaming kernel, which also has the short K.  More tokens go to the library."""
+    if M > SKINNY_MAX_ROWS:
+        return "library"
+    if fits_tc and -(-N // 128) >= TC_TARGET_BLOCKS:
+        return "tc"
+    if K >= FEWROWS_MIN_K and fits_fewrows and (M > 2 or -(-N // 16) <= 2 * sm_count):
+        return "fewrows"
+    if fits_skinny and not (fits_tc and K >= 8192):
+        return "skinny"
+    if fits_tc:
+        return "tc_split"
+    return "library"
+
+
 class CublasHandle:
     """One cuBLAS handle with a caller-owned workspace (no allocation inside a step)."""
 

@@ -343,3 +343,23 @@ def test_random_workloads_with_and_without_running_ahead(seed):
     for rid, p, sp, _ in reqs:
         toks = calm[0].get(rid, [])
         assert len(toks) <= sp.max_tokens and len(p) + len(toks) <= max_context + 1
+
+
+def test_which_kernel_takes_a_few_rows_product():
+    """The measured rule, as a table: the shapes of the three model sizes at 1, 8 and 16 tokens."""
+    from ccinfer_b200 import kernels
+
+    def pick(M, N, K):
+        return kernels.few_rows_product_kernel(M, N, K, 148, True, True, K % 32 == 0)
+
+    # 8B: q|k|v 6144 x 4096, o 4096 x 4096, gate|up 24576 x 4096, down 4096 x 12288, vocabulary 151936 x 4096
+    assert [pick(8, *s) for s in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096))] == \
+        ["fewrows", "fewrows", "tc", "fewrows", "tc"]
+    assert [pick(1, *s) for s in ((6144, 4096), (4096, 4096), (4096, 12288))] == ["skinny", "fewrows", "fewrows"]
+    # 14B / 32B with one token: the ring kernel's blocks do not fit two per SM; long K goes to the tcgen05 kernel
+    assert [pick(1, *s) for s in ((7168, 5120), (5120, 5120), (5120, 17408), (5120, 8192))] == \
+        ["skinny", "skinny", "tc_split", "tc_split"]
+    assert [pick(16, *s) for s in ((7168, 5120), (5120, 17408), (34816, 5120))] == ["fewrows", "fewrows", "tc"]
+    # short K, more rows than the own kernels take, shapes no own kernel fits
+    assert pick(8, 4096, 1024) == "skinny" and pick(17, 4096, 4096) == "library"
+    assert kernels.few_rows_product_kernel(8, 4096, 4100, 148, False, False, False) == "library"
