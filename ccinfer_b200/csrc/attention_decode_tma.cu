@@ -229,7 +229,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
       if (lane < pages_per_tile) {
         const int lp = ((tile * kTileKeys) >> page_shift) + lane;
         int page = (lp <= lp_last && lp < bt_stride) ? bt[lp] : -1;
-        if (page < 0 || page >= num_pages) page = bt[lp_last];
+        if (page < 0 || page >= num_pages) {
+          // A page the tile reaches but no query of the row reads (before the window, beyond the position)
+          // is replaced by one that certainly exists and its keys are masked.  One that holds a visible key
+          // must be there: its absence is reported, not papered over.
+          const int k_lo = lp << page_shift;
+          if (k_lo <= p_seen && k_lo + page_size - 1 >= j0) set_status(status, CCB_ST_BAD_PAGE);
+          page = bt[lp_last];
+        }
         if (page < 0 || page >= num_pages) {
           set_status(status, CCB_ST_BAD_PAGE);
           page = 0;

@@ -137,7 +137,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     auto page_row = [&](int t) -> int {
       const int lp = (((first_tile + t) * kTK) >> page_shift) + lane;
       int page = (lp <= lp_last && lp < bt_stride) ? bt[lp] : -1;
-      if (page < 0 || page >= num_pages) page = bt[lp_last];
+      if (page < 0 || page >= num_pages) {
+        // stands in only for pages none of the tile's queries reads; a missing page with a visible key is reported
+        const int k_lo = lp << page_shift;
+        if (k_lo <= p_last && k_lo + page_size - 1 >= j_lo) set_status(status, CCB_ST_BAD_PAGE);
+        page = bt[lp_last];
+      }
       if (page < 0 || page >= num_pages) {
         set_status(status, CCB_ST_BAD_PAGE);
         page = 0;

@@ -44,6 +44,7 @@ GROUPS = {
         "gemm_tcgen05.cu",
         "gemm_fewrows.cu",
         "sampling.cu",
+        "random_init.cu",
     ],
 }
 GROUP_LIBS = {"core": ["-lcublas"]}
@@ -129,8 +130,8 @@ def library_path(group: str = "core", verbose: bool = True) -> str:
     th = threading.Thread(target=ticker, daemon=True)
     if verbose:
         th.start()
+    objs = [os.path.join(bdir, f"{group}_{os.path.splitext(s)[0]}.{os.getpid()}.o") for s in srcs]
     try:
-        objs = [os.path.join(bdir, f"{group}_{os.path.splitext(s)[0]}.{os.getpid()}.o") for s in srcs]
         with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
             futs = {ex.submit(_compile_one, nvcc, s, o): s for s, o in zip(srcs, objs)}
             for fut in concurrent.futures.as_completed(futs):
@@ -146,13 +147,13 @@ def library_path(group: str = "core", verbose: bool = True) -> str:
         with open(stamp_file + f".{os.getpid()}", "w") as f:
             f.write(stamp)
         os.replace(stamp_file + f".{os.getpid()}", stamp_file)
-        for o in objs:
+    finally:
+        done.set()
+        for o in objs:   # also after a failed build: no object files are left behind
             try:
                 os.unlink(o)
             except OSError:
                 pass
-    finally:
-        done.set()
     if verbose:
         _say(f"built {os.path.basename(lib)} in {time.time() - t0:.0f} s")
     return lib

@@ -79,6 +79,10 @@ class Engine:
             raise Unsupported(f"dtype {opt.dtype!r}: bfloat16 or float32") from None
         if opt.page_size <= 0:
             raise InvalidArgument("page_size must be > 0")
+        if not (0 < opt.max_requests <= opt.max_tokens_per_step):
+            # a step of max_requests single tokens (padded to a graph's size) must fit the token arrays
+            raise InvalidArgument(f"max_requests ({opt.max_requests}) must lie in 1 .. max_tokens_per_step "
+                                  f"({opt.max_tokens_per_step})")
         plan.validate()
         self.plan = plan
         self.vocab_size = plan.vocab_size
@@ -162,6 +166,7 @@ class Engine:
         self._pending_tokens = torch.zeros(opt.max_requests, dtype=torch.int32, device=rt.device)
         self._pending_slots = set()   # slots whose pending token is valid
         self._last_row_slot = None    # (device view, host list) of the most recent step's logits rows
+        self._last_logits = None      # (address, shape) of the logits that the most recent step returned
         self._sample_dev = torch.zeros((5, opt.max_tokens_per_step), dtype=torch.int32, device=rt.device)
         self.steps_run = 0
         self.graph_replays = 0
@@ -221,7 +226,7 @@ class Engine:
         if len(entries) > self.options.max_requests:
             raise InvalidArgument(f"{len(entries)} entries in a step, at most {self.options.max_requests}")
         seen = set()
-        total = 0
+        total = wanted = 0
         for e in entries:
             if e.req_id in seen:
                 raise InvalidArgument(f"request {e.req_id!r} appears twice in one step")
@@ -241,8 +246,11 @@ class Engine:
             for w in e.want:
                 if not (0 <= w < n):
                     raise InvalidArgument(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
+            wanted += len(e.want)
         if total > self.options.max_tokens_per_step:
             raise InvalidArgument(f"{total} tokens in a step, at most {self.options.max_tokens_per_step}")
+        if wanted > self.options.max_tokens_per_step:  # a place may be named twice: the rows have their own limit
+            raise InvalidArgument(f"{wanted} logits rows wanted in a step, at most {self.options.max_tokens_per_step}")
 
     def _build(self, entries: List[StepEntry], pad_to: int = 0) -> StepContext:
         """Fills the pinned buffer, copies it to the device and returns the views of the step."""
@@ -281,6 +289,8 @@ class Engine:
         pending = first < 0
         if pending.any():
             first[pending] = -1 - slots[:n_single][pending]  # resolved on the device from the pending tokens
+        # a pending token serves one step: this one reads it, or brings the request's token itself
+        self._pending_slots.difference_update(slots.tolist())
         tok[T:Tp] = 0
         posv[T:Tp] = 0
         eot[T:Tp] = -1
@@ -329,6 +339,7 @@ class Engine:
         step.row_slot = dv(lay.o_row_slot, max(R, 1))
         step.pending_tokens = self._pending_tokens
         self._last_row_slot = (step.row_slot, row_slots[:len(given)] if pad_to else row_slots)
+        self._last_logits = None   # set by step() once the logits exist
         step.cu_q = dv(lay.o_cu_q, Bp + 1)
         step.pos0 = dv(lay.o_pos0, Bp)
         step.ctx_after = dv(lay.o_ctx_after, Bp)
@@ -397,7 +408,8 @@ class Engine:
         are padding: they cache nothing and attend to nothing)."""
         step = self._build(entries, pad_to=bucket)
         if bucket not in self._graphs:
-            self._forward(step)  # once eagerly: every scratch buffer exists before the capture
+            self._forward(step)  # once eagerly: every scratch buffer exists before the capture ...
+            self.rt.scratch.freeze()  # ... and none may move once a graph holds its address
             graph = torch.cuda.CUDAGraph()
             own0, lib0 = kernels.counters.own, kernels.counters.library
             with torch.cuda.graph(graph):
@@ -455,6 +467,9 @@ class Engine:
         Either the whole step happens (every request's cached length grows by its
         token count) or nothing does: if pages run out (KVBlockExhausted) or a
         launch fails, the pages taken for the step are given back.
+
+        The logits are a view of a buffer of the engine: they stay valid until the
+        next step is launched (copy them to keep them longer).
         """
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
@@ -478,6 +493,7 @@ class Engine:
         self.steps_run += 1
         if logits is None:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.rt.device)
+        self._last_logits = (logits.data_ptr(), tuple(logits.shape))
         return logits
 
     def sample(self, logits: torch.Tensor, params: Sequence, out_index: Sequence[int]) -> List[int]:
@@ -498,7 +514,9 @@ class Engine:
         The tokens go to pinned host memory (``SampledTokens.tokens()`` waits for them) and stay on the
         device per request: the request's next entry may bring ``[PENDING]`` in place of the token, so the
         next step can be launched before this one's tokens have been read.  At most two results may be
-        outstanding."""
+        outstanding.  Only the tensor that the most recent ``step`` returned leaves its tokens with the
+        requests (a pending token serves the request's next step only); any other float [rows, vocab]
+        tensor is sampled without that."""
         R = logits.shape[0]
         if len(params) != R or len(out_index) != R:
             raise InvalidArgument("one parameter set and one output index per logits row")
@@ -508,8 +526,10 @@ class Engine:
             self._sample_events[turn].synchronize()  # the copies that used this turn's pinned buffers are over
         tokens = self._sample_tokens[:R]
         slot_dev = slots = None
-        if self._last_row_slot is not None and len(self._last_row_slot[1]) == R:
+        if (self._last_row_slot is not None and self._last_logits == (logits.data_ptr(), tuple(logits.shape))
+                and len(self._last_row_slot[1]) == R):
             slot_dev, slots = self._last_row_slot
+            self._last_logits = None   # the rows of a step leave their tokens once
         if R and all(p.temperature <= 0 for p in params):
             kernels.sample_rows(logits, tokens, slot_of_row=slot_dev, by_slot=self._pending_tokens)
         elif R:

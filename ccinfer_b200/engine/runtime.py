@@ -6,16 +6,20 @@ from typing import Dict, Tuple
 import torch
 
 from .. import kernels
-from ..errors import DeviceFault, ExtensionMissing, Unsupported
+from ..errors import DeviceFault, ExtensionMissing, ScratchMoved, Unsupported
 
 
 class ScratchPool:
-    """Named buffers that live as long as the engine and never move.
+    """Named buffers that live as long as the engine.
 
-    ``get(key, shape, dtype)`` returns the same storage for the same key, grown
-    only before the first step; parts ask for ``[max_tokens, width]`` once and
-    slice the rows of a step.  Layers of equal shape share a buffer by using the
-    same key, and fixed addresses let a decode step be replayed from a graph.
+    ``get(key, shape, dtype)`` returns the same storage for the same key; parts
+    ask for their largest shape (``[max_tokens, width]``) and slice the rows of a
+    step.  Layers share a buffer by using the same key; a key asked with a larger
+    size gets new storage, which is harmless until a CUDA graph has recorded the
+    old address.  The engine therefore runs a step eagerly (every key reaches the
+    largest size the model's parts ask for) and then calls ``freeze()`` before it
+    captures the first graph: from then on a request for more than a buffer holds
+    raises instead of moving it from under the graphs.
     """
 
     def __init__(self, device):
@@ -31,11 +35,16 @@ class ScratchPool:
         buf = self._bufs.get(full_key)
         if buf is None or buf.numel() < n:
             if self.frozen:
-                raise RuntimeError(f"scratch buffer '{key}' asked to grow after the pool was frozen "
-                                   f"({n} > {0 if buf is None else buf.numel()} elements)")
+                raise ScratchMoved(f"scratch buffer '{key}' ({dtype}) is asked for {n} elements after CUDA graphs "
+                                   f"recorded the addresses of the pool (it holds "
+                                   f"{0 if buf is None else buf.numel()}): a part must ask for its largest "
+                                   f"shape, not for the shape of the step")
             buf = torch.empty(n, dtype=dtype, device=self.device)
             self._bufs[full_key] = buf
         return buf[:n].view(shape)
+
+    def freeze(self) -> None:
+        self.frozen = True
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
@@ -100,13 +109,13 @@ class Runtime:
         M, K = x.shape
         N = w.shape[0]
         if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M <= kernels.SKINNY_MAX_ROWS
-                and kernels.gemm_tc_fits(K, x, w) and -(-N // 128) >= kernels.TC_TARGET_BLOCKS
+                and kernels.gemm_tc_fits(K, x, w) and -(-N // 128) >= self.sm_count
                 and kernels.gemm_tc_splits(M, N, K) == 1):
             kernels.gemm_tc_swiglu_bf16(act, x, w, self.status)
             return act
         if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M <= kernels.FEWROWS_MAX_ROWS
                 and K >= kernels.FEWROWS_MIN_K and N % 128 == 0 and kernels.gemm_fewrows_fits(M, K, x, w)
-                and -(-N // 128) < kernels.TC_TARGET_BLOCKS):
+                and -(-N // 128) < self.sm_count):
             kernels.gemm_fewrows_bf16(act, x, w, swiglu=True, status=self.status)
             return act
         gu = self.scratch.get("ffn_gate_up", (self.max_tokens, N), self.dtype)[:M]

@@ -66,3 +66,9 @@ class DeviceFault(CcinferError):
     """A kernel reported a bad index through the device status word."""
 
     code = "CudaLaunchFailed"
+
+
+class ScratchMoved(CcinferError):
+    """A part asked for a larger scratch buffer after CUDA graphs had recorded the pool's addresses."""
+
+    code = "InvalidState"

@@ -79,6 +79,7 @@ _SIGNATURES = {
                              c_void_p],
     "ccb_gemm_tc_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_void_p, c_void_p],
+    "ccb_init_random": [c_void_p, c_longlong, c_int, ctypes.c_ulonglong, ctypes.c_ulonglong, c_float, c_int, c_void_p],
     "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_int, c_void_p, c_void_p, c_int, c_void_p],
 }
@@ -272,7 +273,26 @@ def paged_attention_generic(q, k_cache, v_cache, out, positions, entry_of_token,
            "paged_attention_generic")
 
 
-SPLIT_TARGET_BLOCKS = 2 * 148   # blocks the split kernel aims for: two per SM
+B200_SM_COUNT = 148
+_sm_count = None
+
+
+def sm_count() -> int:
+    """SMs of the current CUDA device, asked once.  Without a device: a B200's number, so that the rules
+    that size grids can be tabulated on a CPU."""
+    global _sm_count
+    if _sm_count is None:
+        if not torch.cuda.is_available():
+            return B200_SM_COUNT
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sm_count
+
+
+def split_target_blocks() -> int:
+    """Blocks the split attention kernels aim for: two per SM."""
+    return 2 * sm_count()
+
+
 SPLIT_MAX = 32
 
 
@@ -288,8 +308,9 @@ def attention_split_plan(n_rows: int, nq: int, nkv: int, hd: int, heads_per_bloc
     launches the same grid (and its results do not depend on the lengths in the batch)."""
     gt = heads_per_block or attention_split_heads_per_block(nq, nkv, hd)
     per_split = n_rows * nkv * -(-(nq // nkv) // gt)
-    splits = max(1, min(SPLIT_MAX, SPLIT_TARGET_BLOCKS // max(1, per_split)))
-    return splits, SPLIT_TARGET_BLOCKS * gt * hd, SPLIT_TARGET_BLOCKS * gt * 2
+    target = split_target_blocks()
+    splits = max(1, min(SPLIT_MAX, target // max(1, per_split)))
+    return splits, target * gt * hd, target * gt * 2
 
 
 def attention_split(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
@@ -477,7 +498,12 @@ def gemm_skinny_bf16(c, a, w) -> None:
 
 
 TC_SWAP_MAX_ROWS = 64     # up to here the weights are the 128-row side of the tensor-core tile
-TC_TARGET_BLOCKS = 148    # one block per SM
+
+
+def tc_target_blocks() -> int:
+    """Blocks a tensor-core product of a few rows aims for: one per SM."""
+    return sm_count()
+
 
 
 def gemm_tc_fits(K: int, a, w) -> bool:
@@ -491,7 +517,7 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
         return 1
     tiles = -(-N // 128)
     kb = -(-K // 64)
-    s = max(1, min(-(-TC_TARGET_BLOCKS // tiles), kb // 4, 16))
+    s = max(1, min(-(-tc_target_blocks() // tiles), kb // 4, 16))
     while s > 1 and (s - 1) * (-(-kb // s)) >= kb:   # every slice must hold a k block
         s -= 1
     return s
@@ -547,7 +573,7 @@ def few_rows_product_kernel(M: int, N: int, K: int, sm_count: int, fits_tc: bool
     register-streaming kernel, which also has the short K.  More tokens go to the library."""
     if M > SKINNY_MAX_ROWS:
         return "library"
-    if fits_tc and -(-N // 128) >= TC_TARGET_BLOCKS:
+    if fits_tc and -(-N // 128) >= sm_count:
         return "tc"
     if K >= FEWROWS_MIN_K and fits_fewrows and (M > 2 or -(-N // 16) <= 2 * sm_count):
         return "fewrows"
@@ -607,3 +633,11 @@ def sample_rows(logits, tokens, temperature=None, seed=None, out_index=None, slo
     _check(lib().ccb_sample_rows(_p(logits), logits.stride(0), _p(tokens), _p(temperature), _p(seed),
                                  _p(out_index), _p(top_k), _p(top_p), R, V, _p(slot_of_row), _p(by_slot),
                                  0 if by_slot is None else by_slot.numel(), _stream()), "sample_rows")
+
+
+def init_random(out: torch.Tensor, seed: int, key: int, std: float, add_one: bool = False) -> None:
+    """out (float or bfloat16, contiguous) = std * z (+ 1), z ~ N(0, 1) from the counter-based stream of
+    (seed, key); the same bits as ``weights.random_init.normal_host`` (bfloat16: rounded once from float)."""
+    _cuda(out)
+    _check(lib().ccb_init_random(_p(out), out.numel(), _dt(out), int(seed) & (2 ** 64 - 1), int(key) & (2 ** 64 - 1),
+                                 float(std), 1 if add_one else 0, _stream()), "init_random")

@@ -1,6 +1,8 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w (7QiC/ccInfer: src/kernel/norm/rms_norm.cu:24-60)."""
 from __future__ import annotations
 
+import torch
+
 from .. import kernels
 from .base import Norm, Residual, TensorSpec
 
@@ -33,6 +35,6 @@ class RMSNorm(Norm):
         return y
 
     def apply(self, x):
-        y = self.rt.scratch.get(self.scratch_key + "_plain", tuple(x.shape), x.dtype)
+        y = torch.empty_like(x)  # the part alone, outside a step: not a buffer of the pool
         kernels.rmsnorm(y, x, self.w, self.eps)
         return y

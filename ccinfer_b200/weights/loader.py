@@ -5,7 +5,13 @@ As in 7QiC/ccInfer the model folder holds one ``model.safetensors``
 an expected shape (src/model/loader.h:87-155).  Unlike the reference, which
 stops at the first missing tensor and never looks at the others, the whole
 file is compared with the model's wants first and ONE error lists every
-missing tensor, every unexpected one and every wrong shape.
+missing tensor, every unexpected one and every wrong shape.  Tensors the model
+does not ask for are no fault by themselves (the reference never enumerates
+the file, src/model/qwen3/qwen3_weights.cpp:74-152, and checkpoints of tied
+models may still carry ``lm_head.weight`` or old rotary tables): alone they are
+reported by a warning and ``fetch.unexpected``; beside a real fault they are
+listed in the error, where a mistyped name shows up as one missing and one
+unexpected tensor.
 
 Types on the device: matrices in the compute type (bfloat16 for serving, float
 for the 32-bit path); per-channel vectors (norm weights) always in float, which
@@ -15,15 +21,16 @@ when the compute type is bfloat16.
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
+import warnings
 from typing import Callable, Dict, List
 
 import torch
 
 from ..errors import ModelLoadFailed
 from ..parts.base import TensorSpec
+from .random_init import normal_tensor
 from .safetensors_io import SafetensorsFile, write_safetensors
 
 WEIGHTS_FILE = "model.safetensors"
@@ -80,8 +87,9 @@ def open_checkpoint(model_dir: str):
                           f"or {INDEX_FILE} with its shards)")
 
 
-def check_tensors(specs: List[TensorSpec], entries: Dict[str, tuple], where: str) -> None:
-    """Raises ModelLoadFailed naming all missing, unexpected and mis-shaped tensors, or returns."""
+def check_tensors(specs: List[TensorSpec], entries: Dict[str, tuple], where: str, strict: bool = False) -> List[str]:
+    """Raises ModelLoadFailed naming all missing, unexpected and mis-shaped tensors, or returns the names
+    of the tensors that the file holds and the model does not want (with ``strict`` those raise as well)."""
     wanted = {s.name: s for s in specs}
     missing = sorted(n for n in wanted if n not in entries)
     unexpected = sorted(n for n in entries if n not in wanted)
@@ -96,8 +104,8 @@ def check_tensors(specs: List[TensorSpec], entries: Dict[str, tuple], where: str
             if integer != (s.role == "table"):
                 bad_type.append(f"{n}: stored as {entries[n][0]}, model wants "
                                 f"{'an integer table' if s.role == 'table' else 'floating point'}")
-    if not (missing or unexpected or wrong or bad_type):
-        return
+    if not (missing or wrong or bad_type or (strict and unexpected)):
+        return unexpected
     lines = [f"{where} does not match the model:"]
     if missing:
         lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
@@ -119,18 +127,24 @@ def device_dtype(spec: TensorSpec, compute_dtype: torch.dtype) -> torch.dtype:
 
 
 def open_weights(model_dir: str, specs: List[TensorSpec], device, compute_dtype,
-                 shared=()) -> Callable[[str], torch.Tensor]:
+                 shared=(), strict: bool = False) -> Callable[[str], torch.Tensor]:
     """Checks the folder's file against ``specs`` and returns ``fetch(name) -> device tensor``.
+
+    Tensors of the file that the model does not want are left alone: ``fetch.unexpected`` names them and a
+    warning says so once (``strict`` turns them into the load error).
 
     Names in ``shared`` (wanted by more than one part, like a tied head) are
     copied once and handed out again; every other call makes a fresh copy that
     the asking part owns."""
     f, path = open_checkpoint(model_dir)
     try:
-        check_tensors(specs, f.entries, path)
+        unexpected = check_tensors(specs, f.entries, path, strict=strict)
     except ModelLoadFailed:
         f.close()
         raise
+    if unexpected:
+        warnings.warn(f"{path}: {len(unexpected)} tensors that the model does not use are ignored: "
+                      + ", ".join(unexpected[:8]) + (" ..." if len(unexpected) > 8 else ""), stacklevel=2)
     by_name = {s.name: s for s in specs}
     cache: Dict[str, torch.Tensor] = {}
 
@@ -144,31 +158,23 @@ def open_weights(model_dir: str, specs: List[TensorSpec], device, compute_dtype,
         return t
 
     fetch.close = f.close  # type: ignore[attr-defined]
+    fetch.unexpected = unexpected  # type: ignore[attr-defined]
     return fetch
 
 
 # ---------------------------------------------------------------------------------------------
 # random weights
 # ---------------------------------------------------------------------------------------------
-def _tensor_seed(seed: int, name: str) -> int:
-    d = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(d[:8], "little") & ((1 << 63) - 1)
+def random_tensor(spec: TensorSpec, seed: int, std: float, device="cpu", dtype=torch.float32) -> torch.Tensor:
+    """One tensor of the random model: N(0, std), or 1 + N(0, std) for norm weights, in ``dtype``.
 
-
-def random_tensor(spec: TensorSpec, seed: int, std: float, device="cpu") -> torch.Tensor:
-    """Float values of one tensor: N(0, std), or 1 + N(0, std) for norm weights.
-
-    The stream depends on (seed, tensor name) only, so a tensor's values do not
-    change with the order or the number of the others.
+    The values are those of the counter-based stream of (seed, tensor name) (see ``random_init``): they do
+    not change with the order or the number of the other tensors, nor with where they are drawn; bfloat16
+    is the float value rounded once.
     """
-    g = torch.Generator(device=device)
-    g.manual_seed(_tensor_seed(seed, spec.name))
     if spec.role == "table":
         raise ModelLoadFailed(f"no random rule for the integer table '{spec.name}'")
-    t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * std
-    if spec.init == "one_plus_normal":
-        t += 1.0
-    return t
+    return normal_tensor(spec.shape, seed, spec.name, std, spec.init == "one_plus_normal", dtype, device)
 
 
 def write_random_model(model_dir: str, config, seed: int, std: float = 0.02, store_dtype: str = None) -> str:
@@ -202,7 +208,7 @@ def random_fetch(specs: List[TensorSpec], seed: int, std: float, device, compute
         if name in cache:
             return cache[name]
         spec = by_name[name]
-        t = random_tensor(spec, seed, std, device=device).to(device_dtype(spec, compute_dtype))
+        t = random_tensor(spec, seed, std, device=device, dtype=device_dtype(spec, compute_dtype))
         if name in shared:
             cache[name] = t
         return t

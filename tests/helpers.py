@@ -72,7 +72,7 @@ def trace_portions(reqs, sizes=(7, 2, 13, 3, 2, 5, 16, 2, 9)):
     return steps
 
 
-def trace_mixed(reqs, max_live=4, seed=0, prefill_frac=0.6):
+def trace_mixed(reqs, max_live=4, seed=0, prefill_frac=0.6, portion_choices=(2, 3, 5, 7, 11, 16)):
     """Up to ``max_live`` live requests; portions of some beside decoded tokens of others in one step.
 
     A request is first fed in portions of random size up to ``prefill_frac`` of its
@@ -92,7 +92,7 @@ def trace_mixed(reqs, max_live=4, seed=0, prefill_frac=0.6):
             if rng.rand() < 0.15 and len(live) > 1:
                 continue  # left out of this step, goes on later
             if cur < pend:
-                n = min(int(rng.choice([2, 3, 5, 7, 11, 16])), pend - cur)
+                n = min(int(rng.choice(list(portion_choices))), pend - cur)
             else:
                 n = 1
             entries.append({"id": rid, "tokens": toks[cur:cur + n], "want": list(range(n))})
@@ -102,6 +102,29 @@ def trace_mixed(reqs, max_live=4, seed=0, prefill_frac=0.6):
                 del live[rid]
         if entries:
             steps.append({"entries": entries, "end": end})
+    return steps
+
+
+def trace_many_decoders(reqs, decode_steps=6, per_prefill_step=5):
+    """All requests live at once: their prompts a few requests per step, then ``decode_steps`` steps in which
+    every request brings one token (steps of as many single-token rows as there are requests)."""
+    steps = []
+    rids = list(reqs)
+    for i in range(0, len(rids), per_prefill_step):
+        entries = []
+        for rid in rids[i:i + per_prefill_step]:
+            head = max(1, len(reqs[rid]) - decode_steps)
+            entries.append({"id": rid, "tokens": list(reqs[rid][:head]), "want": list(range(head))})
+        steps.append({"entries": entries, "end": []})
+    cursor = {rid: max(1, len(reqs[rid]) - decode_steps) for rid in rids}
+    while any(cursor[rid] < len(reqs[rid]) for rid in rids):
+        entries = []
+        for rid in rids:
+            if cursor[rid] < len(reqs[rid]):
+                entries.append({"id": rid, "tokens": [reqs[rid][cursor[rid]]], "want": [0]})
+                cursor[rid] += 1
+        steps.append({"entries": entries, "end": []})
+    steps[-1]["end"] = rids
     return steps
 
 

@@ -18,6 +18,11 @@ import torch
 
 F64 = torch.float64
 
+_PHILOX_M0 = 0xD2511F53
+_PHILOX_M1 = 0xCD9E8D57
+_PHILOX_W0 = 0x9E3779B9
+_PHILOX_W1 = 0xBB67AE85
+
 
 # ----------------------------------------------------------------------------
 # weights
@@ -64,12 +69,121 @@ def random_weights(cfg: dict, seed: int, std: float = 0.02) -> dict:
     return out
 
 
+def _mulhilo32(a: int, b: torch.Tensor):
+    """High and low 32 bits of a * b for a 32-bit constant a and 32-bit values b held in int64."""
+    bl, bh = b & 0xFFFF, b >> 16
+    lo_part = a * bl                       # < 2^48
+    mid = a * bh + (lo_part >> 16)         # < 2^49
+    hi = mid >> 16
+    lo = ((mid & 0xFFFF) << 16) | (lo_part & 0xFFFF)
+    return hi, lo
+
+
+def philox4x32_torch(c, k):
+    """Philox4x32-10 on int64 tensors holding 32-bit words; c = four counters, k = two keys (Python ints)."""
+    k0, k1 = k
+    c = list(c)
+    for _ in range(10):
+        hi0, lo0 = _mulhilo32(_PHILOX_M0, c[0])
+        hi1, lo1 = _mulhilo32(_PHILOX_M1, c[2])
+        c = [hi1 ^ c[1] ^ k0, lo1, hi0 ^ c[3] ^ k1, lo0]
+        k0, k1 = (k0 + _PHILOX_W0) & 0xFFFFFFFF, (k1 + _PHILOX_W1) & 0xFFFFFFFF
+    return c
+
+
+def _box_muller_f32(wa: torch.Tensor, wb: torch.Tensor):
+    """Two standard normal values from two 32-bit words, in single float operations only.
+
+    The engine's random-weights mode (7QiC/ccInfer has none: src/model/qwen3/qwen3_weights.cpp:49-51 loads
+    checkpoints only) defines its stream so that it can be restated anywhere:
+    u = ((wa >> 9) + 0.5) / 2^23; ln u = e ln 2 + ln m with u = m 2^e, m in (sqrt(1/2), sqrt 2],
+    ln m = 2 s (1 + s^2/3 + s^4/5 + s^6/7 + s^8/9 + s^10/11), s = (m - 1) / (m + 1); r = sqrt(-2 ln u);
+    the direction from the top 24 bits of wb: 3 bits of octant, 21 bits (+ 0.5) of x / (pi / 4), sine and
+    cosine of x by their Taylor polynomials, placed on the circle by the octant.
+    """
+    F = torch.float32
+    one = torch.tensor(1.0, dtype=F, device=wa.device)
+    u = ((wa >> 9).to(F) + 0.5) * (1.0 / 8388608.0)
+    bits = u.view(torch.int32)
+    e = (bits >> 23) - 127
+    m = ((bits & 0x7FFFFF) | 0x3F800000).view(F)
+    big = m > torch.tensor(1.41421354, dtype=F, device=wa.device)
+    m = torch.where(big, m * 0.5, m)
+    e = e + big.to(torch.int32)
+    s = (m - 1.0) / (m + 1.0)
+    s2 = s * s
+    poly = one / 11.0
+    for d in (9.0, 7.0, 5.0, 3.0):
+        poly = poly * s2 + one / d
+    poly = poly * s2
+    two_s = 2.0 * s
+    ln_u = e.to(F) * torch.tensor(0.693147182, dtype=F, device=wa.device) + (two_s + two_s * poly)
+    # the correctly rounded float square root: through float64, since torch's vectorised float sqrt on a
+    # CPU is not (a float64 root, even one unit off, rounds to the right float)
+    r = torch.sqrt((-2.0 * ln_u).double()).float()
+    k = wb >> 8
+    octant = k >> 21
+    x = ((k & 0x1FFFFF).to(F) + 0.5) * (1.0 / 2097152.0) * torch.tensor(0.785398185, dtype=F, device=wa.device)
+    x2 = x * x
+    ps = one / 362880.0
+    for num, d in ((-1.0, 5040.0), (1.0, 120.0), (-1.0, 6.0)):
+        ps = ps * x2 + (num * one) / d
+    sn = x + (x * x2) * ps
+    pc = -one / 3628800.0
+    for num, d in ((1.0, 40320.0), (-1.0, 720.0), (1.0, 24.0), (-1.0, 2.0)):
+        pc = pc * x2 + (num * one) / d
+    cs = 1.0 + x2 * pc
+    swap = (((octant + 1) >> 1) & 1).bool()
+    c = torch.where(swap, sn, cs)
+    sv = torch.where(swap, cs, sn)
+    c = torch.where((octant >= 2) & (octant <= 5), -c, c)
+    sv = torch.where(octant >= 4, -sv, sv)
+    return r * c, r * sv
+
+
+def stream_normal(numel: int, seed: int, name: str, std: float, add_one: bool, device="cpu",
+                  chunk: int = 1 << 22) -> torch.Tensor:
+    """float32 [numel] of the random-weights stream of (seed, tensor name): element i takes word i % 4 of
+    Philox4x32-10(counter = (i // 4 as two words, first 8 bytes of sha256(name) as two words),
+    key = seed as two words); words 0, 1 make elements 0, 1 of a group and words 2, 3 elements 2, 3."""
+    import hashlib
+    key = int.from_bytes(hashlib.sha256(name.encode()).digest()[:8], "little")
+    groups = (numel + 3) // 4
+    out = torch.empty(groups * 4, dtype=torch.float32, device=device)
+    for g0 in range(0, groups, chunk):
+        g = torch.arange(g0, min(groups, g0 + chunk), dtype=torch.int64, device=device)
+        n = g.numel()
+        full = lambda v: torch.full((n,), v, dtype=torch.int64, device=device)
+        w = philox4x32_torch([g & 0xFFFFFFFF, g >> 32, full(key & 0xFFFFFFFF), full(key >> 32)],
+                             (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
+        z0, z1 = _box_muller_f32(w[0], w[1])
+        z2, z3 = _box_muller_f32(w[2], w[3])
+        block = torch.stack([z0, z1, z2, z3], dim=1).reshape(-1) * torch.tensor(std, dtype=torch.float32, device=device)
+        if add_one:
+            block = block + 1.0
+        out[4 * g0:4 * g0 + block.numel()] = block
+    return out[:numel]
+
+
+def stream_weights(cfg: dict, seed: int, std: float = 0.02, device="cpu") -> dict:
+    """The random model that a seed names in the engine's random-weights mode: every tensor from its own
+    stream (``stream_normal``), norm weights 1 + N(0, std), all in float32."""
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        n = 1
+        for d in shape:
+            n *= d
+        norm = name.endswith("norm.weight") or name.endswith("layernorm.weight")
+        out[name] = stream_normal(n, seed, name, std, norm, device).view(shape)
+    return out
+
+
 # ----------------------------------------------------------------------------
 # parts
 # ----------------------------------------------------------------------------
 def embed(table: torch.Tensor, ids) -> torch.Tensor:
     """out[t, :] = table[ids[t], :]  (src/kernel/elementwise/elementwise.cu:67-78)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)]
+    return table[torch.as_tensor(ids, dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -101,7 +215,7 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor)
     x1' = x1 c + x0 s (src/kernel/pos/rope.cu:41-46).
     """
     half = x.shape[-1] // 2
-    angle = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).to(x.dtype)  # [T, half]
+    angle = (positions.to(torch.float32)[:, None] * inv_freq.to(positions.device)[None, :]).to(x.dtype)  # [T, half]
     c = torch.cos(angle)[:, None, :]
     s = torch.sin(angle)[:, None, :]
     x0, x1 = x[..., :half], x[..., half:]
@@ -120,7 +234,7 @@ def causal_attention(q, k, v, window=None) -> torch.Tensor:
     nkv = k.shape[1]
     group = nq // nkv
     scale = 1.0 / math.sqrt(hd)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window is not None:
         visible &= (pos[:, None] - pos[None, :]) < window
@@ -192,10 +306,11 @@ def forward(cfg: dict, weights: dict, tokens, dtype=F64) -> torch.Tensor:
     table as W_lm.
     """
     w = {k: v.to(dtype) for k, v in weights.items()}
+    device = w["model.embed_tokens.weight"].device   # the weights decide where it runs (a GPU for large shapes)
     eps = cfg.get("rms_norm_eps", 1e-6)
     T = len(tokens)
-    positions = torch.arange(T)
-    h = embed(w["model.embed_tokens.weight"], tokens)
+    positions = torch.arange(T, device=device)
+    h = embed(w["model.embed_tokens.weight"], torch.as_tensor(tokens, dtype=torch.long, device=device))
     for l in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{l}."
         x = rms_norm(h, w[p + "input_layernorm.weight"], eps)
@@ -216,12 +331,6 @@ def greedy(logits_row: torch.Tensor) -> int:
     """argmax, ties to the lowest id (src/kernel/sampling/sample.cu:32, 51-52)."""
     m = logits_row.max()
     return int(torch.nonzero(logits_row == m)[0, 0])
-
-
-_PHILOX_M0 = 0xD2511F53
-_PHILOX_M1 = 0xCD9E8D57
-_PHILOX_W0 = 0x9E3779B9
-_PHILOX_W1 = 0xBB67AE85
 
 
 def philox4x32(counter, key):

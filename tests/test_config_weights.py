@@ -164,6 +164,26 @@ def test_one_error_lists_everything(tmp_path):
     assert "wrong storage types (1)" in msg and "k_norm" in msg
 
 
+def test_extra_tensors_alone_are_no_fault(tmp_path):
+    """A tied checkpoint that still carries lm_head.weight and an old rotary table loads (the reference loads by
+    name and never looks at the rest: src/model/qwen3/qwen3_weights.cpp:74-152); strict loading refuses it."""
+    cfg = tiny_configs.TINY_A
+    specs = _specs(cfg)
+    tensors = {s.name: torch.zeros(s.shape, dtype=torch.bfloat16) for s in specs}
+    tensors["lm_head.weight"] = torch.zeros(256, 64)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    d = tmp_path / "extra"
+    d.mkdir()
+    write_safetensors(str(d / "model.safetensors"), tensors)
+    with pytest.warns(UserWarning, match="ignored"):
+        fetch = open_weights(str(d), specs, "cpu", torch.float32)
+    assert fetch.unexpected == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert fetch("model.norm.weight").shape == (64,)
+    fetch.close()
+    with pytest.raises(ModelLoadFailed, match=r"unexpected tensors \(2\)"):
+        open_weights(str(d), specs, "cpu", torch.float32, strict=True)
+
+
 def test_loader_types_on_load(tmp_path):
     cfg = tiny_configs.TINY_A
     specs = _specs(cfg)

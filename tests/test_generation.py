@@ -140,6 +140,16 @@ def test_running_ahead_reads_tokens_a_step_late_and_changes_none(model_b):
     lg = eng.step([StepEntry("z", [PENDING], [0])])          # launched before the first token is read
     second = eng.sample(lg, [SamplingParams()], [1])
     assert first.tokens() + second == plain.generate(cfg, w, prompts[0], 2)
+    # a pending token serves one step, and only the logits of the most recent step leave one
+    lg = eng.step([StepEntry("z", [second[0]], [0])])       # the token itself: the pending one is used up
+    with pytest.raises(InvalidArgument):
+        eng.step([StepEntry("z", [PENDING], [0])])
+    third = eng.sample_async(lg.clone(), [SamplingParams()], [2]).tokens()   # a copy is not the step's tensor
+    with pytest.raises(InvalidArgument):
+        eng.step([StepEntry("z", [PENDING], [0])])
+    assert eng.sample_async(lg, [SamplingParams()], [2]).tokens() == third
+    eng.step([StepEntry("z", [PENDING], [0])])
+    assert first.tokens() + second + third == plain.generate(cfg, w, prompts[0], 3)
     eng.close_request("z")
     eng.check()
 

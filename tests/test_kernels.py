@@ -142,6 +142,24 @@ def test_gemm_f32(M, N, K):
     assert torch.equal(c1[0], c[M - 1])
 
 
+@pytest.mark.parametrize("M,N,K", [(3, 6144, 4096), (70, 4096, 12288), (2, 151936, 4096)])
+def test_gemm_f32_at_the_sizes_of_a_large_model(M, N, K):
+    """The sums of the 8B layer shape: 4,096 and 12,288 terms, the vocabulary's 151,936 features (a sample
+    of them is compared in float64 on the GPU)."""
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    a = torch.randn((M, K), generator=g, device="cuda")
+    w = torch.randn((N, K), generator=g, device="cuda") * 0.02
+    c = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    _k().gemm_f32(c, a, w)
+    cols = torch.randperm(N, generator=g, device="cuda")[:4096]
+    ref = a.double() @ w[cols].double().T
+    assert _rel(c[:, cols], ref) <= 1e-5   # float accumulation over up to 12,288 terms against float64
+    assert _rel(c[:, N - 1:], a.double() @ w[N - 1:].double().T) <= 1e-5   # the last feature of a ragged tile
+    c1 = torch.empty((1, N), dtype=torch.float32, device="cuda")
+    _k().gemm_f32(c1, a[M - 1:M].contiguous(), w)
+    assert torch.equal(c1[0], c[M - 1])
+
+
 @pytest.mark.parametrize("out", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(1, 24, 40), (7, 304, 80), (64, 1000, 256), (200, 96, 512)])
 def test_gemm_bf16(out, M, N, K):
@@ -535,6 +553,25 @@ def test_attention_decode_tma_fused(case, splits, plain_keys):
     assert int(status.item()) == 0 and int(counters.abs().sum().item()) == 0
     live = [b for b in range(B) if b not in padding]
     assert _rel(got[live], want[live].double().cpu()) <= 1e-2
+    # and what the plain functions make of the same rows: norm, rotation, the cached keys of the request's
+    # pages followed by the new one, causal (windowed) attention of the last position
+    for b in live:
+        L = ctx[b] + 1
+        row = qkv[b].double().cpu()
+        qn = row[:nq * hd].view(1, nq, hd)
+        kn = row[nq * hd:(nq + nkv) * hd].view(1, nkv, hd)
+        vn = row[(nq + nkv) * hd:].view(1, nkv, hd)
+        if not plain_keys:
+            here = torch.tensor([ctx[b]])
+            qn = plain.apply_rope(plain.rms_norm(qn, qw.double().cpu(), eps), here, inv_freq.cpu())
+            kn = plain.apply_rope(plain.rms_norm(kn, kw.double().cpu(), eps), here, inv_freq.cpu())
+        pages = bt[b, :L // P + 1].long()
+        k_old = kc0.double().cpu()[pages].permute(0, 2, 1, 3).reshape(-1, nkv, hd)[:ctx[b]]
+        v_old = vc0.double().cpu()[pages].permute(0, 2, 1, 3).reshape(-1, nkv, hd)[:ctx[b]]
+        q_all = torch.zeros((L, nq, hd), dtype=torch.float64)
+        q_all[-1] = qn[0]
+        ref = plain.causal_attention(q_all, torch.cat([k_old, kn]), torch.cat([v_old, vn]), window)[-1]
+        assert _rel(got[b], ref) <= 1.5e-2, b
     assert float(got[list(padding)].abs().max()) == 0 if padding else True
     assert torch.equal(vc1, vc2)                                  # values are copied
     assert _rel(kc1, kc2.double().cpu()) <= 8e-3                   # keys: the same up to the rounding of the norm
@@ -600,6 +637,43 @@ def test_attention_decode_mma_window_edge(edge):
     for splits in (1, 4):
         out = _run_split(q, kc, vc, pos, eot, bt, 1, W, hd, splits, fn=_k().attention_decode_mma)
         assert _rel(out, ref) <= 1.5e-2
+
+
+@pytest.mark.parametrize("kernel", ["split", "decode_mma", "decode_tma", "prefill_mma", "prefill_tc"])
+def test_attention_reports_a_missing_page_with_a_visible_key(kernel):
+    """A block-table entry of -1 where a query reads keys: the status word says so (the TMA kernels stand a
+    page that certainly exists in for pages that a tile reaches but no query reads, never for a needed one).
+    The same entry behind a window is no fault and changes nothing."""
+    k = _k()
+    nq, nkv, hd, P, W = 4, 2, 128, 16, 100
+    prefill = kernel.startswith("prefill")
+    ctx, new = ([300], [70]) if prefill else ([299], [1])
+
+    def run(window, dead_page):
+        q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", ctx, new, nq, nkv, hd, P, seed=3, window=window)
+        bt = bt.clone()
+        bt[0, dead_page] = -1
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = torch.zeros_like(q)
+        scale = 1 / math.sqrt(hd)
+        if prefill:
+            cu = torch.tensor([0, new[0]], dtype=torch.int32, device="cuda")
+            pos0 = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+            getattr(k, "attention_" + kernel)(q, kc, vc, out, cu, pos0, bt, 0, 1, new[0], window or 0, scale, status)
+        else:
+            acc = torch.empty(nq * 4 * hd, dtype=torch.float32, device="cuda")
+            ml = torch.empty(nq * 4 * 2, dtype=torch.float32, device="cuda")
+            getattr(k, "attention_" + kernel)(q, kc, vc, out, acc, ml, pos, eot, bt, 1, 0, 1, window or 0, scale, 4,
+                                              status)
+        return int(status.item()), out, ref
+
+    word, _, _ = run(None, 3)             # keys 48..63 are read by every query
+    assert word == k.ST_BAD_PAGE
+    word, _, _ = run(W, 18)               # inside the window of the last queries
+    assert word == k.ST_BAD_PAGE
+    word, out, ref = run(W, 3)            # long before the window of the first query (position 300 - 99 = 201)
+    assert word == 0
+    assert _rel(out, ref) <= 1.5e-2
 
 
 PREFILL_CASES = [

@@ -371,3 +371,43 @@ def test_toy_routed_feed_forward_and_other_position_encodings(pos_kind):
     y = torch.stack([x[t] @ wd[f"moe.expert{int(e[t])}"].T * p[t, e[t]] for t in range(T)])
     ref = plain.rms_norm(h + y, wd["nf"], eps) @ wd["head"].T
     assert _rel(got, ref) <= 2e-5
+
+
+def test_scratch_that_follows_the_step_is_refused_once_a_graph_holds_it():
+    """A part that sizes its scratch by the step, not by its largest shape: after a decode step has been
+    captured, the step that would move the buffer from under the graph raises instead."""
+    from ccinfer_b200.engine.engine import Engine, EngineOptions, StepEntry
+    from ccinfer_b200.engine.plan import ModelPlan, RunEntry
+    from ccinfer_b200.errors import ScratchMoved
+    from ccinfer_b200.parts import OutputHead, PreNormBlock, RMSNorm, SwiGLU, TokenEmbedding
+    from ccinfer_b200.parts.base import Mixer, TensorSpec
+
+    class Careless(Mixer):
+        def __init__(self, dim):
+            self.dim = dim
+
+        def bind(self, rt, fetch):
+            self.rt = rt
+
+        def forward(self, x, step, cache, state):
+            out = self.rt.scratch.get("careless_out", tuple(x.shape), x.dtype)   # the step's shape: the fault
+            out.copy_(x)
+            return out
+
+    D, V, eps = 32, 41, 1e-6
+    block = PreNormBlock(RMSNorm(D, eps, "n1"), Careless(D), RMSNorm(D, eps, "n2"),
+                         SwiGLU(D, 64, {k: f"f.{k}" for k in ("gate", "up", "down")}))
+    plan = ModelPlan(TokenEmbedding(V, D, "emb"), [block], [RunEntry(0)], RMSNorm(D, eps, "nf"),
+                     OutputHead(D, V, "head"), V, 64)
+    w = _weights(plan.tensor_specs(), 2)
+    eng = Engine(plan, _fetch(w, plan.tensor_specs(), torch.float32),
+                 EngineOptions(dtype="float32", page_size=8, kv_tokens=64, max_requests=4, max_tokens_per_step=32))
+    eng.open_request("a")
+    eng.open_request("b")
+    eng.step([StepEntry("a", [1], [0])])          # a decode step of one row: captured, the pool is frozen
+    assert eng.graph_replays == 1 and eng.rt.scratch.frozen
+    eng.step([StepEntry("a", [2], [0])])          # the same shape: fine
+    with pytest.raises(ScratchMoved, match="careless_out"):
+        eng.step([StepEntry("a", [3], [0]), StepEntry("b", [4], [0])])
+    assert eng.context_len("a") == 2 and eng.context_len("b") == 0   # the refused step changed nothing
+    eng.cache.check_consistency()

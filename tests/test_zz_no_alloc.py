@@ -46,6 +46,23 @@ def _case(dtype, seed, B=3, ctx=(150, 40, 9), nq=8, nkv=2, hd=64, P=16):
     return q, kc, vc, pos, eot, bt.cuda()
 
 
+def _plain_attention(q, kc, vc, pos, bt):
+    """softmax(q k^T / sqrt(hd)) v in float64 for one query per request over its pages' first pos + 1 keys."""
+    B, nq, hd = q.shape
+    nkv, P = kc.shape[1], kc.shape[2]
+    out = torch.zeros((B, nq, hd), dtype=torch.float64)
+    for b in range(B):
+        L = int(pos[b]) + 1
+        pages = bt[b, :-(-L // P)].long().cpu()
+        k = kc.double().cpu()[pages].permute(0, 2, 1, 3).reshape(-1, nkv, hd)[:L]
+        v = vc.double().cpu()[pages].permute(0, 2, 1, 3).reshape(-1, nkv, hd)[:L]
+        for h in range(nq):
+            kh = h // (nq // nkv)
+            p = torch.softmax((k[:, kh] @ q[b, h].double().cpu()) / math.sqrt(hd), dim=0)
+            out[b, h] = p @ v[:, kh]
+    return out
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_no_alloc_entry_point_matches_the_allocating_one(dtype):
     from ccinfer_b200 import kernels
@@ -71,6 +88,10 @@ def test_no_alloc_entry_point_matches_the_allocating_one(dtype):
         assert torch.isfinite(got.float()).all()
         err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
         assert err <= (1e-5 if dtype == torch.float32 else 1.5e-2), f"call {call}: relative error {err}"
+        # and both against plain float64 attention of each row over the keys its block table names
+        ref = _plain_attention(q, kc, vc, pos, bt)
+        err = float((got.double().cpu() - ref).abs().max() / ref.abs().max())
+        assert err <= (1e-5 if dtype == torch.float32 else 1.5e-2), f"call {call}: relative error {err} to plain"
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
