@@ -5,15 +5,29 @@ inv_freq[i] = 1 / theta^(2i / head_dim), angle = float(pos) * inv_freq[i]
 (7QiC/ccInfer: src/model/rope/rope_cache.cpp:31-45, src/kernel/pos/rope.cu:41-46).
 The reference tabulates cos and sin for every position up to
 max_position_embeddings on the host; here only the inverse frequencies are a
-table (evaluated in float64, rounded once to float) and the kernel takes sine
-and cosine of the float angle, so no position bound comes from a table.
+table and the kernel takes sine and cosine of the float angle, so no position
+bound comes from a table.  The frequencies are evaluated as the reference
+does, in 32-bit steps: exponent = float(2i) / float(head_dim), theta^exponent
+rounded to float, 1.0f / that (a model trained with a 32-bit table sees the
+frequencies it was trained with; evaluating in float64 and rounding once gives
+another float for a third of the entries).  The power is taken in float64 and
+rounded, i.e. correctly rounded, where the reference's powf is within an ulp.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from .. import kernels
 from .base import PositionEncoding
+
+
+def rotary_inv_freq(rotary_dim: int, theta: float) -> np.ndarray:
+    """float32 [rotary_dim / 2]: 1.0f / powf(theta, float(2i) / float(rotary_dim)), every step in 32 bits
+    (src/model/rope/rope_cache.cpp:31-35)."""
+    exponent = np.arange(0, rotary_dim, 2, dtype=np.float32) / np.float32(rotary_dim)
+    power = np.power(np.float64(np.float32(theta)), exponent.astype(np.float64)).astype(np.float32)
+    return (np.float32(1.0) / power).astype(np.float32)
 
 
 class RotaryHalf(PositionEncoding):
@@ -26,9 +40,7 @@ class RotaryHalf(PositionEncoding):
 
     def bind(self, rt, fetch):
         self.rt = rt
-        i = torch.arange(0, self.head_dim, 2, dtype=torch.float64)
-        inv = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), i / self.head_dim)
-        self.inv_freq = inv.to(torch.float32).to(rt.device)
+        self.inv_freq = torch.from_numpy(rotary_inv_freq(self.head_dim, self.theta)).to(rt.device)
 
     def rotary_table(self):
         return self.inv_freq

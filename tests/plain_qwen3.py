@@ -198,13 +198,15 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def rope_inv_freq(head_dim: int, theta: float) -> torch.Tensor:
-    """inv_freq[i] = 1 / theta^(2i / head_dim), i < head_dim / 2.
+    """inv_freq[i] = 1.0f / powf(theta, float(2i) / float(head_dim)), i < head_dim / 2, in 32-bit steps as
+    src/model/rope/rope_cache.cpp:31-35 (and tests/kernel/test_rope.cu:15-28) evaluate it.
 
-    src/model/rope/rope_cache.cpp:31-35.  Evaluated in float64 and rounded
-    once to float32, which is what a 32-bit table holds.
+    The power is taken in float64 and rounded to float32 (the correctly rounded powf); compared with the
+    reference's own evaluation in tests/golden/parts_golden.npz.
     """
-    i = torch.arange(0, head_dim, 2, dtype=F64)
-    return (1.0 / torch.pow(torch.tensor(float(theta), dtype=F64), i / head_dim)).to(torch.float32)
+    exponent = torch.arange(0, head_dim, 2, dtype=torch.float32) / torch.tensor(float(head_dim), dtype=torch.float32)
+    power = torch.pow(torch.tensor(float(theta), dtype=torch.float32).double(), exponent.double()).float()
+    return torch.tensor(1.0, dtype=torch.float32) / power
 
 
 def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:

@@ -15,8 +15,8 @@ pytestmark = pytest.mark.gpu
 
 # relative to the largest logit of the request; bfloat16: about twice the worst a B200 run has shown for the
 # configuration (every test prints its own as "[worst] ...")
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
-TOL16 = {"A": 3e-2, "B": 3e-2, "C": 3e-2, "D": 3e-2, "E": 3e-2}
+TOL = {"float32": 2e-5}   # seen: 1.2e-6 at most
+TOL16 = {"A": 6e-3, "B": 1.3e-2, "C": 1.5e-2, "D": 1.5e-2, "E": 1.6e-2}   # seen: 2.6e-3, 6.4e-3, 7.5e-3, 7.1e-3, 8.0e-3
 
 
 def _tol(name, dtype):
@@ -107,7 +107,7 @@ def test_many_decoding_requests_match_plain(models, name, dtype, n_live, graphs)
     """Decode steps of 17 to 64 rows: from 17 rows on the products of the bfloat16 path go to the library,
     from 49 on the attention is no longer fused with the rotation and the cache write, and the graphs of 32
     and 64 rows are captured."""
-    d, cfg, page, _, _ = models[name]
+    d, cfg, page = models[name][:3]
     rng = np.random.RandomState(n_live)
     reqs = {f"m{i}": rng.randint(0, cfg["vocab_size"], size=int(rng.randint(8, 60))).tolist() for i in range(n_live)}
     weights = models[name][5]

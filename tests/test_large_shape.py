@@ -33,7 +33,7 @@ MID_SHAPE = {
 # relative to the largest logit of the request; bfloat16: about twice the worst seen on a B200 (printed by
 # every run as "[worst] ...")
 TOL32 = 2e-5
-TOL16 = {"8b": 2.5e-2, "mid": 2.5e-2}
+TOL16 = {"8b": 3e-2, "mid": 2.6e-2}   # seen: 1.5e-2, 1.3e-2 (and 8.4e-6, 4.5e-6 in 32-bit)
 
 
 class _Model:

@@ -122,3 +122,97 @@ def test_filtered_draws_stay_in_their_set_and_follow_the_renormalised_distributi
     counts = np.array([draws.count(t) for t in keep])
     chi2 = float(((counts - n * pk) ** 2 / (n * pk)).sum())
     assert chi2 < 30.0, chi2
+
+
+# ---------------------------------------------------------------------------------------------
+# The plain functions against what 7QiC/ccInfer's own CPU functions computed (tests/golden/parts_golden.npz,
+# made by tests/golden/make_parts_golden.py from the function bodies of the reference's kernel tests).
+# The reference computes in float and rounds its outputs to bfloat16; the plain functions compute in float64.
+# ---------------------------------------------------------------------------------------------
+import os
+
+import pytest
+
+BF16_ROUNDING = 2.0 ** -8     # half a unit in the last place of a bfloat16 value, relative, with room for float sums
+
+
+@pytest.fixture(scope="module")
+def golden():
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "parts_golden.npz"))
+    return {k: g[k] for k in g.files}
+
+
+def _close_to_bf16(got: torch.Tensor, ref: np.ndarray):
+    ref = torch.from_numpy(ref).double().view(got.shape)
+    return bool(((got.double() - ref).abs() <= BF16_ROUNDING * ref.abs() + 1e-6).all())
+
+
+def test_rms_norm_matches_the_references_cpu_function(golden):
+    g = golden
+    y = plain.rms_norm(torch.from_numpy(g["norm_x"]).double(), torch.from_numpy(g["norm_w"]).double(),
+                       float(g["size_NORM_EPS"]))
+    assert _close_to_bf16(y, g["norm_out"])
+
+
+def test_inverse_frequencies_match_the_references_evaluation(golden):
+    """1.0f / std::pow(theta, float(2i) / float(dim)) as src/model/rope/rope_cache.cpp:31-35 evaluates it:
+    equal in all but a few entries (1 of 432), where the reference's powf is one unit off the correctly rounded power."""
+    ref = golden["inv_freq"]
+    at = differ = 0
+    for theta in (1e4, 5e4, 1e6):
+        for dim in (16, 32, 48, 64, 128):
+            mine = plain.rope_inv_freq(dim, theta).numpy()
+            theirs = ref[at:at + dim // 2]
+            at += dim // 2
+            differ += int((mine != theirs).sum())
+            assert np.all(np.abs(mine - theirs) <= 2 * np.spacing(theirs))   # one unit of the power: two of 1 / power
+    assert at == ref.size and differ <= 2, differ
+
+
+def test_rotation_matches_the_references_cpu_function(golden):
+    g = golden
+    T, nq, nkv, hd = (int(g["size_ROPE_" + k]) for k in ("T", "NQ", "NKV", "HD"))
+    inv = plain.rope_inv_freq(hd, float(g["size_ROPE_THETA"]))
+    pos = torch.from_numpy(g["rope_pos"].astype(np.int64))
+    q = plain.apply_rope(torch.from_numpy(g["rope_q"]).double().view(T, nq, hd), pos, inv)
+    k = plain.apply_rope(torch.from_numpy(g["rope_k"]).double().view(T, nkv, hd), pos, inv)
+    assert _close_to_bf16(q, g["rope_q_out"]) and _close_to_bf16(k, g["rope_k_out"])
+
+
+def test_silu_mul_matches_the_references_cpu_function(golden):
+    g = golden
+    gate, up = torch.from_numpy(g["silu_g"]).double(), torch.from_numpy(g["silu_u"]).double()
+    # the activation of plain.swiglu, with identity projections around it
+    eye = torch.eye(gate.numel(), dtype=torch.float64)
+    act = plain.swiglu(torch.ones(1, 1, dtype=torch.float64), gate[:, None], up[:, None], eye)
+    assert _close_to_bf16(act.view(-1), g["silu_out"])
+
+
+def test_causal_attention_matches_the_references_cpu_function(golden):
+    g = golden
+    T, nq, nkv, hd = (int(g["size_ATT_" + k]) for k in ("T", "NQ", "NKV", "HD"))
+    o = plain.causal_attention(torch.from_numpy(g["att_q"]).double().view(T, nq, hd),
+                               torch.from_numpy(g["att_k"]).double().view(T, nkv, hd),
+                               torch.from_numpy(g["att_v"]).double().view(T, nkv, hd))
+    assert _close_to_bf16(o, g["att_out"])
+
+
+def test_attention_over_pages_matches_the_references_cpu_function(golden):
+    """One query per request over the keys that a block table names (the reference's cache layout:
+    [page * page_size + offset][kv head][head size]); the reference's function returns float."""
+    g = golden
+    B, nq, nkv, hd, P, stride = (int(g["size_DEC_" + k]) for k in ("B", "NQ", "NKV", "HD", "P", "STRIDE"))
+    kc = torch.from_numpy(g["dec_k"]).double().view(-1, P, nkv, hd)
+    vc = torch.from_numpy(g["dec_v"]).double().view(-1, P, nkv, hd)
+    q = torch.from_numpy(g["dec_q"]).double().view(B, nq, hd)
+    bt = g["dec_bt"].reshape(B, stride)
+    ref = torch.from_numpy(g["dec_out"]).double().view(B, nq, hd)
+    for b in range(B):
+        L = int(g["dec_ctx"][b])
+        pages = torch.from_numpy(bt[b, :-(-L // P)].astype(np.int64))
+        k = kc[pages].reshape(-1, nkv, hd)[:L]
+        v = vc[pages].reshape(-1, nkv, hd)[:L]
+        q_all = torch.zeros((L, nq, hd), dtype=torch.float64)
+        q_all[-1] = q[b]
+        o = plain.causal_attention(q_all, k, v)[-1]
+        assert float((o - ref[b]).abs().max()) <= 2e-6 * float(ref[b].abs().max()) + 1e-6
