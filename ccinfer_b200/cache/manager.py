@@ -20,8 +20,8 @@ Beyond the reference:
   per-request state tensors of fixed size (for mixers that have such state)
   and is returned when the request is closed.
 
-Everything here is host-side bookkeeping; the device tensors belong to
-engine.CacheStorage.
+Everything here is host-side bookkeeping; the device tensors (one set per
+layer that keeps a cache) belong to the engine.
 """
 from __future__ import annotations
 

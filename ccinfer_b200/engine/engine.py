@@ -59,9 +59,10 @@ class EngineOptions:
     dtype: object = "bfloat16"
     device: str = "cuda:0"
     page_size: int = 16              # tokens per cache page (the reference's constant, src/cache/block.h:9)
-    kv_tokens: Optional[int] = None  # tokens the cache pool of each group holds; default 1024 pages as the reference
+    kv_tokens: Optional[int] = None  # tokens the pool of a group that keeps every token holds; default 1024 pages
     kv_memory_fraction: Optional[float] = None  # instead of kv_tokens: this share of the memory that is free once
                                                 # the weights are on the device goes to the cache pools
+    kv_group_tokens: Optional[dict] = None      # tokens of single groups' pools, by group key: {("window", 40): 256}
     max_requests: int = 64           # live requests = state slots (src/worker/worker.h:102)
     max_tokens_per_step: int = 4096  # the reference's compute budget (src/scheduler/scheduler.cpp:25)
     max_context: Optional[int] = None  # longest request; default min(model limit, pool)
@@ -95,30 +96,13 @@ class Engine:
         P = opt.page_size
         if opt.kv_tokens is not None and opt.kv_memory_fraction is not None:
             raise InvalidArgument("give kv_tokens or kv_memory_fraction, not both")
-        if opt.kv_memory_fraction is not None:
-            if not (0.0 < opt.kv_memory_fraction <= 1.0):
-                raise InvalidArgument("kv_memory_fraction lies in (0, 1]")
-            elt = torch.empty((), dtype=self.dtype).element_size()
-            page_bytes = 0   # of one page in every pool: keys and values of every entry that keeps its own
-            for e in plan.order:
-                need = plan.layers[e.layer].mixer.cache_need()
-                if e.cache_of is None and need is not None:
-                    page_bytes += 2 * need.kv_heads * P * need.head_dim * elt
-            free_bytes = torch.cuda.mem_get_info(rt.device)[0]
-            num_pages = max(1, int(free_bytes * opt.kv_memory_fraction) // max(page_bytes, 1))
-        else:
-            kv_tokens = opt.kv_tokens if opt.kv_tokens is not None else 1024 * P
-            num_pages = max(1, -(-kv_tokens // P))
-        limit = num_pages * P
-        if plan.max_position is not None:
-            limit = min(limit, plan.max_position)
-        self.max_context = min(opt.max_context, limit) if opt.max_context else limit
         group_keys: List[tuple] = []
+        windows: List[Optional[int]] = []
+        token_bytes: List[int] = []   # per group: bytes one token costs in all its layers
+        owners: Dict[int, object] = {}  # run entry -> its CacheNeed
         self._entry_group: Dict[int, int] = {}
-        self._cache_k: Dict[int, torch.Tensor] = {}
-        self._cache_v: Dict[int, torch.Tensor] = {}
+        self._cache: Dict[int, Dict[str, torch.Tensor]] = {}
         self._state: Dict[int, torch.Tensor] = {}
-        windows = []
         for i, e in enumerate(plan.order):
             mixer = plan.layers[e.layer].mixer
             need = mixer.cache_need()
@@ -128,13 +112,16 @@ class Engine:
                 if getattr(mixer, "own_kv", False):
                     raise InvalidArgument(f"order[{i}] reads another entry's cache but its mixer writes keys")
             elif need is not None:
+                if len({t.name for t in need.tensors}) != len(need.tensors) or not need.tensors:
+                    raise InvalidArgument(f"order[{i}]: a cache need names at least one tensor, each once")
                 if need.group_key not in group_keys:
                     group_keys.append(need.group_key)
                     windows.append(need.window)
-                self._entry_group[i] = group_keys.index(need.group_key)
-                shape = (num_pages, need.kv_heads, P, need.head_dim)
-                self._cache_k[i] = torch.zeros(shape, dtype=self.dtype, device=rt.device)
-                self._cache_v[i] = torch.zeros(shape, dtype=self.dtype, device=rt.device)
+                    token_bytes.append(0)
+                g = group_keys.index(need.group_key)
+                self._entry_group[i] = g
+                token_bytes[g] += need.bytes_per_token(self.dtype)
+                owners[i] = need
             sn = mixer.state_need()
             if sn is not None:
                 self._state[i] = torch.zeros((opt.max_requests,) + tuple(sn.shape), dtype=sn.dtype, device=rt.device)
@@ -143,7 +130,19 @@ class Engine:
                 if e.cache_of not in self._entry_group:
                     raise InvalidArgument(f"order[{i}] reads the cache of entry {e.cache_of}, which keeps none")
                 self._entry_group[i] = self._entry_group[e.cache_of]
-        self.cache = CacheManager([GroupSpec(k, w, P, num_pages) for k, w in zip(group_keys, windows)],
+        pages = self._pages_per_group(opt, group_keys, windows, token_bytes)
+        for i, need in owners.items():
+            n = pages[self._entry_group[i]]
+            self._cache[i] = {t.name: torch.zeros((n,) + t.page_shape(P), dtype=t.dtype or self.dtype, device=rt.device)
+                              for t in need.tensors}
+        # the longest request: what the smallest pool of a group that keeps every token holds (a window group
+        # gives pages back as a request moves on and bounds no length), and the model's own limit
+        all_keys = [n for n, w in zip(pages, windows) if w is None]
+        limit = (min(all_keys) if all_keys else self._base_pages(opt, P)) * P
+        if plan.max_position is not None:
+            limit = min(limit, plan.max_position)
+        self.max_context = min(opt.max_context, limit) if opt.max_context else limit
+        self.cache = CacheManager([GroupSpec(k, w, P, n) for k, w, n in zip(group_keys, windows, pages)],
                                   opt.max_requests)
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in plan.parts())
 
@@ -171,6 +170,50 @@ class Engine:
         self.steps_run = 0
         self.graph_replays = 0
         self._graphs: Dict[int, tuple] = {}
+
+    @staticmethod
+    def _base_pages(opt: "EngineOptions", P: int) -> int:
+        kv_tokens = opt.kv_tokens if opt.kv_tokens is not None else 1024 * P
+        return max(1, -(-kv_tokens // P))
+
+    def _pages_per_group(self, opt, group_keys, windows, token_bytes) -> List[int]:
+        """Pages of each cache group's pool, from what a token costs there and a budget.
+
+        A group that keeps every token gets ``kv_tokens`` tokens (default 1024 pages, the reference's pool:
+        src/worker/worker.cpp:272), or its share of ``kv_memory_fraction`` of the free memory.  A window
+        group never needs more than what ``max_requests`` requests can hold at once, the window plus the
+        step's new tokens each, and gets no more than that.  ``kv_group_tokens`` sets single groups by their
+        key (("all",) or ("window", W)).
+        """
+        P = opt.page_size
+        explicit = dict(opt.kv_group_tokens or {})
+        for key in explicit:
+            if tuple(key) not in group_keys:
+                raise InvalidArgument(f"kv_group_tokens names the group {key!r}; the model has {group_keys}")
+
+        def window_cap(w):
+            return opt.max_requests * (w // P + 2) + -(-opt.max_tokens_per_step // P)
+
+        if opt.kv_memory_fraction is not None:
+            if not (0.0 < opt.kv_memory_fraction <= 1.0):
+                raise InvalidArgument("kv_memory_fraction lies in (0, 1]")
+            budget = int(torch.cuda.mem_get_info(self.rt.device)[0] * opt.kv_memory_fraction)
+            page_bytes = [b * P for b in token_bytes]
+            capped = [window_cap(w) if w is not None else None for w in windows]
+            fixed = sum(c * pb for c, pb in zip(capped, page_bytes) if c is not None)
+            open_bytes = sum(pb for c, pb in zip(capped, page_bytes) if c is None)
+            if fixed > budget // 2:   # the window groups would take most of it: every group the same count instead
+                each = max(1, budget // max(1, sum(page_bytes)))
+                pages = [min(each, c) if c is not None else each for c in capped]
+            else:
+                each = max(1, (budget - fixed) // max(1, open_bytes))
+                pages = [c if c is not None else each for c in capped]
+        else:
+            base = self._base_pages(opt, P)
+            pages = [base if w is None else min(base, window_cap(w)) for w in windows]
+        for key, tokens in explicit.items():
+            pages[group_keys.index(tuple(key))] = max(1, -(-int(tokens) // P))
+        return pages
 
     # ------------------------------------------------------------------------------------
     @classmethod
@@ -382,8 +425,7 @@ class Engine:
             cache = None
             if i in self._entry_group:
                 src = i if e.cache_of is None else e.cache_of
-                cache = LayerCache(self._cache_k[src], self._cache_v[src], step.groups[self._entry_group[i]],
-                                   own=e.cache_of is None)
+                cache = LayerCache(self._cache[src], step.groups[self._entry_group[i]], own=e.cache_of is None)
             block.forward(stream, step, cache, self._state.get(i))
         if step.n_logit_rows == 0:
             return None

@@ -126,8 +126,10 @@ class Scheduler:
         if len(prompt) > self.engine.max_context:
             raise RequestTooLong(f"a prompt of {len(prompt)} tokens exceeds the longest context "
                                  f"{self.engine.max_context}")
-        pool_tokens = min(g.num_pages * g.page_size for g in self.engine.cache.groups) \
-            if self.engine.cache.groups else None
+        # a group that keeps every token must be able to hold the prompt (a window group gives pages back as the
+        # request moves on: its pool bounds the size of a portion, not the length of a prompt)
+        pool_tokens = min((g.num_pages * g.page_size for g in self.engine.cache.groups if g.window is None),
+                          default=None)
         if pool_tokens is not None and len(prompt) > pool_tokens:
             raise RequestTooLong(f"a prompt of {len(prompt)} tokens can never fit the cache pool of "
                                  f"{pool_tokens} tokens")

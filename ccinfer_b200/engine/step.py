@@ -23,7 +23,7 @@ The reference finds a token's request by a linear scan of query_start_loc
 from __future__ import annotations
 
 import dataclasses
-from typing import List, Optional
+from typing import Dict, List, Optional
 
 import numpy as np
 import torch
@@ -44,11 +44,20 @@ class GroupStep:
 
 @dataclasses.dataclass
 class LayerCache:
-    """What a mixer gets of the cache: its key and value pages and its group's step arrays."""
-    k: torch.Tensor              # [pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    """What a mixer gets of the cache: the paged tensors it asked for in ``cache_need()`` (by name, each
+    [pages, *page shape]) and its group's step arrays."""
+    tensors: Dict[str, torch.Tensor]
     group: GroupStep
     own: bool                    # False: the pages belong to another run entry; read only
+
+    @property
+    def k(self) -> torch.Tensor:
+        """Keys of an attention layer: [pages, kv_heads, page_size, head_dim]."""
+        return self.tensors["k"]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.tensors["v"]
 
 
 class StepContext:

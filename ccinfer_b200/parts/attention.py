@@ -9,7 +9,10 @@
 The three projections are one merged matrix (rows q, then k, then v), as the
 reference merges them at load (src/model/qwen3/qwen3_weights.cpp:16-43).  A
 layer that reads another layer's cache (``own_kv=False``) has only the q and
-o projections.
+o projections (and must use the position encoding of the layer whose keys it
+reads).  Head sizes are multiples of 16 up to 256: others are refused (the
+reference's decode kernel takes any head size up to 128,
+src/kernel/attention/decode_attn.cu:521-569).
 """
 from __future__ import annotations
 
@@ -55,20 +58,46 @@ class GroupedQueryAttention(Mixer):
         return specs
 
     def cache_need(self):
-        return CacheNeed(kv_heads=self.nkv, head_dim=self.hd, window=self.window)
+        return CacheNeed.keys_and_values(self.nkv, self.hd, self.window)
 
     def bind(self, rt, fetch):
         self.rt = rt
         n = self.names
-        if self.own_kv:
-            self.w_qkv = torch.cat([fetch(n["q"]), fetch(n["k"]), fetch(n["v"])], dim=0).contiguous()
+        self.position.bind(rt, fetch)
+        if self.position.score_bias() is not None:
+            raise Unsupported("a position encoding that adds to the scores: the attention kernels take rotations "
+                              "of q and k only")
+        table = self.position.rotary_table()
+        if table is not None and (table.dtype != torch.float32 or table.numel() != self.hd // 2):
+            raise Unsupported(f"a rotary table of {self.hd // 2} float frequencies is wanted for head size "
+                              f"{self.hd}, the position encoding gives {tuple(table.shape)} {table.dtype}")
+        # the encoding's own pairing of coordinates, brought into the kernels' layout (pairs (j, j + hd / 2))
+        # by permuting the rows of the query and key projections and the head norms' weights alike
+        perm = self.position.head_permutation()
+        if perm is not None:
+            if sorted(perm) != list(range(self.hd)):
+                raise Unsupported(f"head_permutation() must name each of the {self.hd} coordinates once")
+            idx = torch.tensor(perm, device=rt.device)
+
+            def heads(w, n_heads):
+                return w.view(n_heads, self.hd, -1)[:, idx, :].reshape(n_heads * self.hd, -1)
         else:
-            self.w_qkv = fetch(n["q"])
+            idx = None
+
+            def heads(w, n_heads):
+                return w
+        if self.own_kv:
+            self.w_qkv = torch.cat([heads(fetch(n["q"]), self.nq), heads(fetch(n["k"]), self.nkv), fetch(n["v"])],
+                                   dim=0).contiguous()
+        else:
+            self.w_qkv = heads(fetch(n["q"]), self.nq).contiguous()
         self.w_o = fetch(n["o"])
         if self.qk_norm_eps is not None:
             self.q_norm_w = fetch(n["q_norm"])
             self.k_norm_w = fetch(n["k_norm"]) if self.own_kv else None
-        self.position.bind(rt, fetch)
+            if idx is not None:
+                self.q_norm_w = self.q_norm_w[idx].contiguous()
+                self.k_norm_w = self.k_norm_w[idx].contiguous() if self.k_norm_w is not None else None
 
     def _attend(self, q, o, cache, step, T):
         """Attention of every token row of the step over its request's pages.

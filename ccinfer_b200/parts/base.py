@@ -16,8 +16,8 @@ What a part must provide:
 
 A mixer further says what it needs to remember between steps:
 
-* ``cache_need()``: keys and values per token, kept in pages (all of them, or a
-  window), or None;
+* ``cache_need()``: the tensors it keeps per token, in pages (of all tokens, or
+  of a window of them), or None;
 * ``state_need()``: a tensor of fixed size per request, or None.
 """
 from __future__ import annotations
@@ -40,22 +40,57 @@ class TensorSpec:
 
 
 @dataclasses.dataclass(frozen=True)
-class CacheNeed:
-    """Keys and values of every token, kept in pages.
+class CachedTensor:
+    """One tensor a mixer keeps per token, in pages.
 
-    ``window`` None: a query may read every earlier key, pages live as long as
-    the request.  ``window`` W: a query at position p reads keys p-W+1 .. p;
+    ``shape`` is that of one token; a page holds ``page_size`` tokens along a new axis put at ``token_axis``
+    of it: keys of shape (kv_heads, head_dim) with token_axis 1 live in [pages, kv_heads, page_size, head_dim]
+    (one (page, head) is a contiguous tile), a latent vector of shape (r,) with token_axis 0 in
+    [pages, page_size, r], where row ``slot_map[t]`` of the [pages * page_size, r] view is token t's.
+    ``dtype`` None: the engine's compute type.
+    """
+    name: str
+    shape: Tuple[int, ...]
+    token_axis: int = 0
+    dtype: Optional[torch.dtype] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        if not (0 <= self.token_axis <= len(self.shape)):
+            raise ValueError(f"cached tensor '{self.name}': token_axis {self.token_axis} outside its shape {self.shape}")
+        return tuple(self.shape[:self.token_axis]) + (int(page_size),) + tuple(self.shape[self.token_axis:])
+
+    def bytes_per_token(self, compute_dtype: torch.dtype) -> int:
+        n = 1
+        for d in self.shape:
+            n *= int(d)
+        return n * torch.empty((), dtype=self.dtype or compute_dtype).element_size()
+
+
+@dataclasses.dataclass(frozen=True)
+class CacheNeed:
+    """What a mixer keeps of every token, in pages: any number of named tensors.
+
+    ``window`` None: a query may read every earlier token, pages live as long as
+    the request.  ``window`` W: a query at position p reads tokens p-W+1 .. p;
     pages wholly before that are given back while the request runs.  Layers
     with equal (window) share a page pool and block tables (a cache group);
-    each layer has its own key and value tensors of its own geometry.
+    each layer has its own tensors of its own geometry.
     """
-    kv_heads: int
-    head_dim: int
+    tensors: Tuple[CachedTensor, ...]
     window: Optional[int] = None
+
+    @classmethod
+    def keys_and_values(cls, kv_heads: int, head_dim: int, window: Optional[int] = None) -> "CacheNeed":
+        """Keys "k" and values "v" of an attention layer: [pages, kv_heads, page_size, head_dim] each."""
+        shape = (int(kv_heads), int(head_dim))
+        return cls((CachedTensor("k", shape, token_axis=1), CachedTensor("v", shape, token_axis=1)), window)
 
     @property
     def group_key(self):
         return ("window", self.window) if self.window is not None else ("all",)
+
+    def bytes_per_token(self, compute_dtype: torch.dtype) -> int:
+        return sum(t.bytes_per_token(compute_dtype) for t in self.tensors)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -103,9 +138,32 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """How positions enter a mixer.
+
+    The attention kernels know ONE rotation: pairs (j, j + head_dim / 2) of a head turned by the angle
+    position * table[j].  Every encoding of the rotary family fits that form through two things it states:
+
+    * ``rotary_table()``: float [head_dim / 2], the inverse frequency of each of the kernels' pairs (0 = the
+      pair is not rotated), or None for no rotation at all;
+    * ``head_permutation()``: which of the head's own coordinates sits at each place of the kernels' layout
+      (None = as they are).  A mixer applies it to the rows of its query and key projections (and to the
+      per-head norm weights) when it binds its weights; scores q.k do not change when q and k are permuted
+      alike, values are not touched.  Partial rotation (the first r coordinates, pairs (i, i + r / 2)) and
+      interleaved pairs (2i, 2i + 1) are permutations plus a table; see ``parts.position``.
+
+    An encoding that changes scores by something else than a rotation of q and k (a bias that depends on
+    the distance, say) states it in ``score_bias()``; the attention kernels here have no such argument and
+    the package's mixer refuses it.
+    """
+
     def rotary_table(self) -> Optional[torch.Tensor]:
-        """Float inverse frequencies [head_dim / 2] for a rotate-half rotation, or None for none."""
         raise NotImplementedError
+
+    def head_permutation(self) -> Optional[List[int]]:
+        return None
+
+    def score_bias(self):
+        return None
 
 
 class Mixer(Part):

@@ -31,26 +31,58 @@ def rotary_inv_freq(rotary_dim: int, theta: float) -> np.ndarray:
 
 
 class RotaryHalf(PositionEncoding):
-    def __init__(self, head_dim: int, theta: float):
-        if head_dim % 2:
-            raise ValueError("rotate-half needs an even head size")
-        self.head_dim, self.theta = int(head_dim), float(theta)
+    """Rotate-half rotation of the first ``rotary_dim`` coordinates of a head (default: all of them, as the
+    reference: src/kernel/pos/rope.cu:37-46 pairs (i, i + head_dim / 2)).
+
+    ``rotary_dim`` < head_dim: pairs (i, i + rotary_dim / 2), the other coordinates pass through.
+    ``interleaved``: pairs (2i, 2i + 1) instead.  Both are a permutation of the head's coordinates into the
+    kernels' layout plus a table with zeros for the pairs that do not turn (see PositionEncoding).
+    """
+
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, interleaved: bool = False):
+        rotary_dim = int(head_dim if rotary_dim is None else rotary_dim)
+        if head_dim % 2 or rotary_dim % 2 or not (0 < rotary_dim <= head_dim):
+            raise ValueError(f"rotation of {rotary_dim} of {head_dim} coordinates: both even, 0 < rotary_dim <= head_dim")
+        self.head_dim, self.theta, self.rotary_dim, self.interleaved = int(head_dim), float(theta), rotary_dim, interleaved
         self.inv_freq = None
         self.rt = None
 
     def bind(self, rt, fetch):
         self.rt = rt
-        self.inv_freq = torch.from_numpy(rotary_inv_freq(self.head_dim, self.theta)).to(rt.device)
+        table = np.zeros(self.head_dim // 2, dtype=np.float32)
+        table[:self.rotary_dim // 2] = rotary_inv_freq(self.rotary_dim, self.theta)
+        self.inv_freq = torch.from_numpy(table).to(rt.device)
 
     def rotary_table(self):
         return self.inv_freq
 
+    def head_permutation(self):
+        hd, rd, half = self.head_dim, self.rotary_dim, self.head_dim // 2
+        if rd == hd and not self.interleaved:
+            return None
+        # the kernels' pair j is places (j, j + half): the rotated pairs first, then the rest in pairs of its own
+        firsts = [2 * i for i in range(rd // 2)] if self.interleaved else list(range(rd // 2))
+        seconds = [2 * i + 1 for i in range(rd // 2)] if self.interleaved else [i + rd // 2 for i in range(rd // 2)]
+        rest = list(range(rd, hd))
+        firsts += rest[:len(rest) // 2]
+        seconds += rest[len(rest) // 2:]
+        assert len(firsts) == len(seconds) == half
+        return firsts + seconds
+
     def apply(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """Rotates x [T, H, head_dim] on its own (the attention mixer fuses this with its cache write)."""
         T, H, hd = x.shape
+        perm = self.head_permutation()
+        if perm is not None:
+            idx = torch.tensor(perm, device=x.device)
+            x = x[..., idx].contiguous()
         out = torch.empty_like(x)
         kernels.qk_norm_rope_kv_write(x.view(T, H * hd), out, None, None, positions, None, self.inv_freq, None,
                                       None, 1.0, H, 0, hd, 1)
+        if perm is not None:
+            back = torch.empty_like(idx)
+            back[idx] = torch.arange(hd, device=x.device)
+            out = out[..., back].contiguous()
         return out
 
 

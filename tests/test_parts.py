@@ -104,7 +104,7 @@ def test_parts_alone(dtype):
                                  wd[p + "mlp.down_proj.weight"])) <= TOL[dtype]
     # mixer (windowed attention over the paged cache)
     from ccinfer_b200.engine.step import LayerCache
-    cache = LayerCache(eng._cache_k[0], eng._cache_v[0], step.groups[0], True)
+    cache = LayerCache(eng._cache[0], step.groups[0], True)
     att = block.mixer.forward(x, step, cache, None)
     ref_att = plain.attention_block(x_ref, wd, p + "self_attn.", cfg, torch.arange(T), window=20)
     assert _rel(att, ref_att) <= TOL[dtype]
@@ -152,7 +152,7 @@ def test_order_of_layers_is_data(dtype):
                      eng.step([StepEntry("r", toks[6:8], [0, 1])]),
                      eng.step([StepEntry("r", toks[8:], list(range(5)))])]).cpu()
     eng.check()
-    assert len(eng._cache_k) == 2  # runs 0 and 2 own a cache, run 1 borrows
+    assert len(eng._cache) == 2  # runs 0 and 2 own a cache, run 1 borrows
 
     wd = {k: v.double() for k, v in w.items()}
     T = len(toks)
@@ -411,3 +411,236 @@ def test_scratch_that_follows_the_step_is_refused_once_a_graph_holds_it():
         eng.step([StepEntry("a", [3], [0]), StepEntry("b", [4], [0])])
     assert eng.context_len("a") == 2 and eng.context_len("b") == 0   # the refused step changed nothing
     eng.cache.check_consistency()
+
+
+# ---------------------------------------------------------------------------------------------
+# a toy mixer that caches ONE vector per token (not keys and values), defined here
+# ---------------------------------------------------------------------------------------------
+def _toy_latent_mixer():
+    from ccinfer_b200.parts.base import CachedTensor, CacheNeed, Mixer, TensorSpec
+
+    class LatentMean(Mixer):
+        """c_t = A x_t (r numbers) is cached in pages; y_t = B mean(c_j, j <= t, within the window if any)."""
+        graph_safe = False   # it walks the step's host arrays
+
+        def __init__(self, dim, r, prefix, window=None):
+            self.dim, self.r, self.prefix, self.window = dim, r, prefix, window
+
+        def tensor_specs(self):
+            return [TensorSpec(f"{self.prefix}.down", (self.r, self.dim)), TensorSpec(f"{self.prefix}.up", (self.dim, self.r))]
+
+        def cache_need(self):
+            return CacheNeed((CachedTensor("latent", (self.r,), token_axis=0, dtype=torch.float32),), self.window)
+
+        def bind(self, rt, fetch):
+            self.a, self.b = fetch(f"{self.prefix}.down"), fetch(f"{self.prefix}.up")
+
+        def forward(self, x, step, cache, state):
+            g = cache.group
+            pool = cache.tensors["latent"]                      # [pages, page_size, r]
+            flat = pool.view(-1, self.r)
+            c = x.float() @ self.a.float().T
+            flat[g.slot_map.long()] = c                         # slot = page * page_size + offset
+            out = torch.empty_like(x)
+            P = g.page_size
+            for b in range(step.n_entries):
+                lo, hi = int(step.host.cu_q[b]), int(step.host.cu_q[b + 1])
+                table = g.host_block_table[b]
+                for t in range(lo, hi):
+                    p = int(step.host.positions[t])
+                    first = 0 if self.window is None else max(0, p - self.window + 1)
+                    slots = [int(table[j // P]) * P + j % P for j in range(first, p + 1)]
+                    assert min(slots) >= 0, "a page of the window was given back too early"
+                    out[t] = (flat[torch.tensor(slots, device=x.device)].mean(0) @ self.b.float().T).to(x.dtype)
+            return out
+
+    return LatentMean
+
+
+@pytest.mark.parametrize("window", [None, 11])
+def test_toy_mixer_that_caches_one_vector_per_token(window):
+    """The cache need of a mixer is a list of named tensors of its own shapes and types: here one float vector
+    of 6 numbers per token in [pages, page_size, 6], beside an attention layer's keys and values in another
+    group, with so few pages that they are used again."""
+    from ccinfer_b200.engine.engine import Engine, EngineOptions, StepEntry
+    from ccinfer_b200.engine.plan import ModelPlan, RunEntry
+    from ccinfer_b200.parts import (GroupedQueryAttention, OutputHead, PreNormBlock, RMSNorm, RotaryHalf, SwiGLU,
+                                    TokenEmbedding)
+    LatentMean = _toy_latent_mixer()
+    D, V, eps, r, hd = 32, 61, 1e-6, 6, 16
+    names = {k: f"a.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+    blocks = [PreNormBlock(RMSNorm(D, eps, "b0.n1"), LatentMean(D, r, "b0.mix", window), RMSNorm(D, eps, "b0.n2"),
+                           SwiGLU(D, 48, {k: f"b0.{k}" for k in ("gate", "up", "down")})),
+              PreNormBlock(RMSNorm(D, eps, "b1.n1"), GroupedQueryAttention(D, 2, 1, hd, RotaryHalf(hd, 1e4), names),
+                           RMSNorm(D, eps, "b1.n2"), SwiGLU(D, 48, {k: f"b1.{k}" for k in ("gate", "up", "down")}))]
+    plan = ModelPlan(TokenEmbedding(V, D, "emb"), blocks, [RunEntry(0), RunEntry(1)], RMSNorm(D, eps, "nf"),
+                     OutputHead(D, V, "head"), V, 256)
+    w = _weights(plan.tensor_specs(), 21, std=0.2)
+    opts = EngineOptions(dtype="float32", page_size=4, kv_tokens=128, max_requests=2, max_tokens_per_step=32,
+                         use_graphs=False)
+    eng = Engine(plan, _fetch(w, plan.tensor_specs(), torch.float32), opts)
+    groups = {g.key: g for g in eng.cache.groups}
+    if window is None:
+        assert len(groups) == 1 and eng._cache[0]["latent"].shape == (32, 4, r) and eng._cache[0]["latent"].dtype == torch.float32
+        assert eng._cache[1]["k"].shape == (32, 1, 4, hd)
+    else:   # two groups; the window group's pool is as small as two requests can ever need
+        assert groups[("window", 11)].num_pages == 2 * (11 // 4 + 2) + 32 // 4 < groups[("all",)].num_pages
+    rng = np.random.RandomState(5)
+    a, b = (rng.randint(0, V, size=n).tolist() for n in (41, 23))
+    eng.open_request("a")
+    eng.open_request("b")
+    got = {"a": [], "b": []}
+    ia = ib = 0
+    for na, nb in ((5, 0), (1, 7), (9, 2), (1, 1), (13, 6), (2, 7), (10, 0)):
+        entries = []
+        if na:
+            entries.append(StepEntry("a", a[ia:ia + na], range(na)))
+        if nb:
+            entries.append(StepEntry("b", b[ib:ib + nb], range(nb)))
+        out = eng.step(entries).cpu()
+        # rows come in the order of the entries
+        if na:
+            got["a"].append(out[:na])
+        if nb:
+            got["b"].append(out[na:])
+        ia, ib = ia + na, ib + nb
+        eng.cache.check_consistency()
+    assert ia == len(a) and ib == len(b)
+    eng.check()
+
+    def plain_forward(toks):
+        wd = {k: v.double() for k, v in w.items()}
+        T = len(toks)
+        h = plain.embed(wd["emb"], toks)
+        c = plain.rms_norm(h, wd["b0.n1"], eps) @ wd["b0.mix.down"].T
+        mean = torch.stack([c[max(0, t - window + 1) if window else 0:t + 1].mean(0) for t in range(T)])
+        h = h + mean @ wd["b0.mix.up"].T
+        h = h + plain.swiglu(plain.rms_norm(h, wd["b0.n2"], eps), wd["b0.gate"], wd["b0.up"], wd["b0.down"])
+        x = plain.rms_norm(h, wd["b1.n1"], eps)
+        pos = torch.arange(T)
+        inv = plain.rope_inv_freq(hd, 1e4)
+        q = plain.apply_rope((x @ wd["a.q"].T).view(T, 2, hd), pos, inv)
+        k = plain.apply_rope((x @ wd["a.k"].T).view(T, 1, hd), pos, inv)
+        h = h + plain.causal_attention(q, k, (x @ wd["a.v"].T).view(T, 1, hd)).reshape(T, -1) @ wd["a.o"].T
+        h = h + plain.swiglu(plain.rms_norm(h, wd["b1.n2"], eps), wd["b1.gate"], wd["b1.up"], wd["b1.down"])
+        return plain.rms_norm(h, wd["nf"], eps) @ wd["head"].T
+
+    for rid, toks in (("a", a), ("b", b)):
+        assert _rel(torch.cat(got[rid]), plain_forward(toks)) <= 2e-5, rid
+    if window is not None:   # the window group really gave pages back while the requests ran
+        pool = eng.cache.pools[list(groups).index(("window", 11))]
+        assert pool.high_water < (41 + 23) // 4
+
+
+# ---------------------------------------------------------------------------------------------
+# position encodings with another pairing of coordinates: one defined here, and the package's options
+# ---------------------------------------------------------------------------------------------
+def _plain_partial_rope(x, positions, rotary_dim, theta, interleaved=False):
+    """The first ``rotary_dim`` coordinates of every head turned, pairs (i, i + rotary_dim / 2) or (2i, 2i + 1)."""
+    inv = plain.rope_inv_freq(rotary_dim, theta).double()
+    ang = positions.double()[:, None] * inv[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    if interleaved:
+        a, b = x[..., 0:rotary_dim:2], x[..., 1:rotary_dim:2]
+        out[..., 0:rotary_dim:2], out[..., 1:rotary_dim:2] = a * c - b * s, b * c + a * s
+    else:
+        a, b = x[..., :rotary_dim // 2], x[..., rotary_dim // 2:rotary_dim]
+        out[..., :rotary_dim // 2], out[..., rotary_dim // 2:rotary_dim] = a * c - b * s, b * c + a * s
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["toy partial", "package partial", "package interleaved"])
+def test_position_encodings_with_other_pairings(kind, dtype):
+    """Partial rotation and interleaved pairs need no kernel of their own: the encoding states a permutation of
+    the head's coordinates and a table with zeros, the attention mixer permutes its projections.  One such
+    encoding is defined here (no file of the package changes), two are options of the package's RotaryHalf."""
+    from ccinfer_b200.engine.engine import StepEntry
+    from ccinfer_b200.engine.plan import ModelPlan, RunEntry
+    from ccinfer_b200.parts import (GroupedQueryAttention, OutputHead, PositionEncoding, PreNormBlock, RMSNorm,
+                                    RotaryHalf, SwiGLU, TokenEmbedding)
+    D, nq, nkv, hd, V, eps, theta, rd = 64, 4, 2, 64, 83, 1e-6, 1e4, 24
+
+    class ToyPartialRotary(PositionEncoding):
+        """Rotates the first rd coordinates, pairs (i, i + rd / 2); written without the package's helper."""
+
+        def bind(self, rt, fetch):
+            table = torch.zeros(hd // 2)
+            table[:rd // 2] = plain.rope_inv_freq(rd, theta)
+            self.table = table.to(rt.device)
+
+        def rotary_table(self):
+            return self.table
+
+        def head_permutation(self):
+            rest = list(range(rd, hd))
+            return (list(range(rd // 2)) + rest[:len(rest) // 2]) + (list(range(rd // 2, rd)) + rest[len(rest) // 2:])
+
+    interleaved = kind == "package interleaved"
+    position = {"toy partial": ToyPartialRotary(), "package partial": RotaryHalf(hd, theta, rotary_dim=rd),
+                "package interleaved": RotaryHalf(hd, theta, rotary_dim=rd, interleaved=True)}[kind]
+    names = {k: f"a.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+    block = PreNormBlock(RMSNorm(D, eps, "n1"), GroupedQueryAttention(D, nq, nkv, hd, position, names, qk_norm_eps=eps),
+                         RMSNorm(D, eps, "n2"), SwiGLU(D, 96, {k: f"f.{k}" for k in ("gate", "up", "down")}))
+    plan = ModelPlan(TokenEmbedding(V, D, "emb"), [block], [RunEntry(0)], RMSNorm(D, eps, "nf"),
+                     OutputHead(D, V, "head"), V, 512)
+    w = _weights(plan.tensor_specs(), 31, std=0.15)
+    eng = _engine(plan, w, dtype, page=16, tokens=256)
+    toks = list(np.random.RandomState(4).randint(0, V, size=150))
+    eng.open_request("r")
+    # a long portion (tensor-core prefill in bfloat16), short ones, and single tokens (the fused decode kernel)
+    cuts = [0, 90, 97, 99] + list(range(100, 151))
+    got = torch.cat([eng.step([StepEntry("r", toks[a:b], range(b - a))]).cpu() for a, b in zip(cuts, cuts[1:])])
+    eng.check()
+
+    wd = {k: v.double() for k, v in w.items()}
+    T = len(toks)
+    pos = torch.arange(T)
+    h = plain.embed(wd["emb"], toks)
+    x = plain.rms_norm(h, wd["n1"], eps)
+    q = plain.rms_norm((x @ wd["a.q"].T).view(T, nq, hd), wd["a.q_norm"], eps)
+    k = plain.rms_norm((x @ wd["a.k"].T).view(T, nkv, hd), wd["a.k_norm"], eps)
+    q, k = (_plain_partial_rope(t, pos, rd, theta, interleaved) for t in (q, k))
+    h = h + plain.causal_attention(q, k, (x @ wd["a.v"].T).view(T, nkv, hd)).reshape(T, -1) @ wd["a.o"].T
+    h = h + plain.swiglu(plain.rms_norm(h, wd["n2"], eps), wd["f.gate"], wd["f.up"], wd["f.down"])
+    ref = plain.rms_norm(h, wd["nf"], eps) @ wd["head"].T
+    assert _rel(got, ref) <= TOL[dtype]
+    if kind != "toy partial":   # the encoding alone
+        xq = torch.randn((7, 3, hd), generator=torch.Generator().manual_seed(1)).to(DT[dtype])
+        p7 = torch.tensor([0, 1, 5, 63, 64, 200, 511], dtype=torch.int32)
+        rot = position.apply(xq.cuda(), p7.cuda())
+        assert _rel(rot, _plain_partial_rope(xq.double(), p7, rd, theta, interleaved)) <= (1e-6 if dtype == "float32" else 8e-3)
+
+
+def test_what_the_attention_mixer_cannot_do_is_refused():
+    from ccinfer_b200.engine.plan import ModelPlan, RunEntry
+    from ccinfer_b200.errors import Unsupported
+    from ccinfer_b200.parts import (GroupedQueryAttention, OutputHead, PositionEncoding, PreNormBlock, RMSNorm, SwiGLU,
+                                    TokenEmbedding)
+    D, hd, V, eps = 32, 16, 19, 1e-6
+
+    class DistanceBias(PositionEncoding):
+        def rotary_table(self):
+            return None
+
+        def score_bias(self):
+            return "slopes"
+
+    class ShortTable(PositionEncoding):
+        def bind(self, rt, fetch):
+            self.t = torch.ones(3, device=rt.device)
+
+        def rotary_table(self):
+            return self.t
+
+    for position in (DistanceBias(), ShortTable()):
+        names = {k: f"a.{k}" for k in ("q", "k", "v", "o")}
+        block = PreNormBlock(RMSNorm(D, eps, "n1"), GroupedQueryAttention(D, 2, 1, hd, position, names),
+                             RMSNorm(D, eps, "n2"), SwiGLU(D, 48, {k: f"f.{k}" for k in ("gate", "up", "down")}))
+        plan = ModelPlan(TokenEmbedding(V, D, "emb"), [block], [RunEntry(0)], RMSNorm(D, eps, "nf"),
+                         OutputHead(D, V, "head"), V, 64)
+        with pytest.raises(Unsupported):
+            _engine(plan, _weights(plan.tensor_specs(), 1), "float32")
+    with pytest.raises(Unsupported, match="multiples of 16"):
+        GroupedQueryAttention(D, 2, 1, 120, DistanceBias(), {})
