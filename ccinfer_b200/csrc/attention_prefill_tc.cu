@@ -35,6 +35,9 @@
 
 using namespace ccb;
 
+// 1: always one q head per block (the older kernel), for comparisons; set by ccb_attention_prefill_tc_single_head
+static int g_ccb_prefill_single_head = 0;
+
 namespace {
 
 constexpr int kTQ = 128;     // query rows per block = TMEM lanes
@@ -49,6 +52,32 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Two floats in one 64-bit register, for the packed float instructions of sm_100 (one issue slot for two
+// results on the FMA pipe).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // HD = 64 * NH
 template <int NH>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -349,6 +378,314 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two q heads of one kv group per block.  The same key and value tiles feed two independent sets of S, P and
+// O in tensor memory, and each head has its own group of four softmax warps: while one head's softmax works
+// on a tile, the tensor pipe runs the other head's products, which a block of one head left idle for most
+// of a tile (the chain S -> exponentials -> P -> P V is serial within a head).  Keys and values are fetched
+// once for two heads.
+//   warps 0..3   softmax, rescaling and store of head h0       (tensor-memory lanes 32 (warp % 4) ..)
+//   warps 4..7   the same for head h0 + 1
+//   warp 8 key loads, warp 9 products, warp 10 value loads, warp 11 idle
+//   tensor memory: S of head a at column 0, of head b at 128; O at 256 and 384.  P (bfloat16 pairs, 64
+//   columns) is written over the first half of its own S once the row's scores are in registers: the next
+//   Q K^T of that head is issued after the P V that reads it, and the tensor pipe runs its products in the
+//   order of their issue, so a head needs one S buffer only.  By the same order a head's S of tile i + 1 is
+//   complete only after its P V of tile i: the softmax threads need no separate wait before they rescale O.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPairThreads = 384;
+
+template <int NH>
+__global__ void __launch_bounds__(kPairThreads, 1)
+attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
+                                 const int* __restrict__ cu_q, const int* __restrict__ pos0,
+                                 const int* __restrict__ block_table, int bt_stride, int entry0, int nq, int nkv,
+                                 int page_size, int page_shift, int num_pages, int window, float scale_log2,
+                                 int* status) {
+  constexpr int HD = 64 * NH;
+  constexpr int HALF_BYTES = 128 * 128;
+  constexpr int TILE_BYTES = NH * HALF_BYTES;
+  constexpr int TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                              // [2 heads]
+  uint8_t* sK = sQ + 2 * TILE_BYTES;               // [stages]
+  uint8_t* sV = sK + kKvStages * TILE_BYTES;       // [stages]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kKvStages * TILE_BYTES);
+  // barriers: q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2 heads], p_ready[2 heads], pv_done[2 heads]
+  const uint32_t b_q = s32(bars), b_kf = s32(bars + 1), b_vf = s32(bars + 3), b_ke = s32(bars + 5),
+                 b_ve = s32(bars + 7), b_sf = s32(bars + 9), b_pr = s32(bars + 11), b_pv = s32(bars + 13);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  static_assert(kKvStages == 2, "the barrier layout above holds two stages");
+
+  const int b = entry0 + blockIdx.z;
+  const int h0 = 2 * blockIdx.x;                   // heads h0 and h0 + 1: the same kv head (the group is even)
+  const int row_begin = cu_q[b], n_new = cu_q[b + 1] - row_begin;
+  const int n_qtiles = (n_new + kTQ - 1) / kTQ;
+  const int qt = n_qtiles - 1 - (int)blockIdx.y;   // the longest tiles first (see the kernel above)
+  if (qt < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = h0 / (nq / nkv);
+  const int p0 = pos0[b];
+  const int q_first = qt * kTQ;
+  const int rows_here = min(kTQ, n_new - q_first);
+  const int p_first = p0 + q_first, p_last = p_first + rows_here - 1;
+  const int* bt = block_table + (size_t)b * bt_stride;
+  const int j_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int first_tile = j_lo / kTK, last_tile = p_last / kTK;
+  const int n_tiles = last_tile - first_tile + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(b_q, 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(b_kf + 8 * s, 1);
+      mbar_init(b_vf + 8 * s, 1);
+      mbar_init(b_ke + 8 * s, 1);
+      mbar_init(b_ve + 8 * s, 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(b_sf + 8 * x, 1);
+      mbar_init(b_pr + 8 * x, 128);
+      mbar_init(b_pv + 8 * x, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8 || warp == 10) {
+    // ---- TMA producers (as in the kernel above): a lane per page of a tile ----
+    pdl_wait();
+    if (warp == 8 && lane == 0) {
+      mbar_expect_tx(b_q, 2 * TILE_BYTES);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf)
+          tma_load_2d(s32(sQ + x * TILE_BYTES + hf * HALF_BYTES), &tmQ, (h0 + x) * HD + hf * 64, row_begin + q_first, b_q);
+    }
+    const int pages_per_tile = kTK >> page_shift;
+    const int lp_last = p_last >> page_shift;
+    auto page_row = [&](int t) -> int {
+      const int lp = (((first_tile + t) * kTK) >> page_shift) + lane;
+      int page = (lp <= lp_last && lp < bt_stride) ? bt[lp] : -1;
+      if (page < 0 || page >= num_pages) {
+        const int k_lo = lp << page_shift;
+        if (k_lo <= p_last && k_lo + page_size - 1 >= j_lo) set_status(status, CCB_ST_BAD_PAGE);
+        page = bt[lp_last];
+      }
+      if (page < 0 || page >= num_pages) {
+        set_status(status, CCB_ST_BAD_PAGE);
+        page = 0;
+      }
+      return (page * nkv + kvh) * page_size;
+    };
+    const uint32_t off = (uint32_t)(lane * page_size) * 128u;
+    const bool keys = warp == 8;
+    const uint32_t b_full = keys ? b_kf : b_vf, b_empty = keys ? b_ke : b_ve;
+    uint8_t* stage0 = keys ? sK : sV;
+    const CUtensorMap* tm = keys ? &tmK : &tmV;
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % kKvStages, ph = (i / kKvStages) & 1;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(b_empty + 8 * s, ph ^ 1) ? 1 : 0;
+        if (ok) mbar_expect_tx(b_full + 8 * s, TILE_BYTES);
+        else set_status(status, CCB_ST_WAIT_TIMEOUT);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        const int grow = page_row(i);
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf)
+          tma_load_2d(s32(stage0 + s * TILE_BYTES + hf * HALF_BYTES) + off, tm, hf * 64, grow, b_full + 8 * s);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {  // ---- MMA issuer ----
+      constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
+                                   ((uint32_t)(128 >> 4) << 24);
+      // S of head x, tile t (the key stage has landed)
+      auto issue_qk = [&](int x, int t) {
+        const int s = t % kKvStages;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t da = smem_desc(s32(sQ + x * TILE_BYTES + (ks >> 2) * HALF_BYTES)) + 2 * (ks & 3);
+          const uint64_t db = smem_desc(s32(sK + s * TILE_BYTES + (ks >> 2) * HALF_BYTES)) + 2 * (ks & 3);
+          tc_mma(tmem_base + x * 128, da, db, idesc_s, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(b_sf + 8 * x);
+      };
+      bool alive = mbar_wait(b_q, 0) && mbar_wait(b_kf, 0);
+      if (alive) {
+        tc_fence_after();
+        issue_qk(0, 0);
+        issue_qk(1, 0);
+        tc_commit(b_ke);
+      }
+      for (int i = 0; i < n_tiles && alive; ++i) {
+        const int s = i % kKvStages, ph = (i / kKvStages) & 1;
+        const int s1 = (i + 1) % kKvStages, ph1 = ((i + 1) / kKvStages) & 1;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          // O_x += P_x V once head x's softmax has written P (and rescaled O) and V has landed
+          alive = mbar_wait(b_pr + 8 * x, i & 1) && (x == 1 || mbar_wait(b_vf + 8 * s, ph));
+          if (!alive) break;
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < kTK / 16; ++ks) {
+            const uint64_t db = smem_desc_mn(s32(sV + s * TILE_BYTES) + ks * 2048, HALF_BYTES, 1024);
+            tc_mma_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + ks * 8, db, idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+          }
+          tc_commit(b_pv + 8 * x);
+          if (x == 1) tc_commit(b_ve + 8 * s);   // both heads' P V of this tile are issued: the value stage
+          // the head's next S, over its P: the tensor pipe keeps the order of issue
+          if (i + 1 < n_tiles) {
+            if (x == 0) {
+              alive = mbar_wait(b_kf + 8 * s1, ph1);
+              if (!alive) break;
+              tc_fence_after();
+            }
+            issue_qk(x, i + 1);
+            if (x == 1) tc_commit(b_ke + 8 * s1);
+          }
+        }
+      }
+      if (!alive) set_status(status, CCB_ST_WAIT_TIMEOUT);
+    }
+  } else if (warp < 8) {  // ---- softmax, rescaling, epilogue: thread = query row = TMEM lane, a group per head ----
+    const int x = warp >> 2;
+    const int h = h0 + x;
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t tmem_sx = tmem_base + x * 128, tmem_ox = tmem_base + 256 + x * 128;
+    const uint32_t bar_sf = b_sf + 8 * x, bar_pr = b_pr + 8 * x, bar_pv = b_pv + 8 * x;
+    const int pr = p_first + row;
+    const int lo = window > 0 ? max(0, pr - window + 1) : 0;
+    float m = -CUDART_INF_F, l = 0.f;
+    bool alive = true;
+    for (int i = 0; i < n_tiles; ++i) {
+      alive = mbar_wait(bar_sf, i & 1);
+      if (!alive) break;
+      tc_fence_after();
+      const int jt = (first_tile + i) * kTK;
+      const bool need_mask = (jt + kTK - 1 > p_first) || (window > 0 && jt < p_first + kTQ - window);
+      uint32_t v[kTK];
+#pragma unroll
+      for (int c0 = 0; c0 < kTK; c0 += 32) tc_ld32(tmem_sx + lane_addr + c0, v + c0);
+      tc_wait_ld();
+      if (need_mask) {
+#pragma unroll
+        for (int e = 0; e < kTK; ++e) {
+          const int j = jt + e;
+          if (!(j <= pr && j >= lo)) v[e] = 0xff800000u;
+        }
+      }
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};  // four chains, two scores a step
+#pragma unroll
+      for (int e = 0; e < kTK; e += 8)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = max3(mx4[u], __uint_as_float(v[e + 2 * u]), __uint_as_float(v[e + 2 * u + 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const float m_new = (m == -CUDART_INF_F || mx > m + 8.f) ? fmaxf(m, mx) : m;
+      const float corr = m_new == -CUDART_INF_F ? 1.f : ex2(m - m_new);
+      const float sub = m_new == -CUDART_INF_F ? 0.f : m_new;
+      m = m_new;
+      // this head's P V of tile i - 1 was issued before the Q K^T whose S has just arrived: it is complete
+      if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          tc_ld32(tmem_ox + lane_addr + c0, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+          tc_st32(tmem_ox + lane_addr + c0, o);
+        }
+        tc_wait_st();
+      }
+      // Exponentials; scale, subtraction and sums run as packed pairs (one issue slot for two results).
+      // Measured and dropped: a quarter or a half of the exponentials as cubics on the FMA pipe, to relieve
+      // the special-function unit (8,192-token prompt: 524 us without, 646 and 746 us with), and the two
+      // heads taking turns at the exponentials (554 us): the softmax threads are short of issue slots and of
+      // latency to hide, not of the unit.
+      const float nsub = -sub;
+      const f32x2 sc2 = pack2(scale_log2, scale_log2), ns2 = pack2(nsub, nsub);
+      f32x2 sum2 = pack2(0.f, 0.f);
+#pragma unroll
+      for (int c0 = 0; c0 < kTK; c0 += 64) {
+        uint32_t packed[32];
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) {
+          const f32x2 t = fma2(pack2(__uint_as_float(v[c0 + e]), __uint_as_float(v[c0 + e + 1])), sc2, ns2);
+          float t0, t1;
+          unpack2(t, t0, t1);
+          const float a = ex2(t0), c = ex2(t1);
+          sum2 = add2(sum2, pack2(a, c));
+          const __nv_bfloat162 hh = __floats2bfloat162_rn(a, c);
+          packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        tc_st32(tmem_sx + lane_addr + (c0 >> 1), packed);   // P over the S that is in registers now
+      }
+      tc_wait_st();
+      float ps0, ps1;
+      unpack2(sum2, ps0, ps1);
+      l = l * corr + (ps0 + ps1);
+      tc_fence_before();
+      mbar_arrive(bar_pr);
+    }
+    if (alive) {
+      alive = mbar_wait(bar_pv, (n_tiles - 1) & 1);
+      tc_fence_after();
+    }
+    if (!alive && lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
+    pdl_trigger();
+    if (alive) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = out + ((size_t)(row_begin + q_first + row) * nq + h) * HD;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(tmem_ox + lane_addr + c0, v);
+        tc_wait_ld();
+        if (row < rows_here) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint32_t p4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[e + 2 * u]) * inv,
+                                                              __uint_as_float(v[e + 2 * u + 1]) * inv);
+              p4[u] = *reinterpret_cast<const uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(orow + c0 + e) = make_uint4(p4[0], p4[1], p4[2], p4[3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
 template <int NH>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q, const int* pos0,
            const int* block_table, int bt_stride, int entry0, int n_entries, int max_new, int n_tokens, int nq,
@@ -362,6 +699,24 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
       !ccb_tensor_map_2d(k_cache, cache_rows, HD, HD, 64, page_size, &tmK) ||
       !ccb_tensor_map_2d(v_cache, cache_rows, HD, HD, 64, page_size, &tmV))
     return CCB_REFUSE_ARG;
+  if (NH == 2 && (nq / nkv) % 2 == 0 && !g_ccb_prefill_single_head) {
+    // head size 128, groups of an even number of q heads: two heads of a group share a block and its key and
+    // value tiles (with head size 64 the products are half as long and one head a block is faster: 46 us
+    // against 55 us for a 2,048-token prompt of 16 heads)
+    const size_t smem2 = (size_t)(2 + 2 * kKvStages) * NH * 128 * 128 + 20 * 8 + 1024;
+    static bool configured2 = false;
+    if (!configured2) {
+      cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_pair_kernel<NH>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+      if (e != cudaSuccess) return (int)e;
+      configured2 = true;
+    }
+    dim3 grid2(nq / 2, (max_new + kTQ - 1) / kTQ, n_entries);
+    ccb_launch(attention_prefill_tc_pair_kernel<NH>, grid2, kPairThreads, smem2, stream, tmQ, tmK, tmV,
+               (__nv_bfloat16*)out, cu_q, pos0, block_table, bt_stride, entry0, nq, nkv, page_size, page_shift,
+               num_pages, window, scale * 1.4426950408889634f, status);
+    return ccb_launch_status();
+  }
   const size_t smem = (size_t)(1 + 2 * kKvStages) * NH * 128 * 128 + 20 * 8 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -399,4 +754,10 @@ CCB_API int ccb_attention_prefill_tc(const void* q, const void* k_cache, const v
     return launch<1>(q, k_cache, v_cache, out, cu_q, pos0, block_table, bt_stride, entry0, n_entries, max_new,
                      n_tokens, nq, nkv, page_size, num_pages, window, scale, status, stream);
   return CCB_REFUSE_SIZE;
+}
+
+// 1: one q head per block even where two heads of a group could share one (for measurements and tests); 0: the default
+CCB_API int ccb_attention_prefill_tc_single_head(int on) {
+  g_ccb_prefill_single_head = on ? 1 : 0;
+  return 0;
 }

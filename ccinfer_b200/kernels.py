@@ -455,7 +455,8 @@ def attention_prefill_tc_fits(hd: int, page_size: int) -> bool:
 def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, pos0, block_table, entry0: int, n_entries: int,
                          max_new: int, window: int, scale: float, status=None) -> None:
     """As attention_prefill_mma, with both products on tcgen05 tensor cores and the accumulators in tensor
-    memory (128-token query tiles, TMA loads page by page).  Page size a power of two from 8 to 128."""
+    memory (128-token query tiles, TMA loads page by page).  Page size a power of two from 8 to 128.  Where the
+    groups hold an even number of q heads, two heads of a group share a block and its key and value tiles."""
     _cuda(q, k_cache, v_cache, out, cu_q, pos0, block_table, status)
     T, nq, hd = q.shape
     num_pages, nkv, page_size, hd2 = k_cache.shape
@@ -466,6 +467,15 @@ def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, pos0, block_table, entr
                                           _p(block_table), block_table.stride(0), entry0, n_entries, max_new, T,
                                           nq, nkv, hd, page_size, num_pages, int(window), float(scale),
                                           _p(status), _stream()), "attention_prefill_tc")
+
+
+def attention_prefill_tc_single_head(on: bool) -> None:
+    """Measurements and tests: with ``on`` attention_prefill_tc always runs one q head per block, also where two
+    heads of a kv group would share a block (and its key and value tiles)."""
+    fn = lib().ccb_attention_prefill_tc_single_head
+    fn.argtypes = [c_int]
+    fn.restype = c_int
+    fn(1 if on else 0)
 
 
 def gemm_f32(c, a, w) -> None:

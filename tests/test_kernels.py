@@ -716,11 +716,21 @@ TC_PREFILL_CASES = [
     ([0, 40, 129], [150, 3, 64], 4, 4, 64, 32, 24),
     ([17, 250], [300, 1], 5, 1, 128, 128, 100),
     ([1000], [200], 8, 2, 128, 64, None),
+    ([0, 700], [700, 260], 32, 8, 128, 16, None),     # the 8B head layout, several query tiles, many key tiles
+    ([130], [400], 16, 2, 64, 16, 200),               # groups of 8, head size 64, a window across tiles
 ]
 
 
+@pytest.fixture(params=["two heads a block where the group is even", "one head a block"])
+def tc_prefill_form(request):
+    single = request.param == "one head a block"
+    _k().attention_prefill_tc_single_head(single)
+    yield request.param
+    _k().attention_prefill_tc_single_head(False)
+
+
 @pytest.mark.parametrize("case", TC_PREFILL_CASES)
-def test_attention_prefill_tc(case):
+def test_attention_prefill_tc(case, tc_prefill_form):
     ctx, new, nq, nkv, hd, P, window = case
     q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", ctx, new, nq, nkv, hd, P, seed=hd + len(ctx),
                                                window=window)
@@ -740,7 +750,7 @@ def test_attention_prefill_tc(case):
 
 
 @pytest.mark.parametrize("far_key", [0, 63, 64, 127, 128, 400, 449])
-def test_attention_prefill_tc_reads_far_key(far_key):
+def test_attention_prefill_tc_reads_far_key(far_key, tc_prefill_form):
     nq, nkv, hd, P = 4, 2, 128, 16
     q, kc, vc, pos, eot, bt, ref = _paged_case("bfloat16", [450], [150], nq, nkv, hd, P, seed=far_key,
                                                peak=(0, far_key))
@@ -754,7 +764,7 @@ def test_attention_prefill_tc_reads_far_key(far_key):
 
 
 @pytest.mark.parametrize("edge", [-1, 0, 1])
-def test_attention_prefill_tc_window_edge(edge):
+def test_attention_prefill_tc_window_edge(edge, tc_prefill_form):
     nq, nkv, hd, P, W = 2, 1, 64, 8, 40
     ctx, new = 130, 70
     L = ctx + new
