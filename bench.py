@@ -8,18 +8,26 @@ hidden 4096, 32 q heads, 8 kv heads, head size 128, intermediate 12288,
 vocabulary 151936, bfloat16, a batch of 8 requests decoding after 2,048-token
 prompts.  It prints ONE JSON line:
 
-  value      decoded tokens a second, from CUDA events around each of the K timed steps
-  e2e        the same through the Python entry point's scheduler, by wall clock: host prompts in, every
-             step one copy of the step's arrays from pinned memory and one read of the sampled token
-             ids into host lists.  The scheduler runs one step ahead: a step is launched before the
-             tokens of the step before it are read (the embedding takes them from the device)
+  value      decoded tokens a second: the median of --runs (5) runs of K timed steps each, from CUDA events
+             around every step
+  e2e        the same through the Python entry point's scheduler, by wall clock, over at least 256 steps
+             (named in config): host prompts in, every step one copy of the step's arrays from pinned memory
+             and one read of the sampled token ids into host lists.  The scheduler runs one step ahead: a
+             step is launched before the tokens of the step before it are read (the embedding takes them
+             from the device)
   prefill    one 2,048-token prompt in one step: tokens a second and the fraction of the bf16 peak
   roofline   the decode step's bytes (every weight once + the cache of the live requests) / its time
-  points     decode at batch 1 and 64
+  points     decode at batch 1 and 64, decode at batch 8 after 8,192- and 32,768-token prompts, prefill of
+             8,192- and 16,384-token prompts (in steps of 2,048 tokens, as the scheduler cuts them)
   clocks     SM clock and throttle reasons sampled during the timed regions
 
 Every timed decode step reads 15 GB of weights, far more than the 126 MB L2, so no flush is needed
 between iterations.  With --gpus N > 1 it prints one line that says so and exits with 2.
+
+    python bench.py --profile-steps N [--layers L] [--batch B] [--context C] [--profile-prefill T] [--shape 8b|14b|32b]
+
+is for profilers: N decode steps of B requests at C cached tokens WITHOUT CUDA graphs (so that a profiler sees
+every kernel) and, with --profile-prefill T, one prompt of T tokens in one step; few layers keep it small.
 
     python bench.py --workload mix14b | long32b [--layers L]
 
@@ -216,6 +224,39 @@ def run_workload(args) -> int:
     return 0
 
 
+def run_profile_steps(args) -> int:
+    """A few eager steps of a random model at a chosen layer shape, for profilers (nothing is timed)."""
+    import numpy as np
+    import torch
+    from ccinfer_b200.config import Qwen3Config
+    from ccinfer_b200.engine.engine import Engine, EngineOptions, StepEntry
+
+    cfg_json = dict({"8b": QWEN3_8B, "14b": SHAPES["mix14b"], "32b": SHAPES["long32b"]}[args.shape])
+    cfg_json["num_hidden_layers"] = args.layers or 2
+    cfg = Qwen3Config.from_json(cfg_json)
+    B, ctx, steps, pre = args.batch, args.context, args.profile_steps, args.profile_prefill
+    longest = max(ctx + steps, pre) + 64
+    eng = Engine.from_random(cfg, 42, options=EngineOptions(
+        dtype="bfloat16", kv_tokens=B * (ctx + steps + 64) + pre + 64, max_requests=B + 1,
+        max_tokens_per_step=max(2048, pre, ctx), max_context=longest, use_graphs=False, use_pdl=args.pdl))
+    rng = np.random.RandomState(0)
+    for b in range(B):
+        eng.open_request(b)
+        eng.step([StepEntry(b, rng.randint(0, cfg.vocab_size, size=ctx).tolist(), [])])
+    torch.cuda.synchronize()
+    for s in range(steps):
+        eng.step([StepEntry(b, [5 + s], [0]) for b in range(B)])
+    torch.cuda.synchronize()
+    if pre:
+        eng.open_request("p")
+        eng.step([StepEntry("p", rng.randint(0, cfg.vocab_size, size=pre).tolist(), [pre - 1])])
+        torch.cuda.synchronize()
+    eng.check()
+    print(f"[bench] profile steps done: {steps} decode steps of {B} requests at {ctx} tokens"
+          + (f", one prompt of {pre} tokens" if pre else ""), file=sys.stderr)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -231,6 +272,13 @@ def main() -> int:
     ap.add_argument("--pdl", type=int, default=1, help="0 off, 1 products start early, 2 every kernel")
     ap.add_argument("--chunk", type=int, default=None,
                     help="prompt portion of the two workloads (default 512, the entry point's own default)")
+    ap.add_argument("--runs", type=int, default=5, help="runs of K timed steps; the value is their median")
+    ap.add_argument("--long-points", default="8192,32768", help="contexts of the further batch-8 decode points")
+    ap.add_argument("--prefill-points", default="8192,16384", help="lengths of the further prefill points")
+    ap.add_argument("--profile-steps", type=int, default=0,
+                    help="for profilers: this many eager decode steps (no CUDA graphs) and nothing else")
+    ap.add_argument("--profile-prefill", type=int, default=0, help="with --profile-steps: one prompt of this length")
+    ap.add_argument("--shape", default="8b", choices=["8b", "14b", "32b"], help="layer shape of --profile-steps")
     ap.add_argument("--workload", default="decode", choices=["decode", "mix14b", "long32b"],
                     help="decode (the default line) or one of the two other workloads of the benchmark record")
     args = ap.parse_args()
@@ -246,6 +294,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.profile_steps:
+        return run_profile_steps(args)
     if args.workload != "decode":
         return run_workload(args)
 
@@ -265,11 +315,22 @@ def main() -> int:
     cfg = Qwen3Config.from_json(cfg_json)
     weight_bytes, kv_per_token, prefill_flops = model_numbers(cfg_json, layers)
     batches = [args.batch] + [int(b) for b in args.points.split(",") if b]
-    ctx, K, W = args.context, args.steps, args.warmup
+    long_ctx = [int(c) for c in args.long_points.split(",") if c]
+    prefill_lens = [] if args.no_prefill else [int(c) for c in args.prefill_points.split(",") if c]
+    ctx, K, W, RUNS = args.context, args.steps, args.warmup, max(1, args.runs)
+    E2E_STEPS = max(K, 256)
     page = 16
-    per_req = -(-(ctx + W + K + 2) // page) * page
-    opt = EngineOptions(dtype="bfloat16", page_size=page, kv_tokens=max(batches) * per_req,
-                        max_requests=max(batches), max_tokens_per_step=max(2048, ctx), max_context=per_req,
+    chunk = 2048   # prompts longer than this are fed in steps of this many tokens, as the scheduler cuts them
+
+    def tokens_held(c, steps):
+        return -(-(c + steps + 2) // page) * page
+
+    per_req = tokens_held(ctx, max(W + RUNS * K, W + E2E_STEPS))
+    kv_tokens = max([max(batches) * per_req] + [args.batch * tokens_held(c, W + RUNS * K) for c in long_ctx]
+                    + [tokens_held(t, 0) for t in prefill_lens])
+    max_context = max([per_req] + [tokens_held(c, W + RUNS * K) for c in long_ctx] + [tokens_held(t, 0) for t in prefill_lens])
+    opt = EngineOptions(dtype="bfloat16", page_size=page, kv_tokens=kv_tokens,
+                        max_requests=max(batches), max_tokens_per_step=max(chunk, ctx), max_context=max_context,
                         use_pdl=args.pdl)
     t0 = time.time()
     engine = Engine.from_random(cfg, seed=42, std=0.02, options=opt)
@@ -280,75 +341,89 @@ def main() -> int:
     sampler = ClockSampler()
     sampler.start()
 
-    # ---- prefill: one 2,048-token prompt in one step ----
-    prefill = None
-    if not args.no_prefill:
-        Tp = 2048
+    # ---- prefill: one prompt, in steps of up to 2,048 tokens; timed from the first step's launch to the last one's end
+    def time_prefill(Tp, reps):
         times = []
-        for i in range(W + 5):
+        for i in range(W + reps if Tp <= chunk else 1 + reps):
             toks = rng.randint(0, V, size=Tp).tolist()
             engine.open_request("p")
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             e0.record()
-            engine.step([StepEntry("p", toks, [Tp - 1])])
+            for at in range(0, Tp, chunk):
+                part = toks[at:at + chunk]
+                engine.step([StepEntry("p", part, [len(part) - 1] if at + chunk >= Tp else [])])
             e1.record()
             torch.cuda.synchronize()
             engine.close_request("p")
-            if i >= W:
-                times.append(e0.elapsed_time(e1))
+            times.append(e0.elapsed_time(e1))
+        times = times[-reps:]
         ms = statistics.median(times)
-        prefill = {"value": round(Tp / ms * 1e3, 1), "tokens": Tp, "ms": round(ms, 3),
-                   "frac": round(prefill_flops(Tp) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        return {"value": round(Tp / ms * 1e3, 1), "tokens": Tp, "ms": round(ms, 3),
+                "frac": round(prefill_flops(Tp) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    prefill = None
+    prefill_points = {}
+    if not args.no_prefill:
+        prefill = time_prefill(2048, 5)
         print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
+        for Tp in prefill_lens:
+            prefill_points[Tp] = time_prefill(Tp, 3)
+            print(f"[bench] prefill {prefill_points[Tp]}", file=sys.stderr, flush=True)
 
     # ---- decode ----
-    def fill(B, sched=None):
-        """Opens B requests and brings each to ``ctx`` cached tokens (prompts in steps of up to 2,048 tokens)."""
-        prompts = [rng.randint(0, V, size=ctx).tolist() for _ in range(B)]
+    def fill(B, c, sched=None, steps=0):
+        """Opens B requests and brings each to ``c`` cached tokens (prompts in steps of up to 2,048 tokens)."""
+        prompts = [rng.randint(0, V, size=c).tolist() for _ in range(B)]
         if sched is not None:
             for b, p in enumerate(prompts):
-                sched.submit(f"d{b}", p, SamplingParams(max_tokens=W + K + 1))
+                sched.submit(f"d{b}", p, SamplingParams(max_tokens=steps + 1))
             return prompts
         last = []
         for b, p in enumerate(prompts):
             engine.open_request(f"d{b}")
-            lg = engine.step([StepEntry(f"d{b}", p, [ctx - 1])])
+            for at in range(0, c, chunk):
+                part = p[at:at + chunk]
+                lg = engine.step([StepEntry(f"d{b}", part, [len(part) - 1] if at + chunk >= c else [])])
             last.append(engine.sample(lg, [SamplingParams()], [0])[0])
         return last
 
-    def decode_device(B):
-        """K decode steps of B requests, each step timed by its own pair of CUDA events."""
-        tokens = fill(B)
-        greedy = [SamplingParams()] * B
-        evs = []
-        launches0 = None
-        for i in range(W + K):
-            if i == W:
-                torch.cuda.synchronize()
-                launches0 = (kernels.counters.own, kernels.counters.library)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
+    def decode_device(B, c):
+        """RUNS runs of K decode steps of B requests after c-token prompts, each step timed by its own pair of
+        CUDA events; returns the runs' times in ms (each the sum of its K steps) and the launches of one run."""
+        tokens = fill(B, c)
+        run_ms, launches = [], None
+        for i in range(W):
             lg = engine.step([StepEntry(f"d{b}", [tokens[b]], [0]) for b in range(B)])
             out = engine._sample_tokens[:B]
             kernels.sample_rows(lg, out)
-            e1.record()
-            tokens = out.tolist()  # waits for the step
-            if i >= W:
+            tokens = out.tolist()
+        for r in range(RUNS):
+            torch.cuda.synchronize()
+            launches0 = (kernels.counters.own, kernels.counters.library)
+            evs = []
+            for i in range(K):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                lg = engine.step([StepEntry(f"d{b}", [tokens[b]], [0]) for b in range(B)])
+                out = engine._sample_tokens[:B]
+                kernels.sample_rows(lg, out)
+                e1.record()
+                tokens = out.tolist()  # waits for the step
                 evs.append((e0, e1))
-        torch.cuda.synchronize()
-        launches = (kernels.counters.own - launches0[0], kernels.counters.library - launches0[1])
-        ms = [a.elapsed_time(b) for a, b in evs]
+            torch.cuda.synchronize()
+            launches = (kernels.counters.own - launches0[0], kernels.counters.library - launches0[1])
+            run_ms.append(sum(a.elapsed_time(b) for a, b in evs))
         for b in range(B):
             engine.close_request(f"d{b}")
         engine.check()
-        return sum(ms), launches
+        return run_ms, launches
 
     def decode_e2e(B):
-        """The same K steps through the scheduler: host token lists in, sampled host tokens out, wall clock."""
+        """E2E_STEPS steps through the scheduler: host token lists in, sampled host tokens out, wall clock."""
         sched = Scheduler(engine, prefill_chunk_size=0, max_tokens_per_step=opt.max_tokens_per_step, max_running=B,
                           run_ahead=True)
-        fill(B, sched)
+        fill(B, ctx, sched, steps=W + E2E_STEPS)
         while any(not r.prefill_done for r in sched.active.values()) or sched.waiting:
             sched.step()
         for _ in range(W):
@@ -356,7 +431,7 @@ def main() -> int:
         torch.cuda.synchronize()
         t = time.perf_counter()
         produced = 0
-        for _ in range(K):  # each call launches a step and returns the host tokens of the step before it
+        for _ in range(E2E_STEPS):  # each call launches a step and returns the host tokens of the step before it
             produced += sum(1 for ev in sched.step() if ev.token is not None)
         torch.cuda.synchronize()
         wall = time.perf_counter() - t
@@ -364,21 +439,35 @@ def main() -> int:
             sched.cancel(rid)
         return produced / wall, produced
 
+    def summarise(B, c, run_ms, launches):
+        med = statistics.median(run_ms)
+        return {"tok_s": B * K / med * 1e3, "ms_per_step": med / K, "launches": launches, "context": c,
+                "runs_ms_per_step": [round(x / K, 4) for x in run_ms]}
+
     results = {}
     for B in batches:
-        total_ms, launches = decode_device(B)
-        results[B] = {"tok_s": B * K / total_ms * 1e3, "ms_per_step": total_ms / K, "launches": launches}
+        results[B] = summarise(B, ctx, *decode_device(B, ctx))
         print(f"[bench] decode batch {B}: {results[B]}", file=sys.stderr, flush=True)
+    long_results = {}
+    for c in long_ctx:
+        long_results[c] = summarise(args.batch, c, *decode_device(args.batch, c))
+        print(f"[bench] decode batch {args.batch} after {c}-token prompts: {long_results[c]}", file=sys.stderr, flush=True)
     e2e = None
     if not args.no_e2e:
         tok_s, produced = decode_e2e(args.batch)
         e2e = {"value": round(tok_s, 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": int(engine.layout.size * 4), "d2h_bytes_per_step": int(args.batch * 4)}
-        print(f"[bench] e2e {e2e} ({produced} tokens)", file=sys.stderr, flush=True)
+               "h2d_bytes_per_step": int(engine.last_h2d_bytes), "d2h_bytes_per_step": int(args.batch * 4)}
+        print(f"[bench] e2e {e2e} ({produced} tokens in {E2E_STEPS} steps)", file=sys.stderr, flush=True)
     sampler.stop()
 
+    def roofline_frac(B, r):
+        """Bytes a decode step of B requests must read (weights once + the live cache at the middle of the runs)
+        over its time, as a fraction of the measured copy bandwidth."""
+        mid = r["context"] + W + (RUNS * K + 1) / 2.0
+        return (weight_bytes + B * mid * kv_per_token) / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
+
     main_r = results[args.batch]
-    mean_ctx = ctx + W + (K + 1) / 2.0
+    mean_ctx = ctx + W + (RUNS * K + 1) / 2.0   # the runs follow one another: the median run sits near the middle
     step_bytes = weight_bytes + args.batch * mean_ctx * kv_per_token
     achieved = step_bytes / (main_r["ms_per_step"] * 1e-3) / 1e9
     line = {
@@ -391,14 +480,21 @@ def main() -> int:
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
                    "seq_len": ctx, "page_size": page, "prefill_tokens": 2048, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (15 GB of weights per step)", "decode": "CUDA graph per batch size",
-                   "peaks": peaks["source"]},
+                   "peaks": peaks["source"], "decode_runs": RUNS, "e2e_steps": E2E_STEPS},
         "e2e": e2e,
         "gpu_launches": int(main_r["launches"][0]),
         "library_launches": int(main_r["launches"][1]),
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
-        "points": {f"decode_b{B}": round(results[B]["tok_s"], 1) for B in batches if B != args.batch},
+        "points": {**{f"decode_b{B}": round(results[B]["tok_s"], 1) for B in batches if B != args.batch},
+                   **{f"decode_b{args.batch}_ctx{c}": round(r["tok_s"], 1) for c, r in long_results.items()},
+                   **{f"prefill_{t}": p["value"] for t, p in prefill_points.items()}},
+        "points_frac": {**{f"decode_b{B}": round(roofline_frac(B, results[B]), 4) for B in batches if B != args.batch},
+                        **{f"decode_b{args.batch}_ctx{c}": round(roofline_frac(args.batch, r), 4)
+                           for c, r in long_results.items()},
+                        **{f"prefill_{t}": p["frac"] for t, p in prefill_points.items()}},
+        "runs_ms_per_step": main_r["runs_ms_per_step"],
         "clocks": sampler.summary(),
     }
     print(json.dumps(line))

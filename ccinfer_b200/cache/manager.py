@@ -1,183 +1,174 @@
-"""Cache manager: pages of keys and values per cache group, block tables per request, state slots.
+"""Cache manager: pages per cache group, block tables per request, state slots.
 
-What 7QiC/ccInfer's manager does is kept where it applies: pages of a fixed
-number of tokens, a FIFO free list (src/cache/kv_cache_manager.cpp:78-82,
-242-244), pages taken on demand just before a step
-(src/worker/batch_translator.cpp:196-211), everything of a request given back
-when it ends (src/worker/worker.cpp:317-326), validate-then-mutate on release
-with double-free detection (src/cache/kv_cache_manager.cpp:216-230), and a
-transactional step: pages taken for a step that fails are returned
-(src/worker/batch_translator.cpp:72-75, 579-589).  Prefix sharing, reference
-counts and the LRU list are left out: a page has exactly one owner.
+The bookkeeping itself is native: ``csrc/host/host_core.cpp`` behind the C interface of
+``csrc/host/ccinfer.h``; the classes here give it the package's names and exceptions and let requests be
+named by any hashable id.  What 7QiC/ccInfer's manager does is kept where it applies: pages of a fixed number
+of tokens, a FIFO free list (src/cache/kv_cache_manager.cpp:78-82, 242-244), pages taken on demand just
+before a step (src/worker/batch_translator.cpp:196-211), everything of a request given back when it ends
+(src/worker/worker.cpp:317-326), validate-then-mutate on release with double-free detection
+(src/cache/kv_cache_manager.cpp:216-230), and a transactional step: pages taken for a step that fails are
+returned (src/worker/batch_translator.cpp:72-75, 579-589).  Prefix sharing, reference counts and the LRU list
+are left out: a page has exactly one owner.
 
 Beyond the reference:
 
-* cache groups.  Layers whose mixers need the same thing (all keys, or a
-  window of W keys) form a group with a page pool and block tables of its own.
-  In a window group the pages that every later query has passed are given
-  back while the request still runs.
-* state slots.  A request gets a slot id when it is opened; the slot indexes
-  per-request state tensors of fixed size (for mixers that have such state)
-  and is returned when the request is closed.
+* cache groups.  Layers whose mixers need the same thing (all tokens, or a window of W) form a group with a
+  page pool and block tables of its own.  In a window group the pages that every later query has passed are
+  given back while the request still runs.
+* state slots.  A request gets a slot id when it is opened; the slot indexes per-request state tensors of
+  fixed size (for mixers that have such state) and is returned when the request is closed.
 
-Everything here is host-side bookkeeping; the device tensors (one set per
-layer that keeps a cache) belong to the engine.
+Everything here is host-side bookkeeping; the device tensors (one set per layer that keeps a cache) belong to
+the engine.
 """
 from __future__ import annotations
 
-import collections
 import dataclasses
 from typing import Dict, Hashable, List, Optional, Tuple
 
 import numpy as np
 
-from ..errors import (InvalidArgument, KVBlockDoubleFree, KVBlockExhausted, KVInvalidBlockTable, SlotExhausted)
+from ..errors import InvalidArgument, KVInvalidBlockTable
+from ..native import HostCore
 
 
 @dataclasses.dataclass(frozen=True)
 class GroupSpec:
-    """A cache group: which keys its layers read (``window`` None = all) and its pool."""
+    """A cache group: which tokens its layers read (``window`` None = all) and its pool."""
     key: Tuple
     window: Optional[int]
     page_size: int
     num_pages: int
 
 
+class _Names:
+    """Hashable ids <-> the 64-bit numbers by which the host core knows owners and sequences."""
+
+    def __init__(self):
+        self._num: Dict[Hashable, int] = {}
+        self._next = 1
+
+    def number(self, name: Hashable, create: bool = True) -> int:
+        n = self._num.get(name)
+        if n is None:
+            if not create:
+                return 0   # a number nobody has
+            n = self._num[name] = self._next
+            self._next += 1
+        return n
+
+    def forget(self, name: Hashable) -> None:
+        self._num.pop(name, None)
+
+
 class PagePool:
     """Pages of one group: FIFO free list and an owner per page."""
 
-    def __init__(self, num_pages: int):
-        if num_pages <= 0:
-            raise InvalidArgument("a page pool needs at least one page")
-        self.num_pages = num_pages
-        self._free = collections.deque(range(num_pages))
-        self._owner: List[Optional[Hashable]] = [None] * num_pages
-        self.high_water = 0
+    def __init__(self, num_pages: int, _core: HostCore = None, _group: int = 0, _names: _Names = None):
+        self._core = _core or HostCore([(None, 1, num_pages)], 1, 1, max(1, num_pages))
+        self._g = _group
+        self._names = _names or _Names()
+        self.num_pages = self._core.stats().pages_total[self._g]
 
     @property
     def free_pages(self) -> int:
-        return len(self._free)
+        return self._core.stats().pages_free[self._g]
 
     @property
     def used_pages(self) -> int:
-        return self.num_pages - len(self._free)
+        return self.num_pages - self.free_pages
+
+    @property
+    def high_water(self) -> int:
+        return self._core.stats().pages_high_water[self._g]
 
     def take(self, owner: Hashable, n: int) -> List[int]:
-        if n < 0:
-            raise InvalidArgument("cannot take a negative number of pages")
-        if n > len(self._free):
-            raise KVBlockExhausted(f"{n} pages wanted, {len(self._free)} free of {self.num_pages}")
-        pages = [self._free.popleft() for _ in range(n)]
-        for p in pages:
-            self._owner[p] = owner
-        self.high_water = max(self.high_water, self.used_pages)
-        return pages
+        return self._core.pool_take(self._g, self._names.number(owner), n)
 
     def give_back(self, owner: Hashable, pages: List[int]) -> None:
-        """All-or-nothing: checks every page before any is freed."""
-        seen = set()
-        for p in pages:
-            if not isinstance(p, int) or not (0 <= p < self.num_pages):
-                raise KVInvalidBlockTable(f"page id {p!r} is outside the pool of {self.num_pages}")
-            if p in seen:
-                raise KVBlockDoubleFree(f"page {p} is named twice in one release")
-            if self._owner[p] is None:
-                raise KVBlockDoubleFree(f"page {p} is already free")
-            if self._owner[p] != owner:
-                raise KVInvalidBlockTable(f"page {p} belongs to {self._owner[p]!r}, not to {owner!r}")
-            seen.add(p)
-        for p in pages:
-            self._owner[p] = None
-            self._free.append(p)
+        """All-or-nothing: every page is checked before any is freed."""
+        self._core.pool_give_back(self._g, self._names.number(owner), list(pages))
 
     def owner_of(self, page: int):
-        return self._owner[page]
+        n = self._core.pool_owner(self._g, page)
+        if n is None:
+            return None
+        for name, num in self._names._num.items():
+            if num == n:
+                return name
+        return n
 
 
 class SlotPool:
     """Fixed number of per-request state slots."""
 
-    def __init__(self, num_slots: int):
-        if num_slots <= 0:
-            raise InvalidArgument("at least one state slot is needed")
-        self.num_slots = num_slots
-        self._free = collections.deque(range(num_slots))
-        self._used = [False] * num_slots
+    def __init__(self, num_slots: int, _core: HostCore = None):
+        self._core = _core or HostCore([], num_slots, max(1, num_slots), 1)
+        self.num_slots = self._core.stats().slots_total
 
     @property
     def free_slots(self) -> int:
-        return len(self._free)
+        return self._core.stats().slots_free
 
     def take(self) -> int:
-        if not self._free:
-            raise SlotExhausted(f"all {self.num_slots} request slots are in use")
-        s = self._free.popleft()
-        self._used[s] = True
-        return s
+        return self._core.slot_take()
 
     def give_back(self, slot: int) -> None:
-        if not (0 <= slot < self.num_slots):
-            raise InvalidArgument(f"slot {slot} is outside the pool of {self.num_slots}")
-        if not self._used[slot]:
-            raise KVBlockDoubleFree(f"slot {slot} is already free")
-        self._used[slot] = False
-        self._free.append(slot)
+        self._core.slot_give_back(int(slot))
 
 
 class RequestCache:
     """What one request holds: its slot, how many tokens are cached, and per group a block table.
 
-    ``tables[g][i]`` is the physical page of logical page i (tokens i*P .. i*P+P-1) or -1
-    when that page was never needed or has been given back (window groups)."""
+    ``tables[g][i]`` is the physical page of logical page i (tokens i*P .. i*P+P-1) or -1 when that page has
+    been given back (window groups)."""
 
-    def __init__(self, req_id: Hashable, slot: int, n_groups: int):
-        self.req_id = req_id
-        self.slot = slot
-        self.ctx_len = 0
-        self.tables: List[List[int]] = [[] for _ in range(n_groups)]
-        # the same tables as int32 arrays (with spare capacity), kept in step by the manager: what the step
-        # function copies into its pinned buffer without walking a Python list per request and step
-        self._arrays: List[np.ndarray] = [np.full(16, -1, dtype=np.int32) for _ in range(n_groups)]
-        # pages taken by reserve() and not yet committed: [(group, logical index)]
-        self._pending: List[Tuple[int, int]] = []
-        self._pending_tokens = 0
+    def __init__(self, core: HostCore, req_id: Hashable, seq: int, slot: int, n_groups: int):
+        self._core, self.req_id, self.seq, self.slot, self._n_groups = core, req_id, seq, slot, n_groups
 
-    def pages_held(self, g: int) -> int:
-        return sum(1 for p in self.tables[g] if p >= 0)
+    @property
+    def ctx_len(self) -> int:
+        return self._core.seq_state(self.seq)[1]
+
+    @property
+    def tables(self) -> List[List[int]]:
+        return [self._core.block_table(self.seq, g) for g in range(self._n_groups)]
+
+    def table_len(self, g: int) -> int:
+        """Logical pages the table of group g spans (given-back ones included)."""
+        return self._core.table_len(self.seq, g)
 
     def table_array(self, g: int) -> np.ndarray:
-        """The block table of group g as an int32 array (a view: do not keep it across steps)."""
-        return self._arrays[g][:len(self.tables[g])]
+        return np.asarray(self._core.block_table(self.seq, g), dtype=np.int32)
 
-    def _append(self, g: int, page: int) -> None:
-        n = len(self.tables[g])
-        if n == self._arrays[g].size:
-            grown = np.full(2 * n, -1, dtype=np.int32)
-            grown[:n] = self._arrays[g]
-            self._arrays[g] = grown
-        self._arrays[g][n] = page
-        self.tables[g].append(page)
-
-    def _pop(self, g: int) -> None:
-        self.tables[g].pop()
-
-    def _drop(self, g: int, i: int) -> None:
-        self.tables[g][i] = -1
-        self._arrays[g][i] = -1
+    def pages_held(self, g: int) -> int:
+        return sum(1 for p in self._core.block_table(self.seq, g) if p >= 0)
 
 
 class CacheManager:
-    def __init__(self, groups: List[GroupSpec], max_requests: int):
+    def __init__(self, groups: List[GroupSpec], max_requests: int, max_tokens_per_step: int = None,
+                 max_context: int = None):
+        """``max_tokens_per_step`` and ``max_context`` size the step arrays that the host core lays out (the
+        engine names them; the defaults serve a manager used for its bookkeeping alone)."""
         self.groups = list(groups)
-        self.pools = [PagePool(g.num_pages) for g in self.groups]
-        self.slots = SlotPool(max_requests)
+        if max_requests <= 0:
+            raise InvalidArgument("at least one state slot is needed")
+        if max_context is None:
+            max_context = max([g.num_pages * g.page_size for g in self.groups if g.window is None] or
+                              [g.num_pages * g.page_size for g in self.groups] or [1])
+        self.core = HostCore([(g.window, g.page_size, g.num_pages) for g in self.groups], max_requests,
+                             max_tokens_per_step or max(max_requests, 1), max(1, max_context))
+        self._names = _Names()
+        self.pools = [PagePool(g.num_pages, self.core, i, self._names) for i, g in enumerate(self.groups)]
+        self.slots = SlotPool(max_requests, self.core)
         self.requests: Dict[Hashable, RequestCache] = {}
 
     # -- requests ----------------------------------------------------------------
     def open(self, req_id: Hashable) -> RequestCache:
         if req_id in self.requests:
             raise InvalidArgument(f"request {req_id!r} is already open")
-        rc = RequestCache(req_id, self.slots.take(), len(self.groups))
+        seq = self._names.number(req_id)
+        rc = RequestCache(self.core, req_id, seq, self.core.alloc_seq(seq), len(self.groups))
         self.requests[req_id] = rc
         return rc
 
@@ -190,12 +181,9 @@ class CacheManager:
     def close(self, req_id: Hashable) -> None:
         """Gives back every page and the slot of a request."""
         rc = self.get(req_id)
-        for g, pool in enumerate(self.pools):
-            pool.give_back(req_id, [p for p in rc.tables[g] if p >= 0])
-            rc.tables[g] = []
-            rc._arrays[g] = np.full(16, -1, dtype=np.int32)
-        self.slots.give_back(rc.slot)
+        self.core.free_seq(rc.seq)
         del self.requests[req_id]
+        self._names.forget(req_id)
 
     # -- page arithmetic -----------------------------------------------------------
     def first_needed_page(self, g: int, ctx_len: int) -> int:
@@ -208,8 +196,7 @@ class CacheManager:
 
     def pages_needed(self, req_id: Hashable, n_new: int) -> List[int]:
         """Pages each group would have to take to hold ``n_new`` more tokens of the request."""
-        rc = self.get(req_id)
-        return [self._pages_needed(rc, g, n_new) for g in range(len(self.groups))]
+        return self.core.pages_needed(self.get(req_id).seq, n_new)
 
     def pages_needed_for(self, ctx_len: int, n_new: int, g: int) -> int:
         """Same for a request described by its length only (nothing held beyond ctx_len's pages)."""
@@ -217,65 +204,20 @@ class CacheManager:
         have = -(-ctx_len // P)
         return -(-(ctx_len + n_new) // P) - have
 
-    def _pages_needed(self, rc: RequestCache, g: int, n_new: int) -> int:
-        P = self.groups[g].page_size
-        return max(0, -(-(rc.ctx_len + n_new) // P) - len(rc.tables[g]))
-
     # -- a step: reserve, then commit or roll back ------------------------------------
     def reserve(self, req_id: Hashable, n_new: int) -> None:
         """Takes the pages for tokens ctx_len .. ctx_len + n_new - 1 in every group.
 
         Either all groups get their pages or none keeps any (KVBlockExhausted)."""
-        rc = self.get(req_id)
-        if n_new <= 0:
-            raise InvalidArgument("a step brings at least one token per request")
-        if rc._pending_tokens:
-            raise InvalidArgument(f"request {req_id!r} has an uncommitted reservation")
-        taken: List[Tuple[int, int]] = []
-        try:
-            for g, pool in enumerate(self.pools):
-                n = self._pages_needed(rc, g, n_new)
-                pages = pool.take(req_id, n)
-                for p in pages:
-                    rc._append(g, p)
-                    taken.append((g, len(rc.tables[g]) - 1))
-        except KVBlockExhausted:
-            self._undo(rc, taken)
-            raise
-        rc._pending = taken
-        rc._pending_tokens = n_new
-
-    def _undo(self, rc: RequestCache, taken: List[Tuple[int, int]]) -> None:
-        for g in range(len(self.groups)):
-            idx = sorted((i for gg, i in taken if gg == g), reverse=True)
-            pages = [rc.tables[g][i] for i in idx]
-            self.pools[g].give_back(rc.req_id, pages)
-            for i in idx:  # they are the tail of the table
-                assert i == len(rc.tables[g]) - 1
-                rc._pop(g)
+        self.core.reserve(self.get(req_id).seq, n_new)
 
     def rollback(self, req_id: Hashable) -> None:
         """Returns the pages of a reservation whose step did not happen."""
-        rc = self.get(req_id)
-        self._undo(rc, rc._pending)
-        rc._pending, rc._pending_tokens = [], 0
+        self.core.rollback(self.get(req_id).seq)
 
     def commit(self, req_id: Hashable) -> None:
         """The step ran: the tokens are cached; window groups give back pages every later query has passed."""
-        rc = self.get(req_id)
-        if not rc._pending_tokens:
-            raise InvalidArgument(f"request {req_id!r} has nothing reserved")
-        rc.ctx_len += rc._pending_tokens
-        rc._pending, rc._pending_tokens = [], 0
-        for g, spec in enumerate(self.groups):
-            if spec.window is None:
-                continue
-            first = min(self.first_needed_page(g, rc.ctx_len), len(rc.tables[g]))
-            stale = [i for i in range(first) if rc.tables[g][i] >= 0]
-            if stale:
-                self.pools[g].give_back(req_id, [rc.tables[g][i] for i in stale])
-                for i in stale:
-                    rc._drop(g, i)
+        self.core.commit(self.get(req_id).seq)
 
     # -- addressing -------------------------------------------------------------------
     def slot_of(self, rc: RequestCache, g: int, position: int) -> int:
@@ -288,37 +230,21 @@ class CacheManager:
 
     # -- figures ------------------------------------------------------------------------
     def stats(self) -> dict:
+        st = self.core.stats()
         return {
-            "requests": len(self.requests),
-            "slots_total": self.slots.num_slots,
-            "slots_free": self.slots.free_slots,
+            "requests": st.seqs,
+            "slots_total": st.slots_total,
+            "slots_free": st.slots_free,
             "groups": [
                 {"key": list(map(str, g.key)), "window": g.window, "page_size": g.page_size,
-                 "pages_total": pool.num_pages, "pages_free": pool.free_pages, "pages_used": pool.used_pages,
-                 "pages_high_water": pool.high_water}
-                for g, pool in zip(self.groups, self.pools)],
+                 "pages_total": st.pages_total[i], "pages_free": st.pages_free[i],
+                 "pages_used": st.pages_total[i] - st.pages_free[i], "pages_high_water": st.pages_high_water[i]}
+                for i, g in enumerate(self.groups)],
         }
 
     def check_consistency(self) -> None:
-        """Every page is free or in exactly one table of its owner (used by tests)."""
-        for g, pool in enumerate(self.pools):
-            held = {}
-            for rc in self.requests.values():
-                for p in rc.tables[g]:
-                    if p >= 0:
-                        if p in held:
-                            raise AssertionError(f"group {g}: page {p} held by {held[p]!r} and {rc.req_id!r}")
-                        held[p] = rc.req_id
-            free = list(pool._free)
-            if len(set(free)) != len(free):
-                raise AssertionError(f"group {g}: a page is on the free list twice")
-            if set(free) & set(held):
-                raise AssertionError(f"group {g}: pages both free and held: {set(free) & set(held)}")
-            if len(free) + len(held) != pool.num_pages:
-                raise AssertionError(f"group {g}: {pool.num_pages - len(free) - len(held)} pages lost")
-            for p, owner in held.items():
-                if pool.owner_of(p) != owner:
-                    raise AssertionError(f"group {g}: page {p} owner mismatch")
-            for rc in self.requests.values():
-                if rc.table_array(g).tolist() != rc.tables[g]:
-                    raise AssertionError(f"group {g}: the array of request {rc.req_id!r} differs from its table")
+        """Every page is free or in exactly one table of its owner, none is lost (used by tests)."""
+        self.core.check()
+        for rid, rc in self.requests.items():
+            if self.core.seq_state(rc.seq)[0] != rc.slot:
+                raise AssertionError(f"request {rid!r}: its slot moved")

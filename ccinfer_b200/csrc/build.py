@@ -26,7 +26,8 @@ from ..errors import ExtensionMissing
 
 CSRC = os.path.dirname(os.path.abspath(__file__))
 
-# group -> source files.  "core" is everything a model step needs.
+# group -> source files.  "core" is every kernel a model step needs; "host" is the C++ host core (cache manager,
+# request slots, the arrays of a step) behind the C interface of host/ccinfer.h: no device code in it.
 GROUPS = {
     "core": [
         "elementwise.cu",
@@ -46,8 +47,12 @@ GROUPS = {
         "sampling.cu",
         "random_init.cu",
     ],
+    "host": [
+        "host/host_core.cpp",
+    ],
 }
 GROUP_LIBS = {"core": ["-lcublas"]}
+GROUP_HEADERS = {"host": ["host/ccinfer.h"]}   # default: every header beside the kernels
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -70,7 +75,7 @@ def find_nvcc() -> str:
 def _stamp(group: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS + GROUP_LIBS.get(group, [])).encode())
-    headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+    headers = GROUP_HEADERS.get(group) or sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
     for name in headers + GROUPS[group]:
         h.update(name.encode())
         with open(os.path.join(CSRC, name), "rb") as f:
@@ -119,7 +124,7 @@ def library_path(group: str = "core", verbose: bool = True) -> str:
     nvcc = find_nvcc()
     srcs = GROUPS[group]
     if verbose:
-        _say(f"compiling {len(srcs)} CUDA files of group '{group}' for sm_100a into {bdir}")
+        _say(f"compiling {len(srcs)} files of group '{group}'" + (" for sm_100a" if group != "host" else "") + f" into {bdir}")
     t0 = time.time()
     done = threading.Event()
 
@@ -130,7 +135,7 @@ def library_path(group: str = "core", verbose: bool = True) -> str:
     th = threading.Thread(target=ticker, daemon=True)
     if verbose:
         th.start()
-    objs = [os.path.join(bdir, f"{group}_{os.path.splitext(s)[0]}.{os.getpid()}.o") for s in srcs]
+    objs = [os.path.join(bdir, f"{group}_{os.path.splitext(os.path.basename(s))[0]}.{os.getpid()}.o") for s in srcs]
     try:
         with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
             futs = {ex.submit(_compile_one, nvcc, s, o): s for s, o in zip(srcs, objs)}

@@ -8,6 +8,10 @@ src/worker/batch_translator.cpp:241-431, src/model/model_runner.h:25-247) with
 these differences: logits are computed only for the wanted rows and handed
 out (the reference computes all rows and keeps them inside the runner),
 sampling is a separate call, and nothing is allocated per step.
+
+Validation, the taking of pages, the step arrays and commit or rollback are the native host core's
+(``csrc/host/host_core.cpp``, ``ccinfer_forward``); the device work of a step, i.e. the model's parts launching
+their kernels, is the runner that this class registers there.
 """
 from __future__ import annotations
 
@@ -21,10 +25,11 @@ from .. import kernels
 from ..cache.manager import CacheManager, GroupSpec
 from ..config.registry import load_config
 from ..errors import InvalidArgument, KVBlockExhausted, RequestTooLong, Unsupported
+from ..native import RunnerFailed
 from ..weights.loader import open_weights, random_fetch
 from .plan import ModelPlan
 from .runtime import Runtime
-from .step import GroupStep, LayerCache, StepContext, StepLayout
+from .step import GroupStep, LayerCache, StepContext
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -143,17 +148,25 @@ class Engine:
             limit = min(limit, plan.max_position)
         self.max_context = min(opt.max_context, limit) if opt.max_context else limit
         self.cache = CacheManager([GroupSpec(k, w, P, n) for k, w, n in zip(group_keys, windows, pages)],
-                                  opt.max_requests)
+                                  opt.max_requests, opt.max_tokens_per_step, self.max_context)
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in plan.parts())
 
-        # ---- the step arrays ----
-        stride = -(-self.max_context // P)
-        self.layout = lay = StepLayout(opt.max_tokens_per_step, opt.max_requests, [stride] * len(group_keys))
-        # two pinned staging buffers in turn: the host may fill one while the copy of the other is in flight
-        self._host_bufs = [torch.zeros(lay.size, dtype=torch.int32).pin_memory() for _ in range(2)]
-        self._host_events = [None, None]
+        # ---- the step arrays: two layouts of the host core (a small one for steps of up to max_requests token
+        # rows, i.e. every decode step, and a large one), each with one device buffer and two pinned staging
+        # buffers in turn: the host may fill one while the copy of the other is in flight ----
+        core = self.cache.core
+        self._layouts = [core.layout(0), core.layout(1)]
+        self._host_bufs = [[torch.zeros(l.size_words, dtype=torch.int32).pin_memory() for _ in range(2)]
+                           for l in self._layouts]
+        self._host_np = [[b.numpy() for b in pair] for pair in self._host_bufs]
+        self._host_events = [[None, None], [None, None]]
         self._host_turn = 0
-        self._dev_buf = torch.zeros(lay.size, dtype=torch.int32, device=rt.device)
+        self._dev_bufs = [torch.zeros(l.size_words, dtype=torch.int32, device=rt.device) for l in self._layouts]
+        core.set_runner(self._run_step)
+        self._runner_fn = None        # in place of the forward pass: see try_step
+        self._runner_error = None
+        self._step_logits = None
+        self._step_bucket = 0
         n_rows = max(opt.max_requests, 1)
         self._sample_tokens = torch.zeros(opt.max_tokens_per_step, dtype=torch.int32, device=rt.device)
         self._sample_host = [torch.zeros((5, opt.max_tokens_per_step), dtype=torch.int32).pin_memory()
@@ -168,6 +181,7 @@ class Engine:
         self._last_logits = None      # (address, shape) of the logits that the most recent step returned
         self._sample_dev = torch.zeros((5, opt.max_tokens_per_step), dtype=torch.int32, device=rt.device)
         self.steps_run = 0
+        self.last_h2d_bytes = 0       # bytes of the step arrays that the most recent step copied to the device
         self.graph_replays = 0
         self._graphs: Dict[int, tuple] = {}
 
@@ -263,159 +277,133 @@ class Engine:
         return self.cache.get(req_id).ctx_len
 
     # ------------------------------------------------------------------------------------
-    def _validate(self, entries: List[StepEntry]) -> None:
-        if not entries:
-            raise InvalidArgument("a step needs at least one entry")
-        if len(entries) > self.options.max_requests:
-            raise InvalidArgument(f"{len(entries)} entries in a step, at most {self.options.max_requests}")
-        seen = set()
-        total = wanted = 0
-        for e in entries:
-            if e.req_id in seen:
-                raise InvalidArgument(f"request {e.req_id!r} appears twice in one step")
-            seen.add(e.req_id)
-            n = len(e.tokens)
-            if n == 0:
-                raise InvalidArgument(f"request {e.req_id!r} brings no tokens")
-            total += n
-            rc = self.cache.get(e.req_id)
-            if rc.ctx_len + n > self.max_context:
-                raise RequestTooLong(f"request {e.req_id!r}: {rc.ctx_len} cached + {n} new tokens exceed the "
-                                     f"limit of {self.max_context}")
-            if min(e.tokens) < 0:
-                if n != 1 or e.tokens[0] != PENDING or rc.slot not in self._pending_slots:
-                    raise InvalidArgument(f"request {e.req_id!r}: token ids are non-negative (PENDING stands alone, "
-                                          f"after a sample_async for the request)")
-            for w in e.want:
-                if not (0 <= w < n):
-                    raise InvalidArgument(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
-            wanted += len(e.want)
-        if total > self.options.max_tokens_per_step:
-            raise InvalidArgument(f"{total} tokens in a step, at most {self.options.max_tokens_per_step}")
-        if wanted > self.options.max_tokens_per_step:  # a place may be named twice: the rows have their own limit
-            raise InvalidArgument(f"{wanted} logits rows wanted in a step, at most {self.options.max_tokens_per_step}")
-
-    def _build(self, entries: List[StepEntry], pad_to: int = 0) -> StepContext:
-        """Fills the pinned buffer, copies it to the device and returns the views of the step."""
-        lay = self.layout
-        turn = self._host_turn
-        self._host_turn ^= 1
-        if self._host_events[turn] is not None:
-            self._host_events[turn].synchronize()  # its last copy has left the buffer
-        host_buf = self._host_bufs[turn]
-        host = host_buf.numpy()
-        # single-token entries (decoding requests) first: kernels treat the two kinds of rows differently
-        order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
-        place = {i: k for k, i in enumerate(order)}
-        given = entries
-        entries = [given[i] for i in order]
-        B = len(entries)
-        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
-        cu = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(counts, out=cu[1:])
-        T = int(cu[-1])
-        Bp = max(B, pad_to)
-        Tp = T + (Bp - B)
-        rcs = [self.cache.get(e.req_id) for e in entries]
-        pos0 = np.fromiter((rc.ctx_len for rc in rcs), dtype=np.int64, count=B)
-
-        tok = host[lay.o_token_ids:lay.o_token_ids + Tp]
-        posv = host[lay.o_positions:lay.o_positions + Tp]
-        eot = host[lay.o_entry_of_token:lay.o_entry_of_token + Tp]
-        for b, e in enumerate(entries):
-            tok[cu[b]:cu[b + 1]] = e.tokens
-        eot[:T] = np.repeat(np.arange(B, dtype=np.int32), counts)
-        posv[:T] = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1] - pos0, counts)
-        slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=B)
-        n_single = int((counts == 1).sum())  # they come first
-        first = tok[:n_single]
-        pending = first < 0
-        if pending.any():
-            first[pending] = -1 - slots[:n_single][pending]  # resolved on the device from the pending tokens
-        # a pending token serves one step: this one reads it, or brings the request's token itself
-        self._pending_slots.difference_update(slots.tolist())
-        tok[T:Tp] = 0
-        posv[T:Tp] = 0
-        eot[T:Tp] = -1
-
-        if pad_to:  # a decode step padded to a graph's size: one row per entry, the padding's rows are ignored
-            rows = list(range(Bp))
-        else:
-            rows = [int(cu[place[i]]) + int(w) for i, e in enumerate(given) for w in e.want]
-        R = len(rows)
-        lr = host[lay.o_logit_rows:lay.o_logit_rows + max(R, 1)]
-        rs = host[lay.o_row_slot:lay.o_row_slot + max(R, 1)]
-        if pad_to:
-            row_slots = slots.tolist() + [-1] * (Bp - B)
-        else:
-            row_slots = [rcs[place[i]].slot for i, e in enumerate(given) for _ in e.want]
-        if R:
-            lr[:R] = rows
-            rs[:R] = row_slots
-        hcu = host[lay.o_cu_q:lay.o_cu_q + Bp + 1]
-        hcu[:B + 1] = cu
-        hcu[B + 1:] = np.arange(T + 1, Tp + 1)
-        hp0 = host[lay.o_pos0:lay.o_pos0 + Bp]
-        hca = host[lay.o_ctx_after:lay.o_ctx_after + Bp]
-        hss = host[lay.o_state_slot:lay.o_state_slot + Bp]
-        hp0[:B] = pos0
-        hca[:B] = pos0 + counts
-        hss[:B] = slots
-        hp0[B:] = 0
-        hca[B:] = 0
-        hss[B:] = -1
-
+    def _context(self, info) -> StepContext:
+        """The views of the step that the host core has just laid out; its arrays go to the device."""
+        which, turn = info.layout, self._turn_in_use
+        lay, host, dev = self._layouts[which], self._host_np[which][turn], self._dev_bufs[which]
+        Tp, Bp, R = info.n_tokens, info.n_entries, info.n_logit_rows
         step = StepContext()
         step.n_tokens, step.n_entries, step.n_logit_rows = Tp, Bp, R
-        step.n_single = n_single + (Bp - B) if n_single == B else n_single   # padding rows are single rows too
-        step.max_q_len = int(counts.max())
-        step.max_ctx = int((pos0 + counts).max())
-        dev = self._dev_buf
+        step.n_single, step.max_q_len, step.max_ctx = info.n_single, info.max_q_len, info.max_ctx
 
         def dv(off, n):
             return dev[off:off + n]
 
-        step.token_ids = dv(lay.o_token_ids, Tp)
-        step.positions = dv(lay.o_positions, Tp)
-        step.entry_of_token = dv(lay.o_entry_of_token, Tp)
-        step.logit_rows = dv(lay.o_logit_rows, max(R, 1))
-        step.row_slot = dv(lay.o_row_slot, max(R, 1))
-        step.pending_tokens = self._pending_tokens
-        self._last_row_slot = (step.row_slot, row_slots[:len(given)] if pad_to else row_slots)
-        self._last_logits = None   # set by step() once the logits exist
-        step.cu_q = dv(lay.o_cu_q, Bp + 1)
-        step.pos0 = dv(lay.o_pos0, Bp)
-        step.ctx_after = dv(lay.o_ctx_after, Bp)
-        step.state_slot = dv(lay.o_state_slot, Bp)
+        def hv(off, n):
+            return host[off:off + n]
 
+        step.token_ids = dv(lay.token_ids, Tp)
+        step.positions = dv(lay.positions, Tp)
+        step.entry_of_token = dv(lay.entry_of_token, Tp)
+        step.logit_rows = dv(lay.logit_rows, max(R, 1))
+        step.row_slot = dv(lay.row_slot, max(R, 1))
+        step.pending_tokens = self._pending_tokens
+        step.cu_q = dv(lay.cu_q, Bp + 1)
+        step.pos0 = dv(lay.pos0, Bp)
+        step.ctx_after = dv(lay.ctx_after, Bp)
+        step.state_slot = dv(lay.state_slot, Bp)
+        stride = lay.block_table_stride
         for g, spec in enumerate(self.cache.groups):
-            P, stride = spec.page_size, lay.group_strides[g]
-            sm = host[lay.o_slot_map[g]:lay.o_slot_map[g] + Tp]
-            bt = host[lay.o_block_table[g]:lay.o_block_table[g] + Bp * stride].reshape(Bp, stride)
-            if T == B:  # every entry brings one token: no per-entry arrays
-                for b, rc in enumerate(rcs):
-                    table = rc.table_array(g)
-                    bt[b, :table.size] = table
-                    pb = int(pos0[b])
-                    sm[b] = int(table[pb // P]) * P + pb % P
-            else:
-                for b, rc in enumerate(rcs):
-                    table = rc.table_array(g)
-                    bt[b, :table.size] = table
-                    p = np.arange(pos0[b], pos0[b] + counts[b])
-                    sm[cu[b]:cu[b + 1]] = table[p // P] * P + p % P
-            sm[T:Tp] = -1
             step.groups.append(GroupStep(
-                index=g, page_size=P, num_pages=spec.num_pages, window=spec.window,
-                slot_map=dv(lay.o_slot_map[g], Tp),
-                block_table=dv(lay.o_block_table[g], Bp * stride).view(Bp, stride),
-                host_slot_map=sm, host_block_table=bt))
-        step.host = _HostView(tok, posv, eot, lr[:R], hcu, hp0, hca, hss)
-        self._dev_buf.copy_(host_buf, non_blocking=True)
+                index=g, page_size=spec.page_size, num_pages=spec.num_pages, window=spec.window,
+                slot_map=dv(lay.slot_map[g], Tp),
+                block_table=dv(lay.block_table[g], Bp * stride).view(Bp, stride),
+                host_slot_map=hv(lay.slot_map[g], Tp),
+                host_block_table=hv(lay.block_table[g], Bp * stride).reshape(Bp, stride)))
+        step.host = _HostView(hv(lay.token_ids, Tp), hv(lay.positions, Tp), hv(lay.entry_of_token, Tp),
+                              hv(lay.logit_rows, R), hv(lay.cu_q, Bp + 1), hv(lay.pos0, Bp), hv(lay.ctx_after, Bp),
+                              hv(lay.state_slot, Bp))
+        # only the ranges that hold this step's data travel: the small arrays, and of every block table the
+        # rows of the step's entries
+        host_t = self._host_bufs[which][turn]
+        copied = 0
+        for c in range(info.n_copies):
+            off, n = info.copy_offset[c], info.copy_words[c]
+            dev[off:off + n].copy_(host_t[off:off + n], non_blocking=True)
+            copied += n
+        self.last_h2d_bytes = 4 * copied
         ev = torch.cuda.Event()
         ev.record()
-        self._host_events[turn] = ev
+        self._host_events[which][turn] = ev
+        self._row_slot_dev = step.row_slot
         return step
+
+    def _run_step(self, info) -> int:
+        """The runner that the host core calls once a step is laid out: the device work.  0 = done; anything
+        else makes the core give the step's pages back (the error itself is kept for ``step`` to raise)."""
+        try:
+            step = self._context(info)
+            if self._runner_fn is not None:
+                self._step_logits = self._runner_fn(step)
+            elif self._step_bucket:
+                self._step_logits = self._replay_decode(step, self._step_bucket, info.n_real_entries)
+            else:
+                self._step_logits = self._forward(step)
+            return 0
+        except BaseException as e:   # an exception must not cross the C frames between here and step()
+            self._runner_error = e
+            return 1
+
+    def _launch(self, entries: List[StepEntry], bucket: int):
+        """One call of the host core's ccinfer_forward for the entries given."""
+        opt = self.options
+        seqs, slots, counts, want_counts = [], [], [], []
+        for e in entries:
+            rc = self.cache.get(e.req_id)
+            seqs.append(rc.seq)
+            slots.append(rc.slot)
+            counts.append(len(e.tokens))
+            want_counts.append(len(e.want))
+            if len(e.tokens) == 1 and e.tokens[0] == PENDING and rc.slot not in self._pending_slots:
+                raise InvalidArgument(f"request {e.req_id!r}: PENDING stands for the token of a sample_async for the "
+                                      f"request, and there was none since its last step")
+        if len(entries) > opt.max_requests:
+            raise InvalidArgument(f"{len(entries)} entries in a step, at most {opt.max_requests}")
+        tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int32, count=sum(counts))
+        wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=sum(want_counts))
+        turn = self._host_turn
+        self._host_turn ^= 1
+        for which in (0, 1):
+            if self._host_events[which][turn] is not None:
+                self._host_events[which][turn].synchronize()   # its last copy has left the buffer
+        self._turn_in_use = turn
+        self._step_bucket = bucket
+        self._runner_error = None
+        self._step_logits = None
+        self._last_logits = self._last_row_slot = None
+        try:
+            self.cache.core.forward(seqs, counts, tokens, want_counts, wants, bucket,
+                                    self._host_bufs[0][turn].data_ptr(), self._host_bufs[1][turn].data_ptr())
+        except RunnerFailed:
+            raise self._runner_error from None
+        # a pending token serves one step: this one read it, or brought the request's token itself
+        self._pending_slots.difference_update(slots)
+        # which request slot each logits row belongs to (a graph's rows are one per entry, in the core's order:
+        # as a set of slots that is the same)
+        self._last_row_slot = (self._row_slot_dev, slots if bucket else [s for s, n in zip(slots, want_counts)
+                                                                         for _ in range(n)])
+        return self._step_logits
+
+    def try_step(self, entries: Sequence[StepEntry], fn):
+        """Lays a step out as ``step`` does (pages taken, arrays on the device), calls ``fn(step_context)`` in
+        place of the model's forward pass and then gives everything back: nothing is committed.  For tests of
+        single parts, which need a real step to run in."""
+        class _GiveBack(Exception):
+            pass
+        result = []
+
+        def run(step):
+            result.append(fn(step))
+            raise _GiveBack()
+
+        self._runner_fn = run
+        try:
+            self._launch([e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries], 0)
+        except _GiveBack:
+            pass
+        finally:
+            self._runner_fn = None
+        return result[0] if result else None
 
     def _forward(self, step: StepContext) -> Optional[torch.Tensor]:
         plan = self.plan
@@ -442,13 +430,12 @@ class Engine:
                 return 0
         return self._bucket_of(len(entries))
 
-    def _replay_decode(self, entries: List[StepEntry], bucket: int) -> torch.Tensor:
-        """A decode step of up to ``bucket`` requests: the step arrays are copied, the kernels replayed.
+    def _replay_decode(self, step: StepContext, bucket: int, n_real: int) -> torch.Tensor:
+        """A decode step of up to ``bucket`` requests: the step arrays have been copied, the kernels are replayed.
 
         The launch sequence of a decode step depends on the number of rows only, and every buffer it
-        touches has a fixed address, so it is captured once per size (rows beyond the live requests
-        are padding: they cache nothing and attend to nothing)."""
-        step = self._build(entries, pad_to=bucket)
+        touches has a fixed address (the small layout's device buffer, the scratch pool), so it is captured
+        once per size (rows beyond the live requests are padding: they cache nothing and attend to nothing)."""
         if bucket not in self._graphs:
             self._forward(step)  # once eagerly: every scratch buffer exists before the capture ...
             self.rt.scratch.freeze()  # ... and none may move once a graph holds its address
@@ -462,7 +449,7 @@ class Engine:
         kernels.counters.own += n_own      # a replay launches what the capture recorded
         kernels.counters.library += n_lib
         self.graph_replays += 1
-        return out[:len(entries)]
+        return out[:n_real]
 
     def warm_up(self, batch_sizes: Sequence[int] = ()) -> List[int]:
         """Captures the decode graphs of the given batch sizes (default: every power of two up to
@@ -514,24 +501,7 @@ class Engine:
         next step is launched (copy them to keep them longer).
         """
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        self._validate(entries)
-        reserved = []
-        try:
-            for e in entries:
-                self.cache.reserve(e.req_id, len(e.tokens))
-                reserved.append(e.req_id)
-            bucket = self._graph_bucket(entries)
-            if bucket:
-                logits = self._replay_decode(entries, bucket)
-            else:
-                step = self._build(entries)
-                logits = self._forward(step)
-        except BaseException:
-            for rid in reserved:
-                self.cache.rollback(rid)
-            raise
-        for e in entries:
-            self.cache.commit(e.req_id)
+        logits = self._launch(entries, self._graph_bucket(entries))
         self.steps_run += 1
         if logits is None:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.rt.device)

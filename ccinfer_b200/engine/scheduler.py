@@ -227,7 +227,7 @@ class Scheduler:
         rc = cache.get(rid)
         best = n
         for g, spec in enumerate(cache.groups):
-            room = (len(rc.tables[g]) + free[g]) * spec.page_size - rc.ctx_len
+            room = (rc.table_len(g) + free[g]) * spec.page_size - rc.ctx_len
             best = min(best, room)
         return max(0, best)
 

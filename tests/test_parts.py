@@ -71,54 +71,57 @@ def test_parts_alone(dtype):
     T = 45
     toks = list(range(3, 3 + T))
     eng.open_request("a")
-    eng.cache.reserve("a", T)
-    step = eng._build([StepEntry("a", toks, [0, T - 1])])
-    block = plan.layers[0]
-    g = torch.Generator().manual_seed(2)
-    x_ref = torch.randn(T, 48, generator=g).to(DT[dtype]).double()
-    x = x_ref.to("cuda", DT[dtype])
-    p = "model.layers.0."
-    wd = {k: v.double() for k, v in w.items()}
-    # embedding
-    stream = plan.embedding.forward(step)
-    assert torch.equal(stream.h.cpu().double(), plain.embed(wd["model.embed_tokens.weight"], toks))
-    # norm: plain apply, fold of a pending delta, fold on picked rows
-    assert _rel(block.norm1.apply(x), plain.rms_norm(x_ref, wd[p + "input_layernorm.weight"], 1e-5)) <= TOL[dtype]
-    h0 = stream.h.clone()
-    stream.pending = x
-    y = block.norm1.fold(stream)
-    assert stream.pending is None and _rel(stream.h, h0.cpu().double() + x_ref) <= 1e-6
-    assert _rel(y, plain.rms_norm(h0.cpu().double() + x_ref, wd[p + "input_layernorm.weight"], 1e-5)) <= TOL[dtype]
-    rows = plan.final_norm.fold(stream, rows=step.logit_rows, n_rows=2)
-    ref_rows = plain.rms_norm(stream.h.cpu().double(), wd["model.norm.weight"], 1e-5)[[0, T - 1]]
-    assert _rel(rows, ref_rows) <= TOL[dtype]
-    # head
-    assert _rel(plan.head.forward(rows), rows.cpu().double() @ wd["lm_head.weight"].T) <= TOL[dtype]
-    # position encoding by itself
-    xq = x.view(T, 3, 16).contiguous()
-    rot = block.mixer.position.apply(xq, step.positions)
-    assert _rel(rot, plain.apply_rope(x_ref.view(T, 3, 16), torch.arange(T), plain.rope_inv_freq(16, 1e4))) <= TOL[dtype]
-    # feed-forward
-    ff = block.ffn.forward(x, step)
-    assert _rel(ff, plain.swiglu(x_ref, wd[p + "mlp.gate_proj.weight"], wd[p + "mlp.up_proj.weight"],
-                                 wd[p + "mlp.down_proj.weight"])) <= TOL[dtype]
-    # mixer (windowed attention over the paged cache)
-    from ccinfer_b200.engine.step import LayerCache
-    cache = LayerCache(eng._cache[0], step.groups[0], True)
-    att = block.mixer.forward(x, step, cache, None)
-    ref_att = plain.attention_block(x_ref, wd, p + "self_attn.", cfg, torch.arange(T), window=20)
-    assert _rel(att, ref_att) <= TOL[dtype]
-    # the block: h += Attn(norm1(h)); pending = MLP(norm2(h))
-    s2 = Residual(h0.clone())
-    block.forward(s2, step, cache, None)
-    hh = h0.cpu().double()
-    hh = hh + plain.attention_block(plain.rms_norm(hh, wd[p + "input_layernorm.weight"], 1e-5), wd,
-                                    p + "self_attn.", cfg, torch.arange(T), window=20)
-    assert _rel(s2.h, hh) <= TOL[dtype]
-    mlp = plain.swiglu(plain.rms_norm(hh, wd[p + "post_attention_layernorm.weight"], 1e-5),
-                       wd[p + "mlp.gate_proj.weight"], wd[p + "mlp.up_proj.weight"], wd[p + "mlp.down_proj.weight"])
-    assert _rel(s2.pending, mlp) <= TOL[dtype] * 2
-    eng.cache.rollback("a")
+
+    def run(step):
+        block = plan.layers[0]
+        g = torch.Generator().manual_seed(2)
+        x_ref = torch.randn(T, 48, generator=g).to(DT[dtype]).double()
+        x = x_ref.to("cuda", DT[dtype])
+        p = "model.layers.0."
+        wd = {k: v.double() for k, v in w.items()}
+        # embedding
+        stream = plan.embedding.forward(step)
+        assert torch.equal(stream.h.cpu().double(), plain.embed(wd["model.embed_tokens.weight"], toks))
+        # norm: plain apply, fold of a pending delta, fold on picked rows
+        assert _rel(block.norm1.apply(x), plain.rms_norm(x_ref, wd[p + "input_layernorm.weight"], 1e-5)) <= TOL[dtype]
+        h0 = stream.h.clone()
+        stream.pending = x
+        y = block.norm1.fold(stream)
+        assert stream.pending is None and _rel(stream.h, h0.cpu().double() + x_ref) <= 1e-6
+        assert _rel(y, plain.rms_norm(h0.cpu().double() + x_ref, wd[p + "input_layernorm.weight"], 1e-5)) <= TOL[dtype]
+        rows = plan.final_norm.fold(stream, rows=step.logit_rows, n_rows=2)
+        ref_rows = plain.rms_norm(stream.h.cpu().double(), wd["model.norm.weight"], 1e-5)[[0, T - 1]]
+        assert _rel(rows, ref_rows) <= TOL[dtype]
+        # head
+        assert _rel(plan.head.forward(rows), rows.cpu().double() @ wd["lm_head.weight"].T) <= TOL[dtype]
+        # position encoding by itself
+        xq = x.view(T, 3, 16).contiguous()
+        rot = block.mixer.position.apply(xq, step.positions)
+        assert _rel(rot, plain.apply_rope(x_ref.view(T, 3, 16), torch.arange(T), plain.rope_inv_freq(16, 1e4))) <= TOL[dtype]
+        # feed-forward
+        ff = block.ffn.forward(x, step)
+        assert _rel(ff, plain.swiglu(x_ref, wd[p + "mlp.gate_proj.weight"], wd[p + "mlp.up_proj.weight"],
+                                     wd[p + "mlp.down_proj.weight"])) <= TOL[dtype]
+        # mixer (windowed attention over the paged cache)
+        from ccinfer_b200.engine.step import LayerCache
+        cache = LayerCache(eng._cache[0], step.groups[0], True)
+        att = block.mixer.forward(x, step, cache, None)
+        ref_att = plain.attention_block(x_ref, wd, p + "self_attn.", cfg, torch.arange(T), window=20)
+        assert _rel(att, ref_att) <= TOL[dtype]
+        # the block: h += Attn(norm1(h)); pending = MLP(norm2(h))
+        s2 = Residual(h0.clone())
+        block.forward(s2, step, cache, None)
+        hh = h0.cpu().double()
+        hh = hh + plain.attention_block(plain.rms_norm(hh, wd[p + "input_layernorm.weight"], 1e-5), wd,
+                                        p + "self_attn.", cfg, torch.arange(T), window=20)
+        assert _rel(s2.h, hh) <= TOL[dtype]
+        mlp = plain.swiglu(plain.rms_norm(hh, wd[p + "post_attention_layernorm.weight"], 1e-5),
+                           wd[p + "mlp.gate_proj.weight"], wd[p + "mlp.up_proj.weight"], wd[p + "mlp.down_proj.weight"])
+        assert _rel(s2.pending, mlp) <= TOL[dtype] * 2
+
+    # a real step is laid out for the parts to run in (pages taken, arrays on the device); nothing is committed
+    eng.try_step([StepEntry("a", toks, [0, T - 1])], run)
+    assert eng.context_len("a") == 0 and all(p.used_pages == 0 for p in eng.cache.pools)
     eng.check()
 
 
