@@ -18,8 +18,9 @@ class ScratchPool:
     size gets new storage, which is harmless until a CUDA graph has recorded the
     old address.  The engine therefore runs a step eagerly (every key reaches the
     largest size the model's parts ask for) and then calls ``freeze()`` before it
-    captures the first graph: from then on a request for more than a buffer holds
-    raises instead of moving it from under the graphs.
+    captures the first graph: from then on a request for more than an existing
+    buffer holds raises instead of moving it from under the graphs (a key asked
+    for the first time still gets its buffer: no graph can hold its address).
     """
 
     def __init__(self, device):
@@ -34,7 +35,7 @@ class ScratchPool:
         full_key = f"{key}:{dtype}"
         buf = self._bufs.get(full_key)
         if buf is None or buf.numel() < n:
-            if self.frozen:
+            if self.frozen and buf is not None:   # a new key is no harm: no graph holds an address of it
                 raise ScratchMoved(f"scratch buffer '{key}' ({dtype}) is asked for {n} elements after CUDA graphs "
                                    f"recorded the addresses of the pool (it holds "
                                    f"{0 if buf is None else buf.numel()}): a part must ask for its largest "
@@ -117,6 +118,12 @@ class Runtime:
                 and K >= kernels.FEWROWS_MIN_K and N % 128 == 0 and kernels.gemm_fewrows_fits(M, K, x, w)
                 and -(-N // 128) < self.sm_count):
             kernels.gemm_fewrows_bf16(act, x, w, swiglu=True, status=self.status)
+            return act
+        if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M >= kernels.PERSIST_SWIGLU_MIN_ROWS
+                and N % 128 == 0 and kernels.gemm_tc_fits(K, x, w)):
+            # many tokens: the persistent tcgen05 product with the activation as its epilogue (the library's
+            # product is faster by itself, but not once the activation's own pass over gate|up is added)
+            kernels.gemm_tc_persist_bf16(act, x, w, swiglu=True, status=self.status)
             return act
         gu = self.scratch.get("ffn_gate_up", (self.max_tokens, N), self.dtype)[:M]
         self.linear(gu, x, w)
