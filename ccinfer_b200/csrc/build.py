@@ -43,6 +43,7 @@ GROUPS = {
         "gemm_cublas.cu",
         "gemm_skinny.cu",
         "gemm_tcgen05.cu",
+        "gemm_tc_pair.cu",
         "gemm_fewrows.cu",
         "sampling.cu",
         "random_init.cu",

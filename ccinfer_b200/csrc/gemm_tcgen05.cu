@@ -306,183 +306,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Many rows (prefill): a persistent form of the normal orientation.  One block per SM walks over output
-// tiles of 128 rows x 256 features; the TMA producer and the MMA issuer run on from one tile into the next
-// (the ring of stages never drains, tensor maps and tensor memory are set up once), and the accumulator has
-// two buffers of 256 columns in tensor memory: while the four epilogue warps read one out, convert and store
-// it, the products of the next tile fill the other.  One tile per block paid about 3 us of start-up per 17 us
-// of products (nothing overlaps between successive blocks of an SM that one block fills).
-// Tiles are numbered with the row tiles fastest, so that the blocks running at one time share a few weight
-// tiles and all token tiles in L2.
-// SWIGLU: the weight rows come in blocks of 64 gate rows and the 64 up rows of the same channels; a thread
-// holds a row's 256 accumulator columns, so silu(gate) * up needs no exchange: the tile writes 128 outputs.
-// ---------------------------------------------------------------------------------------------
-constexpr int kPersistBN = 256;
-constexpr int kPersistStages = 4;
-
-template <bool SWIGLU, typename TOut>
-__global__ void __launch_bounds__(kThreadsTc, 1)
-gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                       TOut* __restrict__ C, int ldc, int rowsA, int rowsB, int K, int* status) {
-  constexpr int BN = kPersistBN, STAGES = kPersistStages;
-  constexpr int B_STAGE_BYTES = BN * BK * 2;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_STAGE_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  const uint32_t full0 = s32(bars), empty0 = s32(bars + STAGES), tfull0 = s32(bars + 2 * STAGES),
-                 tempty0 = s32(bars + 2 * STAGES + 2);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (rowsA + BM - 1) / BM, tiles_n = (rowsB + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n;
-  const int nkb = (K + BK - 1) / BK;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(tfull0 + 8 * b, 1);
-      mbar_init(tempty0 + 8 * b, 4);   // one arrival per epilogue warp
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)),
-                 "r"(512u)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {  // ---- TMA producer: one stream of k blocks over all of the block's tiles ----
-      pdl_wait();
-      pdl_trigger();
-      int it = 0;
-      bool alive = true;
-      for (int t = blockIdx.x; t < n_tiles && alive; t += gridDim.x) {
-        const int tm = t % tiles_m, tn = t / tiles_m;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % STAGES, ph = (it / STAGES) & 1;
-          if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) {
-            set_status(status, CCB_ST_WAIT_TIMEOUT);
-            alive = false;
-            break;
-          }
-          mbar_expect_tx(full0 + 8 * s, A_STAGE_BYTES + B_STAGE_BYTES);
-          tma_load_2d(s32(sA + s * A_STAGE_BYTES), &tmA, kb * BK, tm * BM, full0 + 8 * s);
-          tma_load_2d(s32(sB + s * B_STAGE_BYTES), &tmB, kb * BK, tn * BN, full0 + 8 * s);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {  // ---- MMA issuer ----
-      constexpr uint32_t idesc = instr_desc(BN);
-      int it = 0, local = 0;
-      bool alive = true;
-      for (int t = blockIdx.x; t < n_tiles && alive; t += gridDim.x, ++local) {
-        const int buf = local & 1;
-        // the epilogue has read this accumulator's last tile out (the first use of each passes at once)
-        if (!mbar_wait(tempty0 + 8 * buf, ((local >> 1) & 1) ^ 1)) {
-          set_status(status, CCB_ST_WAIT_TIMEOUT);
-          break;
-        }
-        tc_fence_after();
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % STAGES, ph = (it / STAGES) & 1;
-          if (!mbar_wait(full0 + 8 * s, ph)) {
-            set_status(status, CCB_ST_WAIT_TIMEOUT);
-            alive = false;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t da = smem_desc(s32(sA + s * A_STAGE_BYTES));
-          const uint64_t db = smem_desc(s32(sB + s * B_STAGE_BYTES));
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            tc_mma(tmem_base + buf * BN, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          tc_commit(empty0 + 8 * s);
-        }
-        if (alive) tc_commit(tfull0 + 8 * buf);
-      }
-    }
-  } else {  // ---- epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31 of the finished accumulator ----
-    const int q = warp & 3;
-    const int row = q * 32 + lane;
-    int local = 0;
-    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++local) {
-      const int tm = t % tiles_m, tn = t / tiles_m;
-      const int buf = local & 1;
-      if (!mbar_wait(tfull0 + 8 * buf, (local >> 1) & 1)) {
-        if (lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
-        break;
-      }
-      tc_fence_after();
-      const int ga = tm * BM + row;
-      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
-      if (!SWIGLU) {
-        TOut* crow = C + (size_t)ga * ldc + (size_t)tn * BN;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tc_ld32(taddr + c0, v);
-          tc_wait_ld();
-          if (ga < rowsA) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int n_valid = min(16, rowsB - (tn * BN + c0 + 16 * h));
-              if (n_valid > 0) store16<TOut>(crow + c0 + 16 * h, v + 16 * h, n_valid);
-            }
-          }
-        }
-      } else {
-        // columns: [64 gate | 64 up] twice; output channel = 128 tn + 64 half + c
-        TOut* crow = C + (size_t)ga * ldc + (size_t)tn * (BN / 2);
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-#pragma unroll 1
-          for (int c0 = 0; c0 < 64; c0 += 32) {
-            uint32_t g[32], u[32];
-            tc_ld32(taddr + half * 128 + c0, g);
-            tc_ld32(taddr + half * 128 + 64 + c0, u);
-            tc_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float gv = __uint_as_float(g[j]);
-              g[j] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[j]));
-            }
-            if (ga < rowsA) {
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int n_valid = min(16, rowsB / 2 - (tn * (BN / 2) + half * 64 + c0 + 16 * h));
-                if (n_valid > 0) store16<TOut>(crow + half * 64 + c0 + 16 * h, g + 16 * h, n_valid);
-              }
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);   // this warp's quarter of the accumulator is free again
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
@@ -582,43 +405,7 @@ int dispatch(void* C, const void* A, const void* W, int M, int N, int K, int lda
   return launch_tc<256, 4, false, TOut>(tmX, tmW, C, ldc, M, N, K, 1, nullptr, nullptr, status, stream);
 }
 
-template <bool SWIGLU, typename TOut>
-int launch_persist(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, int M, int N, int K, int sms,
-                   int* status, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)kPersistStages * (A_STAGE_BYTES + kPersistBN * BK * 2) + (2 * kPersistStages + 4) * 8 + 16 + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel<SWIGLU, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  const int tiles = ((M + BM - 1) / BM) * ((N + kPersistBN - 1) / kPersistBN);
-  ccb_launch(gemm_tc_persist_kernel<SWIGLU, TOut>, dim3(tiles < sms ? tiles : sms), kThreadsTc, smem, stream, tmA, tmB,
-             (TOut*)C, ldc, M, N, K, status);
-  return ccb_launch_status();
-}
-
 }  // namespace
-
-// C[M, N] = A[M, K] W[N, K]^T for many rows, as one persistent block per SM (see gemm_tc_persist_kernel).
-// swiglu: W [N = 2F, K] in blocks of 64 gate and 64 up rows (F a multiple of 64), C [M, F] = silu(gate) * up.
-CCB_API int ccb_gemm_tc_persist_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
-                                     int out_dtype, int swiglu, int sms, int* status, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (out_dtype != CCB_F32 && out_dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
-  if (K <= 0 || (K & 7) || lda < K || ldw < K || ldc < (swiglu ? N / 2 : N) || (lda & 7) || (ldw & 7) || sms <= 0 ||
-      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) || (swiglu && (N & 127)))
-    return CCB_REFUSE_SIZE;
-  CUtensorMap tmX, tmW;
-  if (!tensor_map(A, M, K, lda, BM, &tmX) || !tensor_map(W, N, K, ldw, kPersistBN, &tmW)) return CCB_REFUSE_ARG;
-  if (swiglu) {
-    if (out_dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
-    return launch_persist<true, __nv_bfloat16>(tmX, tmW, C, ldc, M, N, K, sms, status, stream);
-  }
-  if (out_dtype == CCB_F32) return launch_persist<false, float>(tmX, tmW, C, ldc, M, N, K, sms, status, stream);
-  return launch_persist<false, __nv_bfloat16>(tmX, tmW, C, ldc, M, N, K, sms, status, stream);
-}
 
 // splits > 1 only with M <= 64; then `partial` holds splits * M * N floats and `counters`
 // ceil(N / 128) ints that are zero before the first launch (the kernel leaves them zero).

@@ -119,11 +119,11 @@ class Runtime:
                 and -(-N // 128) < self.sm_count):
             kernels.gemm_fewrows_bf16(act, x, w, swiglu=True, status=self.status)
             return act
-        if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M >= kernels.PERSIST_SWIGLU_MIN_ROWS
+        if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M >= kernels.PAIR_SWIGLU_MIN_ROWS
                 and N % 128 == 0 and kernels.gemm_tc_fits(K, x, w)):
-            # many tokens: the persistent tcgen05 product with the activation as its epilogue (the library's
-            # product is faster by itself, but not once the activation's own pass over gate|up is added)
-            kernels.gemm_tc_persist_bf16(act, x, w, swiglu=True, status=self.status)
+            # many tokens: the tcgen05 product on pairs of SMs with the activation as its epilogue (level with the
+            # library's product by itself, ahead once the activation's own pass over gate|up is gone)
+            kernels.gemm_tc_pair_bf16(act, x, w, swiglu=True, status=self.status)
             return act
         gu = self.scratch.get("ffn_gate_up", (self.max_tokens, N), self.dtype)[:M]
         self.linear(gu, x, w)

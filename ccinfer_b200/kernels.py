@@ -79,8 +79,8 @@ _SIGNATURES = {
                              c_void_p],
     "ccb_gemm_tc_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_void_p, c_void_p],
-    "ccb_gemm_tc_persist_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_int, c_void_p, c_void_p],
+    "ccb_gemm_tc_pair_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p, c_void_p],
     "ccb_init_random": [c_void_p, c_longlong, c_int, ctypes.c_ulonglong, ctypes.c_ulonglong, c_float, c_int, c_void_p],
     "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_int, c_void_p, c_void_p, c_int, c_void_p],
@@ -551,22 +551,23 @@ def gemm_tc_bf16(c, a, w, splits: int = 1, partial=None, counters=None, status=N
                                   splits, _p(partial), _p(counters), _p(status), _stream()), "gemm_tc_bf16")
 
 
-PERSIST_SWIGLU_MIN_ROWS = 2048   # from here on gate|up with the activation fused beats the library product + silu_mul
-
-
-def gemm_tc_persist_bf16(c, a, w, swiglu: bool = False, status=None) -> None:
-    """c[M, N] (bfloat16 or float) = a[M, K] @ w[N, K]^T for many rows on tcgen05 tensor cores: one persistent
-    block per SM over tiles of 128 x 256, two accumulators in tensor memory so that a tile's epilogue runs under
-    the next tile's products.  With ``swiglu`` w [2F, K] is interleaved in blocks of SWIGLU_BLOCK rows
-    (interleave_gate_up) and c[M, F] = silu(a Wg^T) * (a Wu^T)."""
+def gemm_tc_pair_bf16(c, a, w, swiglu: bool = False, status=None) -> None:
+    """c[M, N] (bfloat16 or float) = a[M, K] @ w[N, K]^T for many rows on tcgen05 tensor cores, two SMs on every
+    256 x 256 tile (cta_group::2: each SM holds half of both operands, which halves what its shared memory has
+    to deliver per product), one cluster per pair of SMs walking over the tiles, two accumulators in tensor
+    memory so that a tile's epilogue runs under the next tile's products.  With ``swiglu`` w [2F, K] is
+    interleaved in blocks of SWIGLU_BLOCK rows (interleave_gate_up) and c[M, F] = silu(a Wg^T) * (a Wu^T)."""
     _cuda(w, status)
     assert a.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT and c.is_cuda and a.is_cuda
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and c.shape == (M, N // 2 if swiglu else N)
     assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
-    _check(lib().ccb_gemm_tc_persist_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _dt(c),
-                                          1 if swiglu else 0, sm_count(), _p(status), _stream()), "gemm_tc_persist_bf16")
+    _check(lib().ccb_gemm_tc_pair_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _dt(c),
+                                       1 if swiglu else 0, sm_count(), _p(status), _stream()), "gemm_tc_pair_bf16")
+
+
+PAIR_SWIGLU_MIN_ROWS = 1024   # from here on gate|up with the activation fused beats the library product + silu_mul
 
 
 FEWROWS_MAX_ROWS = 16

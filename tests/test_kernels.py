@@ -211,21 +211,21 @@ def test_gemm_tc_normal(out, M, N, K):
 
 @pytest.mark.parametrize("out", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 520, 192), (65, 96, 4096), (300, 301 * 8, 96), (1000, 2048, 1024),
-                                   (2048, 6144, 512), (129, 257 * 8, 8 * 33)])
-def test_gemm_tc_persistent(out, M, N, K):
-    """One block per SM over many tiles, two accumulators: every tile of every block, ragged edges included."""
+                                   (2048, 6144, 512), (129, 257 * 8, 8 * 33), (5000, 768, 128), (257, 24576, 64)])
+def test_gemm_tc_pair(out, M, N, K):
+    """Two SMs on every tile, one cluster per pair of SMs over many tiles, two accumulators: ragged edges included."""
     k = _k()
     a, a_ref = _rand((M, K), torch.bfloat16, 21)
     w, w_ref = _rand((N, K), torch.bfloat16, 22, scale=0.1)
     c = torch.full((M, N), 7.0, dtype=DT[out], device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    k.gemm_tc_persist_bf16(c, a, w, status=status)
+    k.gemm_tc_pair_bf16(c, a, w, status=status)
     assert int(status.item()) == 0
     assert _rel(c, a_ref @ w_ref.T) <= (2e-5 if out == "float32" else 6e-3)
 
 
 @pytest.mark.parametrize("M,F,K", [(128, 64, 64), (300, 192, 512), (2048, 1024, 256), (77, 64 * 37, 320)])
-def test_gemm_tc_persistent_swiglu(M, F, K):
+def test_gemm_tc_pair_swiglu(M, F, K):
     k = _k()
     a, a_ref = _rand((M, K), torch.bfloat16, 23)
     gate, g_ref = _rand((F, K), torch.bfloat16, 24, scale=0.1)
@@ -233,7 +233,7 @@ def test_gemm_tc_persistent_swiglu(M, F, K):
     w = k.interleave_gate_up(gate, up, k.SWIGLU_BLOCK)
     act = torch.full((M, F), 7.0, dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    k.gemm_tc_persist_bf16(act, a, w, swiglu=True, status=status)
+    k.gemm_tc_pair_bf16(act, a, w, swiglu=True, status=status)
     assert int(status.item()) == 0
     g, u = a_ref @ g_ref.T, a_ref @ u_ref.T
     assert _rel(act, g / (1 + torch.exp(-g)) * u) <= 8e-3
