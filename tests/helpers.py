@@ -9,14 +9,21 @@ import plain_qwen3 as plain
 import tiny_configs
 
 
-def make_model_dir(path, name, store="bfloat16"):
+def make_model_dir(path, name, store="bfloat16", sharpen=None):
     """Writes a tiny random model with the tests' own writer (safetensors library, plain weights).
 
     Values are rounded to bfloat16 once so that the 32-bit and the bfloat16 run
-    see the same weights; ``store`` chooses how the file holds them."""
+    see the same weights; ``store`` chooses how the file holds them.  ``sharpen``: the query norms' weights
+    are multiplied by it, so that scores are that much larger and a query's attention sits on a few keys
+    anywhere in its context: a key that the engine dropped or misplaced then changes the logits visibly, which
+    the flat attention of small random weights would hide."""
     from safetensors.torch import save_file
     cfg, seed, std, page = tiny_configs.get(name)
     w = plain.random_weights(cfg, seed, std)
+    if sharpen:
+        for k in w:
+            if k.endswith("self_attn.q_norm.weight"):
+                w[k] = w[k] * sharpen
     w = {k: v.to(torch.bfloat16) for k, v in w.items()}
     if store == "float32":
         stored = {k: v.to(torch.float32) for k, v in w.items()}

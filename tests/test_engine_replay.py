@@ -131,3 +131,36 @@ def test_cuts_agree_in_float32(models, name):
     b = helpers.replay(_engine(d, "float32", page, 1024), helpers.trace_mixed(reqs, seed=3))
     worst = max(float(np.abs(a[k] - b[k]).max()) / max(1e-6, float(np.abs(ref[k[0]]).max())) for k in a)
     assert worst <= 1e-5, worst
+
+
+SHARPEN = 8.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_sharp_attention_shows_every_key(tmp_path_factory, name, dtype):
+    """Scores eight times larger: a query's attention sits on one or two keys somewhere in its context (with
+    scores of deviation 8 the best of 400 keys outweighs all others together), so a key that was dropped,
+    misplaced or read from a stale page moves the logits by about their own size, where the flat attention
+    of small random weights gives one key in hundreds less than the bfloat16 tolerance.  Long requests, mixed
+    steps with pages used again, long portions and graphs, all against the plain implementation.
+
+    The bounds are those of the ordinary replay tests times the same factor: an error of a query or a key
+    reaches the score multiplied by it, and the score is the exponent of a weight."""
+    d = str(tmp_path_factory.mktemp(f"sharp{name}"))
+    cfg, weights, page = helpers.make_model_dir(d, name, sharpen=SHARPEN)
+    reqs = _requests(cfg, [3, 257, 410, 129, 600, 64], seed=9)
+    ref = {rid: helpers.plain_logits(cfg, weights, toks) for rid, toks in reqs.items()}
+    tol = SHARPEN * _tol(name, dtype)
+    for mode, steps, graphs in (
+            ("whole", helpers.trace_whole(reqs), False),
+            ("mixed", helpers.trace_mixed(reqs, max_live=4, seed=21), False),
+            ("long portions", helpers.trace_mixed(reqs, max_live=3, seed=22, prefill_frac=0.8,
+                                                  portion_choices=(70, 130, 65, 2, 200)), True),
+            ("decode32", helpers.trace_prefill_then_decode(reqs, tail=32), True)):
+        pool = helpers.max_live_tokens(steps, round_to=max(64, page))
+        eng = _engine(d, dtype, page, pool, use_graphs=graphs)
+        rows = helpers.replay(eng, steps)
+        worst = helpers.compare(rows, ref, tol, f"sharp {name} {dtype} {mode}")
+        print(f"[worst] sharp {name}, {dtype}, {mode}: {worst:.3e}")
+        eng.cache.check_consistency()
