@@ -179,7 +179,8 @@ def run_workload(args) -> int:
     produced, calls, decode_calls = 0, [], []
     t_start = time.perf_counter()
     while sched.has_work():
-        decode_only = all(r.prefill_done for r in sched.active.values()) and not sched.waiting
+        c = sched.counts()
+        decode_only = c["prefilling"] == 0 and c["waiting"] == 0
         t = time.perf_counter()
         events = sched.step()
         ms = (time.perf_counter() - t) * 1e3
@@ -424,7 +425,7 @@ def main() -> int:
         sched = Scheduler(engine, prefill_chunk_size=0, max_tokens_per_step=opt.max_tokens_per_step, max_running=B,
                           run_ahead=True)
         fill(B, ctx, sched, steps=W + E2E_STEPS)
-        while any(not r.prefill_done for r in sched.active.values()) or sched.waiting:
+        while sched.counts()["prefilling"] or sched.counts()["waiting"]:
             sched.step()
         for _ in range(W):
             sched.step()
@@ -435,7 +436,7 @@ def main() -> int:
             produced += sum(1 for ev in sched.step() if ev.token is not None)
         torch.cuda.synchronize()
         wall = time.perf_counter() - t
-        for rid in list(sched.active):
+        for rid in sched.active_ids():
             sched.cancel(rid)
         return produced / wall, produced
 

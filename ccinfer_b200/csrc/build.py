@@ -50,6 +50,7 @@ GROUPS = {
     ],
     "host": [
         "host/host_core.cpp",
+        "host/scheduler.cpp",
     ],
 }
 GROUP_LIBS = {"core": ["-lcublas"]}

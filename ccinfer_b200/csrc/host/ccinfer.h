@@ -8,8 +8,10 @@
  * The model itself (layers put together from parts, kernel launches) is not in this library: a step's device
  * work is done by a runner that the owner of the engine registers (the Python package registers its model's
  * forward pass).  ccinfer_forward() = validate -> take pages -> fill the step arrays -> runner -> commit, or
- * give the pages back if anything failed.  Requests, sampling and the scheduler's loop are the Python entry
- * point's (ccinfer_b200.LLM) on top of these calls.
+ * give the pages back if anything failed.  Above it, a scheduler (ccinfer_scheduler_create, ccinfer_add_request,
+ * ccinfer_cancel, ccinfer_step): which requests run in the next step, which portions of their prompts, who
+ * gives way when pages run out, when a request ends.  It runs a step and reads its sampled tokens through hooks
+ * that the owner registers (the Python package's hooks call its step function and its sampling kernels).
  *
  * Not thread-safe: one thread drives an engine.
  */
@@ -96,6 +98,8 @@ CCINFER_API void ccinfer_destroy(ccinfer_engine* e);
 CCINFER_API const char* ccinfer_last_error(const ccinfer_engine* e);
 CCINFER_API int ccinfer_get_layout(const ccinfer_engine* e, int which, ccinfer_layout* out);
 CCINFER_API int ccinfer_stats(const ccinfer_engine* e, ccinfer_stats_t* out);
+/* the groups the engine was created with: copies min(capacity, n) of them and returns n */
+CCINFER_API int ccinfer_get_groups(const ccinfer_engine* e, ccinfer_group* out, int capacity, int* n);
 /* every page is free or in exactly one table of its owner, no page is lost; CCINFER_INVALID_STATE otherwise */
 CCINFER_API int ccinfer_check(const ccinfer_engine* e);
 
@@ -130,6 +134,91 @@ CCINFER_API int ccinfer_set_runner(ccinfer_engine* e, ccinfer_runner run, void* 
 CCINFER_API int ccinfer_forward(ccinfer_engine* e, int n_entries, const int64_t* seqs, const int* counts,
                                 const int* tokens, const int* want_counts, const int* wants, int pad_to,
                                 int32_t* small_buffer, int32_t* large_buffer, ccinfer_step_info* info_out);
+
+/* ------------------------------------------------------------------------------------------------------
+ * the scheduler: continuous batching above ccinfer_forward (or above any step function, through the hooks)
+ * ------------------------------------------------------------------------------------------------------ */
+typedef struct ccinfer_scheduler ccinfer_scheduler;
+
+/* names, meanings and defaults of 7QiC/ccInfer's SamplingParams (src/base/types.h:54-60) */
+typedef struct ccinfer_sampling_params {
+  int max_tokens;      /* generation limit */
+  int top_k;           /* 0 = off */
+  float top_p;         /* >= 1 = off */
+  float temperature;   /* <= 0 = greedy */
+  uint64_t seed;
+} ccinfer_sampling_params;
+
+typedef struct ccinfer_scheduler_options {
+  int prefill_chunk_size;    /* most prompt tokens of one request in a step; 0 = whole prompts */
+  int max_tokens_per_step;   /* the token budget of a step */
+  int max_running;           /* requests whose prompts have started */
+  int max_context;           /* a request ends when its next token would not fit */
+  int eos_token_id;          /* < 0 = off */
+  int run_ahead;             /* 1: a step is launched before the tokens of the step before it have been read */
+} ccinfer_scheduler_options;
+
+/* one step as the scheduler decided it: items in the order they run */
+typedef struct ccinfer_plan {
+  int n_items;
+  const int64_t* reqs;       /* [n_items] */
+  const int* counts;         /* [n_items] tokens of each item */
+  const int* tokens;         /* all items' tokens; -1 in a one-token item = the token last sampled for the request,
+                                which may still be on the device */
+  const int* sample;         /* [n_items] 1: a token is drawn from the item's last position */
+  const int* out_index;      /* [n_items] tokens the request has produced so far (keys the draw) */
+  const ccinfer_sampling_params* params; /* [n_items] */
+  int n_sampled;             /* items with sample = 1 */
+} ccinfer_plan;
+
+typedef struct ccinfer_scheduler_hooks {
+  /* a request enters the engine (again, after it gave way); *seq = the sequence that holds its cache.
+   * NULL: ccinfer_alloc_seq(engine, req), seq = req. */
+  int (*open)(void* user, int64_t req, int64_t* seq);
+  /* the request leaves: everything it holds is given back.  NULL: ccinfer_free_seq. */
+  int (*close)(void* user, int64_t req);
+  /* run the step (cache pages, forward pass) and launch the sampling of its n_sampled rows; their tokens are
+   * asked for later by ticket.  Required. */
+  int (*run)(void* user, const ccinfer_plan* plan, int64_t ticket);
+  /* the tokens of an earlier run, in the order of its sampled items; waits for them.  Required. */
+  int (*read)(void* user, int64_t ticket, int n, int* tokens_out);
+  void* user;
+} ccinfer_scheduler_hooks;
+
+enum { CCINFER_REASON_NONE = 0, CCINFER_REASON_MAX_TOKENS = 1, CCINFER_REASON_MAX_CONTEXT = 2, CCINFER_REASON_EOS = 3 };
+
+typedef struct ccinfer_event {
+  int64_t req;
+  int token;       /* -1: none (a request that ended without a new token) */
+  int finished;
+  int reason;      /* CCINFER_REASON_* when finished */
+} ccinfer_event;
+
+typedef struct ccinfer_scheduler_stats_t {
+  long long steps, preemptions;
+  int waiting, active, prefilling;   /* prefilling: active requests whose prompt is not yet all in the cache */
+  int in_flight;                     /* 1: a step's tokens have not been read yet */
+  int events;                        /* events not yet popped */
+} ccinfer_scheduler_stats_t;
+
+CCINFER_API int ccinfer_scheduler_create(ccinfer_engine* e, const ccinfer_scheduler_options* options,
+                                         const ccinfer_scheduler_hooks* hooks, ccinfer_scheduler** out);
+CCINFER_API void ccinfer_scheduler_destroy(ccinfer_scheduler* s);
+CCINFER_API const char* ccinfer_scheduler_last_error(const ccinfer_scheduler* s);
+CCINFER_API int ccinfer_scheduler_stats(const ccinfer_scheduler* s, ccinfer_scheduler_stats_t* out);
+/* ids of the active requests in their running order: copies min(capacity, n) and returns n */
+CCINFER_API int ccinfer_scheduler_active(const ccinfer_scheduler* s, int64_t* out, int capacity, int* n);
+/* queues a request (first come first served) */
+CCINFER_API int ccinfer_add_request(ccinfer_scheduler* s, int64_t req, const int* prompt, int n_prompt,
+                                    const ccinfer_sampling_params* params);
+/* ends a request wherever it is; *found = 0 if it is not known (or ended while its last token was read) */
+CCINFER_API int ccinfer_cancel(ccinfer_scheduler* s, int64_t req, int* found);
+CCINFER_API int ccinfer_has_work(const ccinfer_scheduler* s, int* yes);
+/* admits, decides and runs one step; what it produced waits in the event queue */
+CCINFER_API int ccinfer_step(ccinfer_scheduler* s);
+/* reads the step in flight, if any */
+CCINFER_API int ccinfer_drain(ccinfer_scheduler* s);
+CCINFER_API int ccinfer_pop_events(ccinfer_scheduler* s, ccinfer_event* out, int capacity, int* n);
 
 #ifdef __cplusplus
 }

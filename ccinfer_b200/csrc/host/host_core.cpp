@@ -341,6 +341,18 @@ int ccinfer_stats(const ccinfer_engine* e, ccinfer_stats_t* out) {
   });
 }
 
+int ccinfer_get_groups(const ccinfer_engine* e, ccinfer_group* out, int capacity, int* n) {
+  return guarded(e, [&] {
+    need(e, "engine");
+    need(n, "n");
+    *n = (int)e->groups.size();
+    for (int g = 0; g < std::min(capacity, *n); ++g) {
+      need(out, "out");
+      out[g] = e->groups[g];
+    }
+  });
+}
+
 int ccinfer_check(const ccinfer_engine* e) {
   return guarded(e, [&] {
     need(e, "engine");

@@ -1,4 +1,5 @@
-"""ctypes face of the C++ host core (``csrc/host/ccinfer.h``): cache manager, request slots, the arrays of a step.
+"""ctypes face of the C++ host core (``csrc/host/ccinfer.h``): cache manager, request slots, the arrays of a step,
+and the scheduler above them.
 
 Every C call returns an error code; here a non-zero code becomes the package's exception of the same name,
 with the message of ``ccinfer_last_error``.  The library is built at the first use (``csrc/build.py``, group
@@ -8,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from ctypes import POINTER, Structure, byref, c_int, c_int32, c_int64, c_longlong, c_void_p
+from ctypes import POINTER, Structure, byref, c_float, c_int, c_int64, c_longlong, c_uint64, c_void_p
 
 from .csrc import build as _build
 from .errors import (CcinferError, ExtensionMissing, InvalidArgument, KVBlockDoubleFree, KVBlockExhausted,
@@ -62,6 +63,44 @@ class Stats(Structure):
 
 RUNNER = ctypes.CFUNCTYPE(c_int, c_void_p, POINTER(StepInfo))
 
+
+class SamplingParamsC(Structure):
+    _fields_ = [("max_tokens", c_int), ("top_k", c_int), ("top_p", c_float), ("temperature", c_float),
+                ("seed", c_uint64)]
+
+
+class SchedulerOptions(Structure):
+    _fields_ = [("prefill_chunk_size", c_int), ("max_tokens_per_step", c_int), ("max_running", c_int),
+                ("max_context", c_int), ("eos_token_id", c_int), ("run_ahead", c_int)]
+
+
+class Plan(Structure):
+    _fields_ = [("n_items", c_int), ("reqs", POINTER(c_int64)), ("counts", POINTER(c_int)), ("tokens", POINTER(c_int)),
+                ("sample", POINTER(c_int)), ("out_index", POINTER(c_int)), ("params", POINTER(SamplingParamsC)),
+                ("n_sampled", c_int)]
+
+
+OPEN_HOOK = ctypes.CFUNCTYPE(c_int, c_void_p, c_int64, POINTER(c_int64))
+CLOSE_HOOK = ctypes.CFUNCTYPE(c_int, c_void_p, c_int64)
+RUN_HOOK = ctypes.CFUNCTYPE(c_int, c_void_p, POINTER(Plan), c_int64)
+READ_HOOK = ctypes.CFUNCTYPE(c_int, c_void_p, c_int64, c_int, POINTER(c_int))
+
+
+class SchedulerHooks(Structure):
+    _fields_ = [("open", OPEN_HOOK), ("close", CLOSE_HOOK), ("run", RUN_HOOK), ("read", READ_HOOK), ("user", c_void_p)]
+
+
+class Event(Structure):
+    _fields_ = [("req", c_int64), ("token", c_int), ("finished", c_int), ("reason", c_int)]
+
+
+class SchedulerStats(Structure):
+    _fields_ = [("steps", c_longlong), ("preemptions", c_longlong), ("waiting", c_int), ("active", c_int),
+                ("prefilling", c_int), ("in_flight", c_int), ("events", c_int)]
+
+
+REASONS = {0: None, 1: "max_tokens", 2: "max_context", 3: "eos"}
+
 _lock = threading.Lock()
 _lib = None
 
@@ -82,6 +121,7 @@ def lib():
             "ccinfer_create": [POINTER(Options), POINTER(E)],
             "ccinfer_get_layout": [E, c_int, POINTER(Layout)],
             "ccinfer_stats": [E, POINTER(Stats)],
+            "ccinfer_get_groups": [E, POINTER(Group), c_int, POINTER(c_int)],
             "ccinfer_check": [E],
             "ccinfer_alloc_seq": [E, c_int64, POINTER(c_int)],
             "ccinfer_free_seq": [E, c_int64],
@@ -100,10 +140,26 @@ def lib():
             "ccinfer_forward": [E, c_int, POINTER(c_int64), POINTER(c_int), POINTER(c_int), POINTER(c_int),
                                 POINTER(c_int), c_int, c_void_p, c_void_p, POINTER(StepInfo)],
         }
+        S = c_void_p
+        sig.update({
+            "ccinfer_scheduler_create": [E, POINTER(SchedulerOptions), POINTER(SchedulerHooks), POINTER(S)],
+            "ccinfer_scheduler_stats": [S, POINTER(SchedulerStats)],
+            "ccinfer_scheduler_active": [S, POINTER(c_int64), c_int, POINTER(c_int)],
+            "ccinfer_add_request": [S, c_int64, POINTER(c_int), c_int, POINTER(SamplingParamsC)],
+            "ccinfer_cancel": [S, c_int64, POINTER(c_int)],
+            "ccinfer_has_work": [S, POINTER(c_int)],
+            "ccinfer_step": [S],
+            "ccinfer_drain": [S],
+            "ccinfer_pop_events": [S, POINTER(Event), c_int, POINTER(c_int)],
+        })
         for name, argtypes in sig.items():
             fn = getattr(h, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        h.ccinfer_scheduler_destroy.argtypes = [S]
+        h.ccinfer_scheduler_destroy.restype = None
+        h.ccinfer_scheduler_last_error.argtypes = [S]
+        h.ccinfer_scheduler_last_error.restype = ctypes.c_char_p
         h.ccinfer_destroy.argtypes = [E]
         h.ccinfer_destroy.restype = None
         h.ccinfer_last_error.argtypes = [E]
@@ -241,3 +297,115 @@ class HostCore:
             byref(info))
         self._ok(rc)
         return info
+
+
+_CODES = {cls: code for code, cls in ERRORS.items()}
+
+
+class SchedulerCore:
+    """One scheduler of the host core above a ``HostCore``.
+
+    The four hooks are Python callables: ``open(req) -> seq``, ``close(req)``, ``run(plan, ticket)`` with
+    ``plan`` a ``Plan`` structure, ``read(ticket, n) -> n tokens``.  An exception inside a hook ends the C call
+    with the error code of its class; the call here then raises that same exception again."""
+
+    def __init__(self, core: HostCore, prefill_chunk_size: int, max_tokens_per_step: int, max_running: int,
+                 max_context: int, eos_token_id, run_ahead: bool, run, read, open=None, close=None):
+        self._lib = lib()
+        self._core = core   # the engine must outlive its scheduler
+        self._error = None
+
+        def guard(fn):
+            def wrapped(*a):
+                try:
+                    fn(*a)
+                    return 0
+                except BaseException as e:   # nothing may pass through the C frames
+                    self._error = e
+                    return next((code for cls, code in _CODES.items() if isinstance(e, cls)), 8)
+            return wrapped
+
+        def _open(user, req, seq_out):
+            seq_out[0] = open(req)
+
+        def _read(user, ticket, n, out):
+            tokens = read(ticket, n)
+            for i in range(n):
+                out[i] = int(tokens[i])
+
+        # without open/close hooks the scheduler calls ccinfer_alloc_seq / ccinfer_free_seq itself (sequence = request)
+        self._hooks = SchedulerHooks(OPEN_HOOK(guard(_open)) if open is not None else OPEN_HOOK(),
+                                     CLOSE_HOOK(guard(lambda user, req: close(req))) if close is not None else CLOSE_HOOK(),
+                                     RUN_HOOK(guard(lambda user, plan, ticket: run(plan.contents, ticket))),
+                                     READ_HOOK(guard(_read)), None)
+        opt = SchedulerOptions(int(prefill_chunk_size), int(max_tokens_per_step), int(max_running), int(max_context),
+                               -1 if eos_token_id is None else int(eos_token_id), int(bool(run_ahead)))
+        self._h = c_void_p()
+        rc = self._lib.ccinfer_scheduler_create(core._h, byref(opt), byref(self._hooks), byref(self._h))
+        if rc:
+            raise ERRORS.get(rc, CcinferError)((self._lib.ccinfer_scheduler_last_error(None) or b"").decode())
+        self._events = (Event * 256)()
+
+    def close(self):
+        if self._h:
+            self._lib.ccinfer_scheduler_destroy(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ok(self, rc: int) -> None:
+        error, self._error = self._error, None
+        if rc:
+            if error is not None:
+                raise error
+            raise ERRORS.get(rc, CcinferError)((self._lib.ccinfer_scheduler_last_error(self._h) or b"").decode())
+
+    def add_request(self, req: int, prompt, max_tokens: int, top_k: int, top_p: float, temperature: float,
+                    seed: int) -> None:
+        n = len(prompt)
+        arr = (c_int * max(1, n))(*prompt)
+        sp = SamplingParamsC(max(-1, min(int(max_tokens), 2**31 - 1)), int(top_k), float(top_p), float(temperature),
+                             int(seed) & (2**64 - 1))
+        self._ok(self._lib.ccinfer_add_request(self._h, req, arr, n, byref(sp)))
+
+    def cancel(self, req: int) -> bool:
+        found = c_int()
+        self._ok(self._lib.ccinfer_cancel(self._h, req, byref(found)))
+        return bool(found.value)
+
+    def has_work(self) -> bool:
+        yes = c_int()
+        self._ok(self._lib.ccinfer_has_work(self._h, byref(yes)))
+        return bool(yes.value)
+
+    def step(self) -> None:
+        self._ok(self._lib.ccinfer_step(self._h))
+
+    def drain(self) -> None:
+        self._ok(self._lib.ccinfer_drain(self._h))
+
+    def pop_events(self):
+        """[(req, token or None, finished, reason or None)] of everything queued."""
+        out, n = [], c_int()
+        while True:
+            self._ok(self._lib.ccinfer_pop_events(self._h, self._events, len(self._events), byref(n)))
+            for ev in self._events[:n.value]:
+                out.append((ev.req, None if ev.token < 0 else ev.token, bool(ev.finished), REASONS.get(ev.reason)))
+            if n.value < len(self._events):
+                return out
+
+    def stats(self) -> SchedulerStats:
+        st = SchedulerStats()
+        self._ok(self._lib.ccinfer_scheduler_stats(self._h, byref(st)))
+        return st
+
+    def active(self):
+        n = c_int()
+        self._ok(self._lib.ccinfer_scheduler_active(self._h, None, 0, byref(n)))
+        out = (c_int64 * max(1, n.value))()
+        self._ok(self._lib.ccinfer_scheduler_active(self._h, out, n.value, byref(n)))
+        return list(out[:n.value])

@@ -158,3 +158,64 @@ def test_window_group_gives_pages_back_at_commit_and_rows_are_cleared():
     with pytest.raises(SlotExhausted):
         core.alloc_seq(3), core.alloc_seq(4)
     core.check()
+
+
+def test_scheduler_through_the_c_calls_alone():
+    """ccinfer_add_request / ccinfer_step / ccinfer_cancel with no Python scheduler above them: the scheduler
+    opens and closes sequences itself (no open/close hooks), the run hook takes the pages of each item through
+    ccinfer_reserve/commit, the read hook answers with tokens that depend on the ticket alone."""
+    core = _core(pages=12, page=4, seqs=3, tokens=16, context=40)
+    ran, tickets = [], {}
+
+    def run(plan, ticket):
+        items, at = [], 0
+        for i in range(plan.n_items):
+            n = plan.counts[i]
+            items.append((plan.reqs[i], plan.tokens[at:at + n], plan.sample[i], plan.out_index[i]))
+            at += n
+        for req, toks, _, _ in items:
+            core.reserve(req, len(toks))
+            core.commit(req)
+        ran.append(items)
+        tickets[ticket] = [100 * ticket + k for k in range(plan.n_sampled)]
+        assert plan.params[0].max_tokens in (3, 5) and abs(plan.params[0].top_p - 0.9) < 1e-6
+
+    sched = native.SchedulerCore(core, prefill_chunk_size=6, max_tokens_per_step=16, max_running=3, max_context=40,
+                                 eos_token_id=None, run_ahead=False, run=run, read=lambda ticket, n: tickets.pop(ticket))
+    sched.add_request(7, list(range(10)), max_tokens=3, top_k=0, top_p=0.9, temperature=0.0, seed=1)
+    sched.add_request(8, list(range(4)), max_tokens=5, top_k=0, top_p=0.9, temperature=0.7, seed=2**63 + 5)
+    with pytest.raises(InvalidArgument, match="already known"):
+        sched.add_request(7, [1], 1, 0, 1.0, 0.0, 0)
+    with pytest.raises(RequestTooLong):
+        sched.add_request(9, list(range(41)), 1, 0, 1.0, 0.0, 0)
+    with pytest.raises(InvalidArgument, match="top_k"):
+        sched.add_request(9, [1], 1, -1, 1.0, 0.0, 0)
+    sched.step()
+    assert ran[-1] == [(7, list(range(6)), 0, 0), (8, list(range(4)), 1, 0)]   # a portion beside a whole prompt
+    assert sched.pop_events() == [(8, 100, False, None)]
+    assert core.seq_state(7)[1] == 6 and core.seq_state(8)[1] == 4 and sched.active() == [7, 8]
+    sched.step()
+    assert ran[-1] == [(8, [100], 1, 1), (7, [6, 7, 8, 9], 1, 0)]                # decoding first, then the rest
+    assert sched.pop_events() == [(8, 200, False, None), (7, 201, False, None)]
+    st = sched.stats()
+    assert (st.steps, st.waiting, st.active, st.prefilling, st.in_flight) == (2, 0, 2, 0, 0)
+    assert sched.cancel(8) and not sched.cancel(8) and core.stats().seqs == 1
+    events = []
+    while sched.has_work():
+        sched.step()
+        events += sched.pop_events()
+    assert [e[1] for e in events] == [300, 400] and events[-1][2:] == (True, "max_tokens")
+    assert core.stats().seqs == 0 and core.stats().pages_free[0] == 12
+    core.check()
+    # a hook that fails ends the call with its error, and nothing has moved
+    sched.add_request(10, [1, 2, 3], 2, 0, 1.0, 0.0, 0)
+
+    def broken(plan, ticket):
+        raise KVBlockExhausted("no pages today")
+    sched2 = native.SchedulerCore(core, 0, 16, 3, 40, None, False, run=broken, read=lambda t, n: [])
+    sched2.add_request(11, [1, 2, 3], 2, 0, 1.0, 0.0, 0)
+    with pytest.raises(KVBlockExhausted, match="no pages today"):
+        sched2.step()
+    assert sched2.stats().steps == 0 and core.seq_state(11)[1] == 0
+    assert sched2.cancel(11) and sched.cancel(10)
+    core.check()
