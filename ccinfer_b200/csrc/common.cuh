@@ -79,6 +79,26 @@ __device__ __forceinline__ void pdl_begin() {
   pdl_trigger();
 }
 
+// Sum of a row of `n` partial sums by one warp, every lane with the result; the order of the additions is
+// fixed (by lane, then a shuffle tree).  The loads are asked for together, not one after the other's use.
+__device__ __forceinline__ float row_ssq(const float* row, int n, int lane) {
+  float ss = 0.f;
+  if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+    for (int p = lane; p < (n >> 2); p += 32) {
+      const float4 v = __ldcg(row4 + p);
+      ss += (v.x + v.y) + (v.z + v.w);
+    }
+  } else {
+#pragma unroll 4
+    for (int p = lane; p < n; p += 32) ss += __ldcg(row + p);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  return ss;
+}
+
 __device__ __forceinline__ void set_status(int* status, int bit) {
   if (status != nullptr) atomicOr(status, bit);
 }

@@ -22,8 +22,16 @@
 //     of 64 gate rows followed by the 64 up rows of the same channels: a block then takes 8 gate rows and
 //     the 8 up rows of the same channels, which the fragment layout puts into the SAME thread (rows gid and
 //     gid + 8), so the activation costs no exchange at all.
-// (7QiC/ccInfer runs these products in cuBLAS, src/backend/cuda/cuda_backend.cpp:82-108, and the activation
-// as a kernel of its own, src/kernel/mlp/silu_mul.cu:24-28.)
+//   * Two more epilogues take the RMSNorm between two products apart, so that it needs no kernel of its own
+//     (y = x * rsqrt(mean(x^2) + eps) * w is linear in x but for one factor per token, and a product commutes
+//     with that factor).  "Into the residual stream": h[t, n] += C[t, n] in float, the block writes
+//     bf16(h * w_norm) in place of C and the sum of h^2 over its 16 features to ssq_out[t][block].  "Row
+//     scale": a product whose tokens are such rows multiplies token t of its result by
+//     1 / sqrt(sum over blocks of ssq_in[t][block] / dim + eps) before anything else (before the activation).
+//     The partial sums are added in the order of the blocks: nothing depends on which block ran first.
+// (7QiC/ccInfer runs these products in cuBLAS, src/backend/cuda/cuda_backend.cpp:82-108, the activation
+// as a kernel of its own, src/kernel/mlp/silu_mul.cu:24-28, and the sum and the norm as two more,
+// src/kernel/norm/rms_norm.cu:24-60.)
 //
 // Every wait on an mbarrier is bounded: after kWaitLimit failed polls the thread records
 // CCB_ST_WAIT_TIMEOUT in the status word and stops waiting; the block still reaches its barriers and returns.
@@ -52,12 +60,28 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 
 __device__ __forceinline__ float silu_fr(float g) { return g / (1.f + __expf(-g)); }
 
+}  // namespace
+
+// the two halves of a norm that has no kernel of its own (see the head of this file); all null / 0 = off
+struct CcbNormFuse {
+  const float* ssq_in;   // [16][parts_in]: partial sums of squares of the token rows of A
+  int parts_in;
+  float dim, eps;        // of the norm whose factor is applied
+  float* h;              // residual stream [M, ldh], float
+  int ldh;
+  const float* norm_w;   // [N]: weight of the norm that follows
+  float* ssq_out;        // [16][blocks]
+};
+
+namespace {
+
 // NB: 8-token tiles (M <= 8 NB).  tmW: box FR_KC x 16 rows (plain) or FR_KC x 8 rows (swiglu); tmX: box
 // FR_KC x 8 NB rows.  Both without a swizzle: a box lies in shared memory as rows of 512 bytes.
 template <int NB, int STAGES, typename TOut>
 __global__ void __launch_bounds__(FR_THREADS)
 gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                    TOut* __restrict__ C, int M, int N, int K, int ldc, int swiglu, int* status) {
+                    TOut* __restrict__ C, int M, int N, int K, int ldc, int swiglu, const CcbNormFuse fuse, int* status) {
+  __shared__ float s_scale[16];
   constexpr int X_BYTES = 8 * NB * FR_KC * 2;
   constexpr int RED_LD = 8 * NB + 1;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -74,6 +98,7 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   const int ch0 = blockIdx.x * 8;
   const int row_g = (ch0 >> 6) * 128 + (ch0 & 63);
 
+  float h_old = 0.f, nw = 0.f;  // of the thread's (token, feature) of the "into the residual stream" epilogue
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
@@ -119,6 +144,24 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       }
     }
   } else {  // ---- consumers: warp w takes k 32 w .. 32 w + 31 of every stage ----
+    if (fuse.ssq_in != nullptr || fuse.h != nullptr) {
+      // what the epilogue needs of the kernels before this one is asked for now, while the first stages are
+      // on their way, not after the last product
+      pdl_wait();
+      if (fuse.ssq_in != nullptr) {  // the factor of each token row: partial sums in the order of their blocks
+        for (int tok = warp; tok < 8 * NB; tok += FR_WARPS) {
+          const float ss = tok < M ? ccb::row_ssq(fuse.ssq_in + (size_t)tok * fuse.parts_in, fuse.parts_in, lane) : 0.f;
+          if (lane == 0) s_scale[tok] = 1.0f / sqrtf(ss / fuse.dim + fuse.eps);
+        }
+      }
+      if (fuse.h != nullptr && threadIdx.x < 16 * 8 * NB) {
+        const int tok = threadIdx.x >> 4, f = threadIdx.x & 15;
+        if (tok < M && n0 + f < N) {
+          h_old = fuse.h[(size_t)tok * fuse.ldh + n0 + f];
+          nw = fuse.norm_w[n0 + f];
+        }
+      }
+    }
     const int gid = lane >> 2, tig = lane & 3;
     float c[NB][4];
 #pragma unroll
@@ -159,7 +202,28 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   }
   __syncthreads();
   if (warp < FR_WARPS) {
-    if (swiglu) {
+    const bool scaled = fuse.ssq_in != nullptr;
+    if (fuse.h != nullptr) {
+      // into the residual stream: 16 consecutive threads hold the 16 features of a token
+      const int idx = threadIdx.x;
+      if (idx < 16 * 8 * NB) {  // whole warps: 128 NB of the 256 consumer threads
+        const int tok = idx >> 4, f = idx & 15;
+        float v = 0.f;
+        if (tok < M && n0 + f < N) {
+          float sum = 0.f;
+#pragma unroll
+          for (int w = 0; w < FR_WARPS; ++w) sum += red[(w * 16 + f) * RED_LD + tok];
+          if (scaled) sum *= s_scale[tok];
+          v = h_old + sum;
+          fuse.h[(size_t)tok * fuse.ldh + n0 + f] = v;
+          C[(size_t)tok * ldc + n0 + f] = from_f32<TOut>(v * nw);
+        }
+        float q = v * v;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+        if (f == 0) fuse.ssq_out[(size_t)tok * gridDim.x + blockIdx.x] = q;
+      }
+    } else if (swiglu) {
       for (int idx = threadIdx.x; idx < 8 * 8 * NB; idx += FR_WARPS * 32) {
         const int tok = idx >> 3, f = idx & 7;  // consecutive threads write consecutive channels of a token
         if (tok < M && 2 * (ch0 + f) < N) {
@@ -169,6 +233,7 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             g += red[(w * 16 + f) * RED_LD + tok];
             u += red[(w * 16 + f + 8) * RED_LD + tok];
           }
+          if (scaled) g *= s_scale[tok], u *= s_scale[tok];
           C[(size_t)tok * ldc + ch0 + f] = from_f32<TOut>(silu_fr(g) * u);
         }
       }
@@ -179,6 +244,7 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           float sum = 0.f;
 #pragma unroll
           for (int w = 0; w < FR_WARPS; ++w) sum += red[(w * 16 + f) * RED_LD + tok];
+          if (scaled) sum *= s_scale[tok];
           C[(size_t)tok * ldc + n0 + f] = from_f32<TOut>(sum);
         }
       }
@@ -190,7 +256,7 @@ int g_fr_stages = 0;  // 0: the default of the shape
 
 template <int NB, int STAGES, typename TOut>
 int launch_fewrows(const CUtensorMap& tmW, const CUtensorMap& tmX, void* C, int M, int N, int K, int ldc, int swiglu,
-                   int* status, cudaStream_t stream) {
+                   const CcbNormFuse& fuse, int* status, cudaStream_t stream) {
   constexpr int RED = FR_WARPS * 16 * (8 * NB + 1);
   constexpr size_t smem = (size_t)STAGES * (FR_W_BYTES + 8 * NB * FR_KC * 2) + (size_t)(RED + (RED & 1)) * 4 + 2 * STAGES * 8;
   static bool configured = false;
@@ -202,7 +268,7 @@ int launch_fewrows(const CUtensorMap& tmW, const CUtensorMap& tmX, void* C, int 
   }
   const int blocks = swiglu ? (N / 2 + 7) / 8 : (N + FR_ROWS - 1) / FR_ROWS;
   ccb_launch_ex(true, gemm_fewrows_kernel<NB, STAGES, TOut>, dim3(blocks), FR_THREADS, smem, stream, tmW, tmX,
-                (TOut*)C, M, N, K, ldc, swiglu, status);
+                (TOut*)C, M, N, K, ldc, swiglu, fuse, status);
   return ccb_launch_status();
 }
 
@@ -212,7 +278,7 @@ int launch_fewrows(const CUtensorMap& tmW, const CUtensorMap& tmX, void* C, int 
 // four).  With more blocks than fit at two stages, four (8 tokens) or three (16 tokens) blocks per SM.
 template <int NB, typename TOut>
 int pick_stages(const CUtensorMap& tmW, const CUtensorMap& tmX, void* C, int M, int N, int K, int ldc, int swiglu,
-                int* status, cudaStream_t stream) {
+                const CcbNormFuse& fuse, int* status, cudaStream_t stream) {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -227,26 +293,26 @@ int pick_stages(const CUtensorMap& tmW, const CUtensorMap& tmX, void* C, int M, 
     else st = per_sm <= 2 ? 6 : (per_sm == 3 ? 4 : (per_sm <= 5 ? 2 : 4));
   }
 #define CCB_FR_CASE(S) \
-  if (st == S) return launch_fewrows<NB, S, TOut>(tmW, tmX, C, M, N, K, ldc, swiglu, status, stream);
+  if (st == S) return launch_fewrows<NB, S, TOut>(tmW, tmX, C, M, N, K, ldc, swiglu, fuse, status, stream);
   CCB_FR_CASE(8)
   CCB_FR_CASE(6)
   CCB_FR_CASE(5)
   CCB_FR_CASE(3)
   CCB_FR_CASE(2)
 #undef CCB_FR_CASE
-  return launch_fewrows<NB, 4, TOut>(tmW, tmX, C, M, N, K, ldc, swiglu, status, stream);
+  return launch_fewrows<NB, 4, TOut>(tmW, tmX, C, M, N, K, ldc, swiglu, fuse, status, stream);
 }
 
 template <typename TOut>
 int dispatch_fewrows(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc, int swiglu,
-                     int* status, cudaStream_t stream) {
+                     const CcbNormFuse& fuse, int* status, cudaStream_t stream) {
   CUtensorMap tmW, tmX;
   const int nb = M <= 8 ? 1 : 2;
   if (!ccb_tensor_map_2d_plain(W, N, K, ldw, FR_KC, swiglu ? 8 : FR_ROWS, &tmW) ||
       !ccb_tensor_map_2d_plain(A, M, K, lda, FR_KC, 8 * nb, &tmX))
     return CCB_REFUSE_ARG;
-  if (nb == 1) return pick_stages<1, TOut>(tmW, tmX, C, M, N, K, ldc, swiglu, status, stream);
-  return pick_stages<2, TOut>(tmW, tmX, C, M, N, K, ldc, swiglu, status, stream);
+  if (nb == 1) return pick_stages<1, TOut>(tmW, tmX, C, M, N, K, ldc, swiglu, fuse, status, stream);
+  return pick_stages<2, TOut>(tmW, tmX, C, M, N, K, ldc, swiglu, fuse, status, stream);
 }
 
 }  // namespace
@@ -259,8 +325,8 @@ CCB_API int ccb_gemm_fewrows_set_stages(int n) {
 // C[M, N] = A[M, K] W[N, K]^T (swiglu = 0), or C[M, N / 2] = silu(A Wg^T) * (A Wu^T) for W [N, K] whose rows
 // come in blocks of 64 gate rows followed by the 64 up rows of the same channels (swiglu = 1, N a multiple
 // of 128).  M <= 16; K and the row strides multiples of 8 elements; A and W 16-byte aligned.
-CCB_API int ccb_gemm_fewrows_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
-                                  int ldc, int out_dtype, int swiglu, int* status, cudaStream_t stream) {
+static int fewrows_checked(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
+                           int out_dtype, int swiglu, const CcbNormFuse& fuse, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (out_dtype != CCB_F32 && out_dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
   if (M > 16 || K <= 0 || (K & 7) || lda < K || ldw < K || (lda & 7) || (ldw & 7) ||
@@ -268,6 +334,37 @@ CCB_API int ccb_gemm_fewrows_bf16(void* C, const void* A, const void* W, int M, 
     return CCB_REFUSE_SIZE;
   if (swiglu ? ((N & 127) || ldc < N / 2) : (ldc < N)) return CCB_REFUSE_SIZE;
   if (out_dtype == CCB_F32)
-    return dispatch_fewrows<float>(C, A, W, M, N, K, lda, ldw, ldc, swiglu, status, stream);
-  return dispatch_fewrows<__nv_bfloat16>(C, A, W, M, N, K, lda, ldw, ldc, swiglu, status, stream);
+    return dispatch_fewrows<float>(C, A, W, M, N, K, lda, ldw, ldc, swiglu, fuse, status, stream);
+  return dispatch_fewrows<__nv_bfloat16>(C, A, W, M, N, K, lda, ldw, ldc, swiglu, fuse, status, stream);
+}
+
+CCB_API int ccb_gemm_fewrows_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                                  int ldc, int out_dtype, int swiglu, int* status, cudaStream_t stream) {
+  return fewrows_checked(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, swiglu, CcbNormFuse{}, status, stream);
+}
+
+// Number of blocks of the plain product, which is the number of partial sums that the "into the residual
+// stream" epilogue writes for every token.
+CCB_API int ccb_gemm_fewrows_blocks(int N) { return (N + FR_ROWS - 1) / FR_ROWS; }
+
+// The same product with the halves of a norm in its epilogue (see the head of this file).
+//   ssq_in != null: token t of the result is multiplied by 1 / sqrt(sum_p ssq_in[t * parts_in + p] / dim + eps),
+//     p < parts_in, before the activation if there is one.
+//   h != null (plain product, bfloat16 result): h[t, n] += result, C[t, n] = bf16(h[t, n] * norm_w[n]) and
+//     ssq_out[t * blocks + block] = sum over the block's 16 features of h[t, n]^2, blocks =
+//     ccb_gemm_fewrows_blocks(N); ssq_out holds 16 * blocks floats.
+CCB_API int ccb_gemm_fewrows_norm_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                                       int ldc, int out_dtype, int swiglu, const float* ssq_in, int parts_in,
+                                       float dim, float eps, float* h, int ldh, const float* norm_w, float* ssq_out,
+                                       int* status, cudaStream_t stream) {
+  CcbNormFuse fuse{};
+  if (ssq_in != nullptr) {
+    if (parts_in <= 0 || !(dim > 0.f)) return CCB_REFUSE_ARG;
+    fuse.ssq_in = ssq_in, fuse.parts_in = parts_in, fuse.dim = dim, fuse.eps = eps;
+  }
+  if (h != nullptr) {
+    if (swiglu || out_dtype != CCB_BF16 || norm_w == nullptr || ssq_out == nullptr || ldh < N) return CCB_REFUSE_ARG;
+    fuse.h = h, fuse.ldh = ldh, fuse.norm_w = norm_w, fuse.ssq_out = ssq_out;
+  }
+  return fewrows_checked(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, swiglu, fuse, status, stream);
 }

@@ -68,6 +68,16 @@ __device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* dst, const
   }
 }
 
+// The factor of an RMSNorm that has no kernel of its own: token t of the result is multiplied by
+// 1 / sqrt(sum_p ssq_in[t * parts + p] / dim + eps), p < parts, before the activation if there is one (the
+// product before this one left bf16(h * w_norm) as the tokens and the partial sums of h^2; see gemm_fewrows.cu).
+// Swapped products of at most 16 tokens without split-K only.  ssq_in == null: off.
+struct CcbRowScale {
+  const float* ssq_in;
+  int parts;
+  float dim, eps;
+};
+
 // ---------------------------------------------------------------------------------------------
 // rowsA / rowsB: valid rows of the matrices behind tmA (tile 128) and tmB (tile BN).
 // SWAP = false: C[rowA, rowB];  SWAP = true: C[rowB, rowA] (A = weights, B = tokens), with split-K.
@@ -76,7 +86,8 @@ template <int BN, int STAGES, bool SWAP, typename TOut>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TOut* __restrict__ C,
                int ldc, int rowsA, int rowsB, int K, int splits, float* __restrict__ partial,
-               int* __restrict__ counters, int swiglu, int* status) {
+               int* __restrict__ counters, int swiglu, const CcbRowScale rs, int* status) {
+  __shared__ float s_scale[16];
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   extern __shared__ uint8_t smem_raw[];
@@ -167,6 +178,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {  // ---- epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31 ----
     const int q = warp & 3;
     const int row = q * 32 + lane;
+    const bool scaled = SWAP && BN == 16 && rs.ssq_in != nullptr;
+    if (scaled) {  // while the products run: the factor of each token, partial sums in the order of their blocks
+      pdl_wait();
+      for (int tok = q; tok < 16; tok += 4) {
+        const float ss = tok < rowsB ? row_ssq(rs.ssq_in + (size_t)tok * rs.parts, rs.parts, lane) : 0.f;
+        if (lane == 0) s_scale[tok] = 1.0f / sqrtf(ss / rs.dim + rs.eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     const bool ok = mbar_wait(tfull, 0);
     if (!ok && lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
     tc_fence_after();
@@ -201,7 +221,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (j < rowsB) {
-              const float g = __uint_as_float(v[j]), u = xch[row * 17 + j];
+              float g = __uint_as_float(v[j]), u = xch[row * 17 + j];
+              if (scaled) g *= s_scale[j], u *= s_scale[j];
               C[(size_t)j * ldc + ch] = from_f32<TOut>(g / (1.f + __expf(-g)) * u);
             }
           }
@@ -216,7 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = tileB * BN + c0 + j;
-              if (t < rowsB) C[(size_t)t * ldc + ga] = from_f32<TOut>(__uint_as_float(v[j]));
+              if (t < rowsB) C[(size_t)t * ldc + ga] = from_f32<TOut>(__uint_as_float(v[j]) * (scaled ? s_scale[j] : 1.f));
             }
           }
         }
@@ -373,7 +394,8 @@ bool tensor_map(const void* ptr, int rows, int K, int ld, int box_rows, CUtensor
 
 template <int BN, int STAGES, bool SWAP, typename TOut>
 int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, int rowsA, int rowsB, int K,
-              int splits, float* partial, int* counters, int* status, cudaStream_t stream, int swiglu = 0) {
+              int splits, float* partial, int* counters, int* status, cudaStream_t stream, int swiglu = 0,
+              const CcbRowScale& rs = CcbRowScale{}) {
   constexpr size_t smem = (size_t)STAGES * (A_STAGE_BYTES + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -384,7 +406,7 @@ int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, 
   }
   dim3 grid((rowsA + BM - 1) / BM, (rowsB + BN - 1) / BN, splits);
   ccb_launch_ex(true, gemm_tc_kernel<BN, STAGES, SWAP, TOut>, grid, kThreadsTc, smem, stream, 
-      tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, swiglu, status);
+      tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, swiglu, rs, status);
   return ccb_launch_status();
 }
 
@@ -435,8 +457,8 @@ CCB_API int ccb_gemm_tc_bf16(void* C, const void* A, const void* W, int M, int N
 // tile of the tensor-core product owns matching gate and up channels.  The products are accumulated in
 // float and the activation is rounded once (7QiC/ccInfer rounds gate and up to bfloat16 first:
 // src/model/qwen3/qwen3_model.cpp:325-370, src/kernel/mlp/silu_mul.cu:24-28).
-CCB_API int ccb_gemm_tc_swiglu_bf16(void* act, const void* A, const void* W, int M, int F, int K, int lda, int ldw,
-                                    int ld_act, int* status, cudaStream_t stream) {
+static int tc_swiglu(void* act, const void* A, const void* W, int M, int F, int K, int lda, int ldw, int ld_act,
+                     const CcbRowScale& rs, int* status, cudaStream_t stream) {
   if (M <= 0 || F <= 0) return 0;
   if (M > 16 || (F & 63)) return CCB_REFUSE_SIZE;
   if (K <= 0 || (K & 7) || lda < K || ldw < K || ld_act < F || (lda & 7) || (ldw & 7) ||
@@ -444,5 +466,18 @@ CCB_API int ccb_gemm_tc_swiglu_bf16(void* act, const void* A, const void* W, int
     return CCB_REFUSE_SIZE;
   CUtensorMap tmW, tmX;
   if (!tensor_map(W, 2 * F, K, ldw, BM, &tmW) || !tensor_map(A, M, K, lda, 16, &tmX)) return CCB_REFUSE_ARG;
-  return launch_tc<16, 6, true, __nv_bfloat16>(tmW, tmX, act, ld_act, 2 * F, M, K, 1, nullptr, nullptr, status, stream, 1);
+  return launch_tc<16, 6, true, __nv_bfloat16>(tmW, tmX, act, ld_act, 2 * F, M, K, 1, nullptr, nullptr, status, stream, 1, rs);
+}
+
+CCB_API int ccb_gemm_tc_swiglu_bf16(void* act, const void* A, const void* W, int M, int F, int K, int lda, int ldw,
+                                    int ld_act, int* status, cudaStream_t stream) {
+  return tc_swiglu(act, A, W, M, F, K, lda, ldw, ld_act, CcbRowScale{}, status, stream);
+}
+
+// The same with the factor of a norm for every token (see CcbRowScale).
+CCB_API int ccb_gemm_tc_swiglu_scaled_bf16(void* act, const void* A, const void* W, int M, int F, int K, int lda,
+                                           int ldw, int ld_act, const float* ssq_in, int parts, float dim, float eps,
+                                           int* status, cudaStream_t stream) {
+  if (ssq_in == nullptr || parts <= 0 || !(dim > 0.f)) return CCB_REFUSE_ARG;
+  return tc_swiglu(act, A, W, M, F, K, lda, ldw, ld_act, CcbRowScale{ssq_in, parts, dim, eps}, status, stream);
 }

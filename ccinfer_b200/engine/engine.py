@@ -414,6 +414,8 @@ class Engine:
             if i in self._entry_group:
                 src = i if e.cache_of is None else e.cache_of
                 cache = LayerCache(self._cache[src], step.groups[self._entry_group[i]], own=e.cache_of is None)
+            nxt = plan.layers[plan.order[i + 1].layer] if i + 1 < len(plan.order) else None
+            stream.next_norm = getattr(nxt, "first_norm", None)
             block.forward(stream, step, cache, self._state.get(i))
         if step.n_logit_rows == 0:
             return None

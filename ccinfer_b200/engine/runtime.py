@@ -7,6 +7,7 @@ import torch
 
 from .. import kernels
 from ..errors import DeviceFault, ExtensionMissing, ScratchMoved, Unsupported
+from ..parts.base import UnscaledRows
 
 
 class ScratchPool:
@@ -69,24 +70,59 @@ class Runtime:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.tc_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)  # split-K tile counters
         self.merge_counters = torch.zeros(8192, dtype=torch.int32, device=self.device)  # attention split counters
+        self._sink_turn = 0
 
-    def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """out[M, N] = x[M, K] @ w[N, K]^T; out may be float for bfloat16 operands (the logits)."""
+    @staticmethod
+    def rows(x):
+        """x as a plain tensor (rows that a norm left short of their factor are finished)."""
+        return x.finish() if isinstance(x, UnscaledRows) else x
+
+    def _into_stream(self, out, x, w, sink) -> bool:
+        """The product as the last one of a part, with few rows: added into the residual stream by its own
+        epilogue, which also leaves the rows of the norm that follows short of one factor per row (the norm
+        then needs no kernel).  False: not this time (another kernel, another kind of norm)."""
+        norm, h = sink.norm, sink.stream.h
+        N = w.shape[0]
+        if (getattr(norm, "unscaled_rows_from", None) is None or sink.stream.pending is not None
+                or h.shape != (x.shape[0], N) or out.dtype != torch.bfloat16):
+            return False
+        self._sink_turn ^= 1   # two sets of buffers in turn: the rows of one norm are read while the next are written
+        ssq = self.scratch.get(f"unscaled_ssq{self._sink_turn}", (16, kernels.gemm_fewrows_blocks(N)), torch.float32)
+        xw = self.scratch.get(f"unscaled_rows{self._sink_turn}", (kernels.FEWROWS_MAX_ROWS, N), self.dtype)[:x.shape[0]]
+        rows = norm.unscaled_rows_from(sink.stream, xw, ssq, kernels.gemm_fewrows_blocks(N))
+        if rows is None:
+            return False
+        kernels.gemm_fewrows_norm_bf16(xw, x, w, into=(h, norm.w, ssq), status=self.status)
+        sink.stream.unscaled = rows
+        return True
+
+    def linear(self, out: torch.Tensor, x, w: torch.Tensor, sink=None):
+        """out[M, N] = x[M, K] @ w[N, K]^T; out may be float for bfloat16 operands (the logits).
+
+        ``x`` may be ``UnscaledRows``.  ``sink`` (a ``ResidualSink``): the product is the last of its part and
+        may add its result into the residual stream itself; then None is returned instead of ``out``."""
         if self.dtype == torch.float32:
-            kernels.gemm_f32(out, x, w)
+            kernels.gemm_f32(out, self.rows(x), w)
             return out
-        M, K = x.shape
+        xt = x.x if isinstance(x, UnscaledRows) else x
+        M, K = xt.shape
         N = w.shape[0]
         choice = "library"
         if M <= kernels.SKINNY_MAX_ROWS:  # a few tokens: the product is a stream of the weights
             choice = kernels.few_rows_product_kernel(
-                M, N, K, self.sm_count, kernels.gemm_tc_fits(K, x, w), kernels.gemm_fewrows_fits(M, K, x, w),
-                kernels.gemm_skinny_fits(M, K, x, w))
+                M, N, K, self.sm_count, kernels.gemm_tc_fits(K, xt, w), kernels.gemm_fewrows_fits(M, K, xt, w),
+                kernels.gemm_skinny_fits(M, K, xt, w))
+        if choice == "fewrows":
+            if sink is not None and xt is x and self._into_stream(out, x, w, sink):
+                return None
+            if xt is not x:
+                kernels.gemm_fewrows_norm_bf16(out, xt, w, scale=x.scale, status=self.status)
+            else:
+                kernels.gemm_fewrows_bf16(out, x, w, status=self.status)
+            return out
+        x = self.rows(x)
         if choice == "tc":
             kernels.gemm_tc_bf16(out, x, w, 1, None, None, self.status)
-            return out
-        if choice == "fewrows":
-            kernels.gemm_fewrows_bf16(out, x, w, status=self.status)
             return out
         if choice == "skinny":
             kernels.gemm_skinny_bf16(out, x, w)
@@ -107,18 +143,29 @@ class Runtime:
 
         A few tokens in bfloat16 with the blocked layout: one kernel (the activation is the product's
         epilogue).  Otherwise the product into scratch and the activation kernel."""
+        un = x if isinstance(x, UnscaledRows) else None
+        if un is not None:
+            x = un.x
         M, K = x.shape
         N = w.shape[0]
         if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M <= kernels.SKINNY_MAX_ROWS
                 and kernels.gemm_tc_fits(K, x, w) and -(-N // 128) >= self.sm_count
                 and kernels.gemm_tc_splits(M, N, K) == 1):
-            kernels.gemm_tc_swiglu_bf16(act, x, w, self.status)
+            if un is not None:
+                kernels.gemm_tc_swiglu_scaled_bf16(act, x, w, *un.scale, status=self.status)
+            else:
+                kernels.gemm_tc_swiglu_bf16(act, x, w, self.status)
             return act
         if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M <= kernels.FEWROWS_MAX_ROWS
                 and K >= kernels.FEWROWS_MIN_K and N % 128 == 0 and kernels.gemm_fewrows_fits(M, K, x, w)
                 and -(-N // 128) < self.sm_count):
-            kernels.gemm_fewrows_bf16(act, x, w, swiglu=True, status=self.status)
+            if un is not None:
+                kernels.gemm_fewrows_norm_bf16(act, x, w, swiglu=True, scale=un.scale, status=self.status)
+            else:
+                kernels.gemm_fewrows_bf16(act, x, w, swiglu=True, status=self.status)
             return act
+        if un is not None:
+            x = un.finish()
         if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M >= kernels.PAIR_SWIGLU_MIN_ROWS
                 and N % 128 == 0 and kernels.gemm_tc_fits(K, x, w)):
             # many tokens: the tcgen05 product on pairs of SMs with the activation as its epilogue (level with the

@@ -75,34 +75,10 @@ class StepContext:
         self.row_slot = None        # request slot of each logits row
         self.pending_tokens = None  # int32 [slots]: the token last sampled per request slot (token id -1 - s)
         self.groups: List[GroupStep] = []
-        self.host = None         # StepLayout.HostView of the same arrays
+        self.host = None         # host copies of the same arrays
+        self.residual_sink = None   # parts.base.ResidualSink offered to the last product of the part that runs
 
-
-class StepLayout:
-    """Fixed offsets of the step arrays inside one int32 buffer."""
-
-    def __init__(self, max_tokens: int, max_entries: int, group_strides: List[int]):
-        self.max_tokens, self.max_entries, self.group_strides = max_tokens, max_entries, list(group_strides)
-        off = 0
-
-        def region(n):
-            nonlocal off
-            start = off
-            off += (n + 3) // 4 * 4  # keep every region 16-byte aligned
-            return start
-
-        self.o_token_ids = region(max_tokens)
-        self.o_positions = region(max_tokens)
-        self.o_entry_of_token = region(max_tokens)
-        self.o_logit_rows = region(max_tokens)
-        self.o_row_slot = region(max_tokens)
-        self.o_cu_q = region(max_entries + 1)
-        self.o_pos0 = region(max_entries)
-        self.o_ctx_after = region(max_entries)
-        self.o_state_slot = region(max_entries)
-        self.o_slot_map = []
-        self.o_block_table = []
-        for stride in self.group_strides:
-            self.o_slot_map.append(region(max_tokens))
-            self.o_block_table.append(region(max_entries * stride))
-        self.size = off
+    def take_sink(self):
+        """The sink offered to the part that is running, once (the part's LAST product may use it)."""
+        sink, self.residual_sink = self.residual_sink, None
+        return sink

@@ -41,6 +41,12 @@ _SIGNATURES = {
     "ccb_gemm_fewrows_set_stages": [c_int],
     "ccb_gemm_fewrows_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_void_p, c_void_p],
+    "ccb_gemm_fewrows_blocks": [c_int],
+    "ccb_gemm_fewrows_norm_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p,
+                                   c_void_p, c_void_p],
+    "ccb_gemm_tc_swiglu_scaled_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_void_p, c_int, c_float, c_float, c_void_p, c_void_p],
     "ccb_residual_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                              c_int, c_void_p, c_void_p],
     "ccb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -210,6 +216,20 @@ def gemm_tc_swiglu_bf16(act, a, w, status=None) -> None:
     assert w.shape == (2 * F, K) and act.shape == (M, F) and a.stride(1) == w.stride(1) == act.stride(1) == 1
     _check(lib().ccb_gemm_tc_swiglu_bf16(_p(act), _p(a), _p(w), M, F, K, a.stride(0), w.stride(0), act.stride(0),
                                          _p(status), _stream()), "gemm_tc_swiglu_bf16")
+
+
+def gemm_tc_swiglu_scaled_bf16(act, a, w, ssq, parts: int, dim: int, eps: float, status=None) -> None:
+    """gemm_tc_swiglu_bf16 whose token rows still lack the factor of their RMSNorm: token t of both products is
+    multiplied by 1 / sqrt(sum_p ssq[t, p] / dim + eps) before the activation (ssq float [16, parts])."""
+    _cuda(act, a, w, ssq, status)
+    assert act.dtype == a.dtype == w.dtype == torch.bfloat16 and ssq.dtype == torch.float32
+    M, K = a.shape
+    F = w.shape[0] // 2
+    assert w.shape == (2 * F, K) and act.shape == (M, F) and a.stride(1) == w.stride(1) == act.stride(1) == 1
+    assert ssq.is_contiguous() and ssq.numel() >= parts * 16
+    _check(lib().ccb_gemm_tc_swiglu_scaled_bf16(_p(act), _p(a), _p(w), M, F, K, a.stride(0), w.stride(0),
+                                                act.stride(0), _p(ssq), int(parts), float(dim), float(eps),
+                                                _p(status), _stream()), "gemm_tc_swiglu_scaled_bf16")
 
 
 def residual_rmsnorm(y, h, delta, w, eps: float, row_idx=None, n_rows=None, status=None) -> None:
@@ -591,6 +611,38 @@ def gemm_fewrows_bf16(c, a, w, swiglu: bool = False, status=None) -> None:
     assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
     _check(lib().ccb_gemm_fewrows_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _dt(c),
                                        1 if swiglu else 0, _p(status), _stream()), "gemm_fewrows_bf16")
+
+
+def gemm_fewrows_blocks(N: int) -> int:
+    """Partial sums per token that gemm_fewrows_norm_bf16 writes when it adds into a residual stream of width N."""
+    return int(lib().ccb_gemm_fewrows_blocks(int(N)))
+
+
+def gemm_fewrows_norm_bf16(c, a, w, swiglu: bool = False, scale=None, into=None, status=None) -> None:
+    """gemm_fewrows_bf16 with the halves of an RMSNorm that has no kernel of its own in its epilogue.
+
+    ``scale = (ssq, parts, dim, eps)``: the rows of ``a`` still lack the factor of their norm; token t of the
+    result is multiplied by 1 / sqrt(sum_p ssq[t, p] / dim + eps) (before the activation, with ``swiglu``).
+    ``into = (h, norm_w, ssq_out)``: h [M, N] (float) += the result; c = bfloat16(h * norm_w); ssq_out
+    [16, gemm_fewrows_blocks(N)] gets each block's sum of h^2 per token: what the next product needs as ``scale``."""
+    _cuda(w, status)
+    assert a.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT and c.is_cuda and a.is_cuda
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N // 2 if swiglu else N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    ssq, parts, dim, eps = scale if scale is not None else (None, 0, 0.0, 0.0)
+    h, norm_w, ssq_out = into if into is not None else (None, None, None)
+    if ssq is not None:
+        assert ssq.dtype == torch.float32 and ssq.is_contiguous() and ssq.numel() >= parts * 16
+    if h is not None:
+        assert not swiglu and c.dtype == torch.bfloat16 and h.dtype == torch.float32 and h.shape == (M, N)
+        assert h.stride(1) == 1 and norm_w.dtype == torch.float32 and norm_w.numel() == N and norm_w.is_contiguous()
+        assert ssq_out.dtype == torch.float32 and ssq_out.is_contiguous() and ssq_out.numel() >= gemm_fewrows_blocks(N) * 16
+    _check(lib().ccb_gemm_fewrows_norm_bf16(
+        _p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _dt(c), 1 if swiglu else 0,
+        _p(ssq), int(parts), float(dim), float(eps), _p(h), h.stride(0) if h is not None else 0, _p(norm_w),
+        _p(ssq_out), _p(status), _stream()), "gemm_fewrows_norm_bf16")
 
 
 def few_rows_product_kernel(M: int, N: int, K: int, sm_count: int, fits_tc: bool, fits_fewrows: bool,

@@ -27,6 +27,8 @@ from .base import CacheNeed, Mixer, PositionEncoding, TensorSpec
 
 
 class GroupedQueryAttention(Mixer):
+    takes_unscaled = True
+
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PositionEncoding, names: dict, qk_norm_eps: Optional[float] = None,
                  window: Optional[int] = None, own_kv: bool = True, scale: Optional[float] = None):
@@ -176,5 +178,4 @@ class GroupedQueryAttention(Mixer):
                 status=rt.status)
             self._attend(q, o, cache, step, T)
         out = rt.scratch.get("attn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
-        rt.linear(out, o.view(T, self.q_width), self.w_o)
-        return out
+        return rt.linear(out, o.view(T, self.q_width), self.w_o, sink=step.take_sink())

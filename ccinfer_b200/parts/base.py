@@ -123,6 +123,43 @@ class Residual:
     def __init__(self, h: torch.Tensor):
         self.h = h
         self.pending: Optional[torch.Tensor] = None
+        # A product that ended a mixer or a feed-forward may have done the sum itself and left the rows of the
+        # norm that follows short of their factor (``UnscaledRows``); the norm's ``fold`` hands them on or
+        # finishes them.  ``takes_unscaled`` says whether the part that the next ``fold`` serves takes such
+        # rows; ``next_norm`` is the norm that the block after this one starts with (None: unknown).
+        self.unscaled: Optional["UnscaledRows"] = None
+        self.takes_unscaled = False
+        self.next_norm = None
+
+
+class UnscaledRows:
+    """The rows of a step after a norm of the form y = x * f(x) * w, without the factor f(x) of each row.
+
+    A product is linear, so the factor can be applied to its result instead (before any activation): the
+    kernels that take such rows do that, and the norm needs no kernel of its own.  ``x`` [T, dim] holds
+    x * w in the compute type; ``ssq`` [16, parts] (float) partial sums of x^2 of each of the (at most 16)
+    rows; the factor of row t is 1 / sqrt(sum_p ssq[t, p] / dim + eps).  ``finish()`` returns the normed rows
+    as a plain tensor for a consumer that has no such kernel (``Runtime.rows`` calls it)."""
+
+    def __init__(self, x, ssq, parts: int, dim: int, eps: float, norm, finish):
+        self.x, self.ssq, self.parts, self.dim, self.eps, self.norm, self._finish = x, ssq, parts, dim, eps, norm, finish
+        self.shape = x.shape
+
+    @property
+    def scale(self):
+        return (self.ssq, self.parts, self.dim, self.eps)
+
+    def finish(self):
+        return self._finish()
+
+
+class ResidualSink:
+    """Where the last product of a mixer or feed-forward may put its result instead of returning it: added
+    into ``stream.h``, with the rows of ``norm`` (the norm that folds the stream next) left as
+    ``stream.unscaled``.  A part that ignores it changes nothing: what it returns becomes ``pending``."""
+
+    def __init__(self, stream: Residual, norm):
+        self.stream, self.norm = stream, norm
 
 
 class Norm(Part):
@@ -167,6 +204,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    takes_unscaled = False   # True: ``forward`` hands x to ``Runtime.linear`` as it comes (it may be UnscaledRows)
+
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 
@@ -184,6 +223,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_unscaled = False   # as for a mixer
+
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         raise NotImplementedError
 

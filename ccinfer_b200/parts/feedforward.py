@@ -16,6 +16,8 @@ from .base import FeedForward, TensorSpec
 
 
 class SwiGLU(FeedForward):
+    takes_unscaled = True
+
     def __init__(self, hidden: int, intermediate: int, names: dict):
         """``names``: tensor names under the keys gate, up, down."""
         self.hidden, self.inter, self.names = int(hidden), int(intermediate), dict(names)
@@ -43,5 +45,4 @@ class SwiGLU(FeedForward):
         act = rt.scratch.get("ffn_act", (rt.max_tokens, self.inter), rt.dtype)[:T]
         rt.gated_up(act, x, self.w_gate_up, self.block)
         out = rt.scratch.get("ffn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
-        rt.linear(out, act, self.w_down)
-        return out
+        return rt.linear(out, act, self.w_down, sink=step.take_sink())

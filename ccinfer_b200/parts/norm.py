@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import Norm, Residual, TensorSpec
+from .base import Norm, Residual, TensorSpec, UnscaledRows
 
 
 class RMSNorm(Norm):
@@ -23,6 +23,11 @@ class RMSNorm(Norm):
     def fold(self, stream: Residual, rows=None, n_rows=None):
         rt = self.rt
         T = stream.h.shape[0]
+        un, stream.unscaled = stream.unscaled, None
+        if un is not None and rows is None and un.norm is self and stream.pending is None:
+            # the product before did the sum and left this norm's rows short of their factor
+            return un if stream.takes_unscaled else un.finish()
+        # (rows left for another norm than this one: h is complete, they are dropped)
         if rows is None:
             y = rt.scratch.get(self.scratch_key, (rt.max_tokens, self.dim), rt.dtype)[:T]
             kernels.residual_rmsnorm(y, stream.h, stream.pending, self.w, self.eps, status=rt.status)
@@ -32,6 +37,21 @@ class RMSNorm(Norm):
             y = rt.scratch.get(self.scratch_key + "_rows", (rt.max_tokens, self.dim), rt.dtype)[:n]
             kernels.residual_rmsnorm(y, stream.h, stream.pending, self.w, self.eps, row_idx=rows, n_rows=n,
                                      status=rt.status)
+        return y
+
+    def unscaled_rows_from(self, stream: Residual, xw, ssq, parts: int):
+        """What a product that adds into the stream itself leaves for this norm: ``xw`` gets h * w, ``ssq``
+        [16, parts] the partial sums of h^2 (see ``Runtime.linear``).  None: this norm takes no such rows."""
+        if xw.shape[1] != self.dim:
+            return None
+        h = stream.h
+        return UnscaledRows(xw, ssq, parts, self.dim, self.eps, self, lambda: self.rows_of(h))
+
+    def rows_of(self, h):
+        """norm(h) of a stream that is complete (nothing pending), as a plain tensor."""
+        rt = self.rt
+        y = rt.scratch.get(self.scratch_key, (rt.max_tokens, self.dim), rt.dtype)[:h.shape[0]]
+        kernels.residual_rmsnorm(y, h, None, self.w, self.eps, status=rt.status)
         return y
 
     def apply(self, x):

@@ -307,6 +307,57 @@ def test_gemm_fewrows_swiglu(M, F, K):
                             torch.zeros((17, K), dtype=torch.bfloat16, device="cuda"), w, swiglu=True, status=status)
 
 
+@pytest.mark.parametrize("M,D,K,N2,F", [(1, 48, 64, 40, 64), (5, 1000, 520, 301, 192), (8, 4096, 4096, 6144, 12288),
+                                        (13, 2560, 9728, 4096, 64 * 151), (16, 136, 2048 + 72, 130, 64 * 3)])
+def test_products_that_take_a_norm_apart(M, D, K, N2, F):
+    """h += a Wo^T, then RMSNorm(h) feeding a plain product and a gated one, with no kernel for the norm: the
+    first product's epilogue adds into h and leaves bf16(h * w_norm) and partial sums of h^2, the products after
+    it multiply their results by each token's factor (before the activation).  Against the plain formulas in
+    64-bit; the 16-feature blocks of the first product and D, N2 ragged against every tile."""
+    k = _k()
+    a, a_ref = _rand((M, K), torch.bfloat16, 70)
+    wo, wo_ref = _rand((D, K), torch.bfloat16, 71, scale=0.05)
+    h, h_ref = _rand((M, D), torch.float32, 72)
+    h[min(M - 1, 2)] *= 30.0    # rows of very different size: each needs its own factor
+    h_ref = h.double().cpu()
+    nw, nw_ref = _rand((D,), torch.float32, 73)
+    eps = 1e-5
+    parts = k.gemm_fewrows_blocks(D)
+    ssq = torch.full((16, parts), float("nan"), dtype=torch.float32, device="cuda")
+    xw = torch.full((M, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.gemm_fewrows_norm_bf16(xw, a, wo, into=(h, nw, ssq), status=status)
+    h_want = h_ref + a_ref @ wo_ref.T
+    assert _rel(h, h_want) <= 2e-5
+    assert _rel(xw, h_want * nw_ref) <= 8e-3
+    assert _rel(ssq[:M].sum(1), (h_want ** 2).sum(1)) <= 2e-5
+    normed = h_want * torch.rsqrt((h_want ** 2).mean(1, keepdim=True) + eps) * nw_ref
+    # a plain product of those rows
+    w2, w2_ref = _rand((N2, D), torch.bfloat16, 74, scale=0.05)
+    for out in (torch.float32, torch.bfloat16):
+        c = torch.full((M, N2), float("nan"), dtype=out, device="cuda")
+        k.gemm_fewrows_norm_bf16(c, xw, w2, scale=(ssq, parts, D, eps), status=status)
+        assert _rel(c, normed @ w2_ref.T) <= 8e-3
+    # the gated product, both kernels that take such rows
+    wg, wg_ref = _rand((F, D), torch.bfloat16, 75, scale=0.05)
+    wu, wu_ref = _rand((F, D), torch.bfloat16, 76, scale=0.05)
+    w = k.interleave_gate_up(wg, wu, k.SWIGLU_BLOCK)
+    g, u = normed @ wg_ref.T, normed @ wu_ref.T
+    want = g / (1 + torch.exp(-g)) * u
+    act = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    k.gemm_fewrows_norm_bf16(act, xw, w, swiglu=True, scale=(ssq, parts, D, eps), status=status)
+    assert _rel(act, want) <= 8e-3
+    if k.gemm_tc_fits(D, xw, w):
+        act2 = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+        k.gemm_tc_swiglu_scaled_bf16(act2, xw, w, ssq, parts, D, eps, status=status)
+        assert _rel(act2, want) <= 8e-3
+    assert int(status.item()) == 0
+    # the same factor as the norm kernel's: the two ways to the normed rows differ by bfloat16 rounding only
+    y = torch.empty((M, D), dtype=torch.bfloat16, device="cuda")
+    k.residual_rmsnorm(y, h, None, nw, eps, status=status)
+    assert _rel(y, normed) <= 8e-3
+
+
 @pytest.mark.parametrize("M,N,K", [(8, 6144, 4096), (16, 6144, 4096), (3, 10240, 5120), (8, 16384, 2048), (12, 12288, 2560)])
 def test_gemm_fewrows_many_blocks_per_sm(M, N, K):
     """Shapes with three to seven blocks resident per SM and more stages than the ring holds: the ring's

@@ -126,6 +126,67 @@ def test_parts_alone(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_product_that_adds_into_the_stream_and_the_norm_after_it(dtype):
+    """With few rows the last product of a part may take the sum and the norm after it apart
+    (``ResidualSink`` / ``UnscaledRows``): whatever the part after the norm is, the rows it gets are
+    norm(h + x W^T): as unscaled rows that the next product finishes, as a plain tensor for a part that takes no
+    such rows, for another norm than the one that was announced, and for picked rows.  In 32-bit nothing is
+    taken apart and the same calls give the same values."""
+    from ccinfer_b200.engine.runtime import Runtime
+    from ccinfer_b200.parts import Residual, RMSNorm
+    from ccinfer_b200.parts.base import ResidualSink, UnscaledRows
+    M, D, K, N2 = 7, 1040, 2304, 520
+    rt = Runtime("cuda:0", DT[dtype], max_tokens=32, max_entries=8)
+    g = torch.Generator().manual_seed(5)
+    x_ref = torch.randn(M, K, generator=g).to(DT[dtype]).double()
+    w_ref = (torch.randn(D, K, generator=g) * 0.05).to(DT[dtype]).double()
+    w2_ref = (torch.randn(N2, D, generator=g) * 0.05).to(DT[dtype]).double()
+    h_ref = torch.randn(M, D, generator=g).float().double()
+    x, w, w2 = (t.to("cuda", DT[dtype]) for t in (x_ref, w_ref, w2_ref))
+    weights = {"n.weight": 1 + 0.1 * torch.randn(D, generator=g), "m.weight": 1 + 0.1 * torch.randn(D, generator=g)}
+    norm, other = RMSNorm(D, 1e-5, "n.weight"), RMSNorm(D, 2e-5, "m.weight", scratch_key="normed_other")
+    for n in (norm, other):
+        n.bind(rt, lambda name: weights[name].float().cuda())
+    h_want = h_ref + x_ref @ w_ref.T
+    want = plain.rms_norm(h_want, weights["n.weight"].double(), 1e-5)
+
+    def produce():
+        stream = Residual(h_ref.float().cuda())
+        out = torch.empty((M, D), dtype=DT[dtype], device="cuda")
+        stream.pending = rt.linear(out, x, w, sink=ResidualSink(stream, norm))
+        return stream
+
+    # the part after the norm takes unscaled rows: a product finishes them
+    stream = produce()
+    taken_apart = stream.unscaled is not None
+    assert taken_apart == (dtype == "bfloat16") and (stream.pending is None) == taken_apart
+    stream.takes_unscaled = True
+    rows = norm.fold(stream)
+    assert isinstance(rows, UnscaledRows) == taken_apart and stream.unscaled is None
+    assert _rel(stream.h, h_want) <= 2e-5
+    y = torch.empty((M, N2), dtype=DT[dtype], device="cuda")
+    rt.linear(y, rows, w2)
+    assert _rel(y, want @ w2_ref.T) <= TOL[dtype]
+    assert _rel(rt.rows(rows), want) <= TOL[dtype]
+    # it takes none: the norm finishes them itself
+    stream = produce()
+    stream.takes_unscaled = False
+    y = norm.fold(stream)
+    assert torch.is_tensor(y) and _rel(y, want) <= TOL[dtype] and _rel(stream.h, h_want) <= 2e-5
+    # another norm than the one announced, and picked rows: the stream is complete, they norm it themselves
+    stream = produce()
+    stream.takes_unscaled = True
+    y = other.fold(stream)
+    assert torch.is_tensor(y) and stream.unscaled is None
+    assert _rel(y, plain.rms_norm(h_want, weights["m.weight"].double(), 2e-5)) <= TOL[dtype]
+    stream = produce()
+    picked = torch.tensor([M - 1, 0], dtype=torch.int32, device="cuda")
+    y = norm.fold(stream, rows=picked, n_rows=2)
+    assert _rel(y, want[[M - 1, 0]]) <= TOL[dtype]
+    rt.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_order_of_layers_is_data(dtype):
     """A layer named twice (two caches) and a layer that reads another run's cache, against plain parts."""
     from ccinfer_b200.engine.engine import StepEntry
