@@ -80,16 +80,17 @@ class Runtime:
     def _into_stream(self, out, x, w, sink) -> bool:
         """The product as the last one of a part, with few rows: added into the residual stream by its own
         epilogue, which also leaves the rows of the norm that follows short of one factor per row (the norm
-        then needs no kernel).  False: not this time (another kernel, another kind of norm)."""
+        then needs no kernel).  False: not this time (another kind of norm)."""
         norm, h = sink.norm, sink.stream.h
-        N = w.shape[0]
+        N, M = w.shape[0], x.shape[0]
         if (getattr(norm, "unscaled_rows_from", None) is None or sink.stream.pending is not None
-                or h.shape != (x.shape[0], N) or out.dtype != torch.bfloat16):
+                or h.shape != (M, N) or out.dtype != torch.bfloat16):
             return False
         self._sink_turn ^= 1   # two sets of buffers in turn: the rows of one norm are read while the next are written
-        ssq = self.scratch.get(f"unscaled_ssq{self._sink_turn}", (16, kernels.gemm_fewrows_blocks(N)), torch.float32)
-        xw = self.scratch.get(f"unscaled_rows{self._sink_turn}", (kernels.FEWROWS_MAX_ROWS, N), self.dtype)[:x.shape[0]]
-        rows = norm.unscaled_rows_from(sink.stream, xw, ssq, kernels.gemm_fewrows_blocks(N))
+        parts = kernels.gemm_fewrows_blocks(N)
+        ssq = self.scratch.get(f"unscaled_ssq{self._sink_turn}", (kernels.FEWROWS_MAX_ROWS, parts), torch.float32)
+        xw = self.scratch.get(f"unscaled_rows{self._sink_turn}", (kernels.FEWROWS_MAX_ROWS, N), self.dtype)[:M]
+        rows = norm.unscaled_rows_from(sink.stream, xw, ssq, parts)
         if rows is None:
             return False
         kernels.gemm_fewrows_norm_bf16(xw, x, w, into=(h, norm.w, ssq), status=self.status)
@@ -164,7 +165,7 @@ class Runtime:
             else:
                 kernels.gemm_fewrows_bf16(act, x, w, swiglu=True, status=self.status)
             return act
-        if un is not None:
+        if un is not None:   # no kernel below takes such rows
             x = un.finish()
         if (self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK and M >= kernels.PAIR_SWIGLU_MIN_ROWS
                 and N % 128 == 0 and kernels.gemm_tc_fits(K, x, w)):

@@ -170,3 +170,29 @@ def test_mid_shape_many_decoding_requests_match_plain(model_mid, n_live):
         assert eng.graph_replays > 0
         del eng
         torch.cuda.empty_cache()
+
+
+def test_8b_layer_shape_steps_of_more_than_2048_rows_match_plain(model_8b):
+    """Steps of 2,048 rows and more (in bfloat16 gate|up with its activation runs on the two-SM tcgen05 kernel
+    from 1,024 rows on, with tiles of 256 rows): a prompt of 2,300 tokens whole (rows that fill no tile), and
+    one of 2,560 tokens as 512 tokens and then 2,048 more after them, beside a short request's prompt and
+    decoded tokens."""
+    rng = np.random.RandomState(11)
+    V = SHAPE_8B_4_OF_36_LAYERS["vocab_size"]
+    reqs = {"long": rng.randint(0, V, size=2300).tolist(), "cut": rng.randint(0, V, size=2560).tolist(),
+            "short": rng.randint(0, V, size=40).tolist()}
+    m = model_8b.with_requests(reqs)
+    steps = [
+        {"entries": [{"id": "long", "tokens": reqs["long"], "want": list(range(2300))}], "end": ["long"]},
+        {"entries": [{"id": "cut", "tokens": reqs["cut"][:512], "want": []},
+                     {"id": "short", "tokens": reqs["short"][:38], "want": list(range(38))}], "end": []},
+        {"entries": [{"id": "short", "tokens": reqs["short"][38:39], "want": [0]},
+                     {"id": "cut", "tokens": reqs["cut"][512:], "want": list(range(2048))}], "end": ["cut"]},
+        {"entries": [{"id": "short", "tokens": reqs["short"][39:], "want": [0]}], "end": ["short"]},
+    ]
+    for dtype in ("float32", "bfloat16"):
+        rows = _run(m, dtype, [dict(s) for s in steps], kv_tokens=4096 + 512, max_requests=4, max_tokens_per_step=2304,
+                    max_context=2624)
+        worst = m.worst(rows)
+        print(f"[worst] 8B layer shape, {dtype}, steps of 2,048 rows and more: {worst:.3e}")
+        assert worst <= (TOL32 if dtype == "float32" else TOL16["8b"])
