@@ -355,10 +355,13 @@ def test_which_kernel_takes_a_few_rows_product():
     # 8B: q|k|v 6144 x 4096, o 4096 x 4096, gate|up 24576 x 4096, down 4096 x 12288, vocabulary 151936 x 4096
     assert [pick(8, *s) for s in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096))] == \
         ["fewrows", "fewrows", "tc", "fewrows", "tc"]
-    assert [pick(1, *s) for s in ((6144, 4096), (4096, 4096), (4096, 12288))] == ["skinny", "fewrows", "fewrows"]
-    # 14B / 32B with one token: the ring kernel's blocks do not fit two per SM; long K goes to the tcgen05 kernel
+    assert [pick(1, *s) for s in ((6144, 4096), (4096, 4096), (4096, 12288))] == ["fewrows", "fewrows", "fewrows"]
+    # 14B / 32B with one token: the same
     assert [pick(1, *s) for s in ((7168, 5120), (5120, 5120), (5120, 17408), (5120, 8192))] == \
-        ["skinny", "skinny", "tc_split", "tc_split"]
+        ["fewrows", "fewrows", "fewrows", "fewrows"]
+    # what the ring kernel does not fit: long K to the tcgen05 kernel in slices, the rest to the register-streaming one
+    assert kernels.few_rows_product_kernel(1, 5120, 17408, 148, True, False, True) == "tc_split"
+    assert kernels.few_rows_product_kernel(1, 5120, 4096, 148, True, False, True) == "skinny"
     assert [pick(16, *s) for s in ((7168, 5120), (5120, 17408), (34816, 5120))] == ["fewrows", "fewrows", "tc"]
     # short K, more rows than the own kernels take, shapes no own kernel fits
     assert pick(8, 4096, 1024) == "skinny" and pick(17, 4096, 4096) == "library"
