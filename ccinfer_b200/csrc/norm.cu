@@ -155,6 +155,85 @@ CCB_API int ccb_residual_rmsnorm(void* y, float* h, const void* delta, const flo
   return ccb_launch_status();
 }
 
+// The first layer's norm together with the embedding: h[t, :] = float(table[ids[t], :]) and
+// y[t, :] = norm(h[t, :]) * w in one pass (7QiC/ccInfer runs the gather, src/kernel/elementwise/elementwise.cu:67-78,
+// and the norm as two kernels).  An id of -1 - s stands for pending[s], as in embed_gather.
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads)
+embed_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ h, const T* __restrict__ table, const int* __restrict__ ids,
+                     const float* __restrict__ w, int D, int V, float eps, const int* __restrict__ pending,
+                     int n_pending, int vec, int* status) {
+  ccb::pdl_begin();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 && pending != nullptr && -1 - id < n_pending) id = pending[-1 - id];
+  float* hr = h + (size_t)t * D;
+  T* yr = y + (size_t)t * D;
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) set_status(status, CCB_ST_BAD_TOKEN);
+    for (int d = threadIdx.x; d < D; d += kNormThreads) {
+      hr[d] = 0.f;
+      yr[d] = from_f32<T>(0.f);
+    }
+    return;
+  }
+  const T* row = table + (size_t)id * D;
+  float ss = 0.f;
+  if (vec) {   // D a multiple of 4 and at most 4 kNormVecs kNormThreads, everything 16-byte aligned
+    const int nvec = D >> 2;
+    float4 v[kNormVecs], g[kNormVecs];
+#pragma unroll
+    for (int j = 0; j < kNormVecs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      if (i < nvec) {
+        g[j] = Vec4<float>::load(w + 4 * i);
+        v[j] = Vec4<T>::load(row + 4 * i);
+        Vec4<float>::store(hr + 4 * i, v[j]);
+        ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+      }
+    }
+    ss = block_sum<kNormThreads>(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int j = 0; j < kNormVecs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      if (i < nvec)
+        Vec4<T>::store(yr + 4 * i, make_float4(v[j].x * inv * g[j].x, v[j].y * inv * g[j].y, v[j].z * inv * g[j].z,
+                                               v[j].w * inv * g[j].w));
+    }
+    return;
+  }
+  for (int d = threadIdx.x; d < D; d += kNormThreads) {
+    const float v = to_f32(row[d]);
+    hr[d] = v;
+    ss += v * v;
+  }
+  ss = block_sum<kNormThreads>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += kNormThreads) yr[d] = from_f32<T>(to_f32(row[d]) * inv * w[d]);
+}
+
+CCB_API int ccb_embed_rmsnorm(void* y, float* h, const void* table, const int* ids, const float* w, int rows, int D,
+                              int V, float eps, int dtype, const int* pending, int n_pending, int* status,
+                              cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (D <= 0 || V <= 0) return CCB_REFUSE_SIZE;
+  const int esize = dtype == CCB_F32 ? 4 : 2;
+  const int vec = (D % 4 == 0) && D <= 4 * kNormVecs * kNormThreads && ((size_t)D * esize) % 8 == 0 &&
+                  ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(table) |
+                    reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+  if (dtype == CCB_F32)
+    ccb_launch(embed_rmsnorm_kernel<float>, rows, kNormThreads, 0, stream, (float*)y, h, (const float*)table, ids, w,
+               D, V, eps, pending, n_pending, vec, status);
+  else if (dtype == CCB_BF16)
+    ccb_launch(embed_rmsnorm_kernel<__nv_bfloat16>, rows, kNormThreads, 0, stream, (__nv_bfloat16*)y, h,
+               (const __nv_bfloat16*)table, ids, w, D, V, eps, pending, n_pending, vec, status);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
 // Plain RMSNorm over the last axis of a [rows, D] tensor of the storage type.
 template <typename T>
 __global__ void rmsnorm_kernel(T* __restrict__ y, const T* __restrict__ x, const float* __restrict__ w, int D,

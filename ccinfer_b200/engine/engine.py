@@ -407,7 +407,10 @@ class Engine:
 
     def _forward(self, step: StepContext) -> Optional[torch.Tensor]:
         plan = self.plan
-        stream = plan.embedding.forward(step)
+        if getattr(plan.embedding, "takes_first_norm", False) and plan.order:
+            stream = plan.embedding.forward(step, getattr(plan.layers[plan.order[0].layer], "first_norm", None))
+        else:
+            stream = plan.embedding.forward(step)
         for i, e in enumerate(plan.order):
             block = plan.layers[e.layer]
             cache = None

@@ -49,6 +49,8 @@ _SIGNATURES = {
                                        c_void_p, c_int, c_float, c_float, c_void_p, c_void_p],
     "ccb_residual_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                              c_int, c_void_p, c_void_p],
+    "ccb_embed_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                          c_void_p, c_int, c_void_p, c_void_p],
     "ccb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
     "ccb_qk_norm_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -185,6 +187,20 @@ def embed_gather(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status
     assert pending is None or pending.dtype == torch.int32
     _check(lib().ccb_embed_gather(_p(h), _p(table), _p(ids), T, D, table.shape[0], _dt(table), _p(pending),
                                   0 if pending is None else pending.numel(), _p(status), _stream()), "embed_gather")
+
+
+def embed_rmsnorm(y, h, table, ids, w, eps: float, status=None, pending=None) -> None:
+    """embed_gather and the norm of the rows it wrote in one pass: h[t, :] = float(table[ids[t], :]) and
+    y[t, :] = RMSNorm(h[t, :]) * w (y and table in the storage type, w float)."""
+    _cuda(y, h, table, ids, w, status, pending)
+    T, D = h.shape
+    assert h.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == D and ids.numel() >= T
+    assert y.shape == (T, D) and y.dtype == table.dtype and w.dtype == torch.float32 and w.numel() == D
+    assert h.is_contiguous() and y.is_contiguous() and table.is_contiguous()
+    assert pending is None or pending.dtype == torch.int32
+    _check(lib().ccb_embed_rmsnorm(_p(y), _p(h), _p(table), _p(ids), _p(w), T, D, table.shape[0], float(eps),
+                                   _dt(table), _p(pending), 0 if pending is None else pending.numel(), _p(status),
+                                   _stream()), "embed_rmsnorm")
 
 
 def silu_mul(act: torch.Tensor, gate_up: torch.Tensor, block: int = 0) -> None:

@@ -130,6 +130,8 @@ class Residual:
         self.unscaled: Optional["UnscaledRows"] = None
         self.takes_unscaled = False
         self.next_norm = None
+        # (norm, rows): the rows of ``norm`` are there already (the embedding wrote them with the stream)
+        self.ready = None
 
 
 class UnscaledRows:

@@ -28,12 +28,23 @@ class TokenEmbedding(Part):
         self.rt = rt
         self.table = fetch(self.weight_name)
 
-    def forward(self, step) -> Residual:
+    takes_first_norm = True
+
+    def forward(self, step, first_norm=None) -> Residual:
+        """``first_norm``: the norm that folds the stream first; where it can, its rows are written by the
+        same kernel as the stream (``stream.ready``)."""
         rt = self.rt
         h = rt.scratch.get("residual", (rt.max_tokens, self.hidden), torch.float32)[:step.n_tokens]
-        kernels.embed_gather(h, self.table, step.token_ids, status=rt.status,
-                             pending=getattr(step, "pending_tokens", None))
-        return Residual(h)
+        pending = getattr(step, "pending_tokens", None)
+        y = None
+        if first_norm is not None and hasattr(first_norm, "from_embedding"):
+            y = first_norm.from_embedding(h, self.table, step.token_ids, pending)
+        if y is None:
+            kernels.embed_gather(h, self.table, step.token_ids, status=rt.status, pending=pending)
+        stream = Residual(h)
+        if y is not None:
+            stream.ready = (first_norm, y)
+        return stream
 
 
 class OutputHead(Part):

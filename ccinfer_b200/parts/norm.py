@@ -23,6 +23,9 @@ class RMSNorm(Norm):
     def fold(self, stream: Residual, rows=None, n_rows=None):
         rt = self.rt
         T = stream.h.shape[0]
+        ready, stream.ready = stream.ready, None
+        if ready is not None and rows is None and ready[0] is self and stream.pending is None:
+            return ready[1]   # written together with the stream (the embedding's kernel)
         un, stream.unscaled = stream.unscaled, None
         if un is not None and rows is None and un.norm is self and stream.pending is None:
             # the product before did the sum and left this norm's rows short of their factor
@@ -37,6 +40,15 @@ class RMSNorm(Norm):
             y = rt.scratch.get(self.scratch_key + "_rows", (rt.max_tokens, self.dim), rt.dtype)[:n]
             kernels.residual_rmsnorm(y, stream.h, stream.pending, self.w, self.eps, row_idx=rows, n_rows=n,
                                      status=rt.status)
+        return y
+
+    def from_embedding(self, h, table, ids, pending):
+        """norm(h) for h = table[ids], both written by one kernel; None where that kernel does not apply."""
+        rt = self.rt
+        if table.dtype != rt.dtype or table.shape[1] != self.dim or not table.is_contiguous():
+            return None
+        y = rt.scratch.get(self.scratch_key, (rt.max_tokens, self.dim), rt.dtype)[:h.shape[0]]
+        kernels.embed_rmsnorm(y, h, table, ids, self.w, self.eps, status=rt.status, pending=pending)
         return y
 
     def unscaled_rows_from(self, stream: Residual, xw, ssq, parts: int):

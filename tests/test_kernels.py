@@ -49,6 +49,35 @@ def test_embed_gather(dtype, T, D, V):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,D,V,eps", [(1, 80, 11, 1e-6), (37, 1000, 301, 1e-5), (5, 4096, 64, 3e-6), (4, 67, 9, 1e-6),
+                                       (3, 8200, 5, 1e-6)])
+def test_embed_rmsnorm(dtype, T, D, V, eps):
+    """The gather and the first norm in one pass: the stream as embed_gather writes it, the normed rows as the
+    plain formula gives them; widths that take the vector path, an odd one and one beyond it; a pending token;
+    a bad id is reported and its rows are zero."""
+    k = _k()
+    table, ref = _rand((V, D), DT[dtype], 1)
+    w, w_ref = _rand((D,), torch.float32, 6)
+    w, w_ref = (w + 1).contiguous(), w_ref + 1
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
+    pending = torch.tensor([0, int(ids[-1])], dtype=torch.int32, device="cuda")
+    sent = ids.clone()
+    sent[-1] = -1 - 1                       # "the token last sampled for slot 1"
+    h = torch.full((T, D), float("nan"), dtype=torch.float32, device="cuda")
+    y = torch.full((T, D), float("nan"), dtype=DT[dtype], device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.embed_rmsnorm(y, h, table, sent.cuda(), w, eps, status=status, pending=pending)
+    want = plain.embed(ref, ids.tolist())
+    assert torch.equal(h.cpu().double(), want) and int(status.item()) == 0
+    assert _rel(y, plain.rms_norm(want, w_ref, eps)) <= (2e-6 if dtype == "float32" else 8e-3)
+    bad = ids.clone()
+    bad[0] = V
+    k.embed_rmsnorm(y, h, table, bad.cuda(), w, eps, status=status)
+    assert int(status.item()) == k.ST_BAD_TOKEN
+    assert float(h[0].abs().max()) == 0.0 == float(y[0].float().abs().max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,D,eps", [(3, 80, 1e-6), (17, 1000, 1e-5), (2, 5120, 3e-6)])
 def test_residual_rmsnorm(dtype, T, D, eps):
     k = _k()

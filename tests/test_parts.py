@@ -82,6 +82,15 @@ def test_parts_alone(dtype):
         # embedding
         stream = plan.embedding.forward(step)
         assert torch.equal(stream.h.cpu().double(), plain.embed(wd["model.embed_tokens.weight"], toks))
+        # the embedding with the norm that folds it first: one kernel writes both
+        s0 = plan.embedding.forward(step, block.norm1)
+        assert torch.equal(s0.h, stream.h) and s0.ready is not None
+        y0 = block.norm1.fold(s0)
+        assert s0.ready is None
+        assert _rel(y0, plain.rms_norm(stream.h.cpu().double(), wd[p + "input_layernorm.weight"], 1e-5)) <= TOL[dtype]
+        s0 = plan.embedding.forward(step, block.norm1)          # another norm than announced: it norms the stream itself
+        assert _rel(block.norm2.fold(s0), plain.rms_norm(stream.h.cpu().double(),
+                                                         wd[p + "post_attention_layernorm.weight"], 1e-5)) <= TOL[dtype]
         # norm: plain apply, fold of a pending delta, fold on picked rows
         assert _rel(block.norm1.apply(x), plain.rms_norm(x_ref, wd[p + "input_layernorm.weight"], 1e-5)) <= TOL[dtype]
         h0 = stream.h.clone()
