@@ -102,6 +102,29 @@ def test_pages_run_out_during_generation(model_b):
     llm.engine.cache.check_consistency()
 
 
+def test_many_requests_two_cache_groups_and_too_few_pages(tmp_path_factory):
+    """Twenty requests of random lengths and sampling parameters through the scheduler on a model with two
+    cache groups (layer 1 of Tiny D reads a window: its pages are given back while a request runs), with so few
+    pages that requests give way and are computed again, prompts in portions beside decoding requests, one step
+    in flight: every request's tokens are those of the plain implementation, nothing is left in the cache."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d = str(tmp_path_factory.mktemp("genD"))
+    cfg, w, page = helpers.make_model_dir(d, "D")
+    rng = np.random.RandomState(31)
+    prompts = _prompts(cfg, [int(n) for n in rng.randint(1, 90, size=20)], 8)
+    sp = [SamplingParams(max_tokens=int(rng.randint(1, 40)), temperature=float(rng.choice([0.0, 0.7, 1.2])), seed=i)
+          for i in range(20)]
+    llm = LLM(d, dtype="float32", page_size=page, kv_tokens=20 * page, prefill_chunk_size=24, max_requests=6,
+              max_running=6, max_tokens_per_step=96, max_context=160)
+    assert llm.scheduler.run_ahead
+    got = llm.generate(prompts, sp)
+    assert llm.scheduler.preemptions > 0
+    want = [plain.generate(cfg, w, p, s.max_tokens, s.temperature, s.seed) for p, s in zip(prompts, sp)]
+    assert got == want
+    llm.engine.cache.check_consistency()
+    assert all(pool.used_pages == 0 for pool in llm.engine.cache.pools) and llm.engine.cache.slots.free_slots == 6
+
+
 def test_running_ahead_reads_tokens_a_step_late_and_changes_none(model_b):
     """The entry point launches a step before it reads the tokens of the step before (they stay on the
     device for the next embedding).  Same tokens as a scheduler that waits for every step, also when a
