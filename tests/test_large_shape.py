@@ -196,3 +196,17 @@ def test_8b_layer_shape_steps_of_more_than_2048_rows_match_plain(model_8b):
         worst = m.worst(rows)
         print(f"[worst] 8B layer shape, {dtype}, steps of 2,048 rows and more: {worst:.3e}")
         assert worst <= (TOL32 if dtype == "float32" else TOL16["8b"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mid_shape_the_same_trace_twice_gives_the_same_bits(model_mid, dtype):
+    """Nothing in a step depends on which block or warp ran first (partial sums are added in fixed orders, counters
+    only say who is last): a mixed trace with decode steps from graphs gives bit-identical logits twice, on two
+    engines."""
+    m = model_mid
+    opts = dict(kv_tokens=2048, max_requests=8, max_tokens_per_step=1024, max_context=1024, use_graphs=True)
+    steps = helpers.trace_mixed(m.reqs, max_live=4, seed=12, portion_choices=(128, 200, 65, 2, 16))
+    first = _run(m, dtype, [dict(s) for s in steps], **opts)
+    second = _run(m, dtype, [dict(s) for s in steps], **opts)
+    assert set(first) == set(second)
+    assert all(np.array_equal(first[k], second[k]) for k in first)
