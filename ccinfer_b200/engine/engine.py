@@ -482,17 +482,21 @@ class Engine:
         return done
 
     def _bucket_of(self, n: int) -> int:
+        """The size of the graph that takes a decode step of n requests: the next power of two, or
+        max_requests where that is no power of two and lies below it."""
+        if n > self.options.max_requests:
+            return 0
         b = 1
         while b < n:
             b *= 2
-        return b if b <= self.options.max_requests else 0
+        return min(b, self.options.max_requests)
 
     def _all_buckets(self) -> List[int]:
         out, b = [], 1
-        while b <= self.options.max_requests:
+        while b < self.options.max_requests:
             out.append(b)
             b *= 2
-        return out
+        return out + [self.options.max_requests]
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the tokens given, as one batch, from the cache; returns float logits [wanted, vocab].

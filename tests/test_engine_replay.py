@@ -123,6 +123,26 @@ def test_many_decoding_requests_match_plain(models, name, dtype, n_live, graphs)
     eng.cache.check_consistency()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graphs_when_the_request_limit_is_no_power_of_two(models, dtype):
+    """Twenty-four request slots: steps of 17 to 24 decoding requests are replayed from a graph of 24 rows (the
+    next power of two does not exist for this engine), smaller ones from graphs of 16 and below."""
+    d, cfg, page = models["E"][:3]
+    weights = models["E"][5]
+    for n_live in (5, 17, 24):
+        rng = np.random.RandomState(n_live)
+        reqs = {f"m{i}": rng.randint(0, cfg["vocab_size"], size=int(rng.randint(8, 40))).tolist() for i in range(n_live)}
+        ref = {rid: helpers.plain_logits(cfg, weights, toks) for rid, toks in reqs.items()}
+        steps = helpers.trace_many_decoders(reqs, decode_steps=4)
+        pool = helpers.max_live_tokens(steps, round_to=max(64, page))
+        eng = _engine(d, dtype, page, pool, use_graphs=True, max_requests=24, max_tokens_per_step=512)
+        rows = helpers.replay(eng, steps)
+        helpers.compare(rows, ref, _tol("E", dtype), f"tiny E {dtype} {n_live} of 24 slots")
+        assert eng.graph_replays >= 3 and sorted(eng._graphs) == [{5: 8, 17: 24, 24: 24}[n_live]]
+        eng.cache.check_consistency()
+    assert eng._all_buckets() == [1, 2, 4, 8, 16, 24] and eng._bucket_of(25) == 0
+
+
 @pytest.mark.parametrize("name", CONFIGS)
 def test_cuts_agree_in_float32(models, name):
     """The same position under two cuttings: equal to 32-bit round-off, far below the distance to bfloat16."""
