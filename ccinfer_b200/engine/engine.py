@@ -24,7 +24,7 @@ import torch
 from .. import kernels
 from ..cache.manager import CacheManager, GroupSpec
 from ..config.registry import load_config
-from ..errors import InvalidArgument, KVBlockExhausted, RequestTooLong, Unsupported
+from ..errors import InvalidArgument, Unsupported
 from ..native import RunnerFailed
 from ..weights.loader import open_weights, random_fetch
 from .plan import ModelPlan
