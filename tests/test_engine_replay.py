@@ -7,7 +7,6 @@ bfloat16, for three tiny configurations.
 """
 import numpy as np
 import pytest
-import torch
 
 import helpers
 

@@ -5,7 +5,6 @@ What 7QiC/ccInfer tests of its translator and manager in tests/unit/test_batch_t
 tests/unit/test_kv_cache_manager.cpp is restated for this interface: the arrays of a mixed step, pages taken
 on demand and returned when a step fails, nothing moved by a refused step.
 """
-import ctypes
 
 import numpy as np
 import pytest

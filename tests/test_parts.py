@@ -1,8 +1,6 @@
 """Each part alone against its plain function, the order of layers as data, and a toy architecture whose
 mixer keeps state of its own, registered, built and stepped without a change to the package's files."""
 import dataclasses
-import json
-import math
 import os
 
 import numpy as np

@@ -8,7 +8,6 @@ row (the array keeps the first call's contents), and sizes beyond the array must
 
 This file is collected last, so a run that stops at the first failure has already run every other test.
 """
-import ctypes
 import math
 from ctypes import c_float, c_int, c_void_p
 
