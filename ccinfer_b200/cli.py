@@ -4,6 +4,9 @@
 chunk 512, 0 = no chunking); ``--max-tokens``, ``--temperature``, ``--top-k``, ``--top-p`` carry the
 names of its request fields (src/http/http_server.cpp:529-555) and ``--seed`` that of its
 SamplingParams.  The server's ``--port`` has no meaning here.  Prompts are token ids.
+``--random-config FILE --weights-seed N`` runs a model of that configuration with random weights drawn on the
+device (the model that ``--write-random-model`` would write for the same seed), ``--dump-config`` prints the
+typed configuration and exits.
 """
 from __future__ import annotations
 
@@ -25,12 +28,21 @@ def _parse_prompts(args) -> list:
                                    [int(t) for t in line.replace(",", " ").split()])
     if args.random_prompts:
         import numpy as np
-        from .config.registry import load_config
-        _, cfg = load_config(args.model_path)
+        cfg = _config(args)
         rng = np.random.RandomState(args.prompt_seed)
         for n in args.random_prompts.split(","):
             prompts.append(rng.randint(0, cfg.vocab_size, size=int(n)).tolist())
     return prompts
+
+
+def _config(args):
+    """The typed configuration of --random-config or of the folder of --model-path."""
+    from .config.registry import architecture_of, load_config
+    if args.random_config:
+        with open(args.random_config) as f:
+            cj = json.load(f)
+        return architecture_of(cj).parse_config(cj)
+    return load_config(args.model_path)[1]
 
 
 def main(argv=None) -> int:
@@ -61,13 +73,20 @@ def main(argv=None) -> int:
     ap.add_argument("--stats", action="store_true", help="print cache and scheduler figures to stderr")
     ap.add_argument("--write-random-model", metavar="CONFIG_JSON",
                     help="write a random model folder to --model-path from this config.json and exit")
+    ap.add_argument("--random-config", metavar="CONFIG_JSON",
+                    help="instead of --model-path: a model of this config.json with random weights (--weights-seed, "
+                         "--weights-std) drawn on the device")
+    ap.add_argument("--dump-config", action="store_true", help="print the typed configuration as JSON and exit")
     ap.add_argument("--weights-seed", type=int, default=0)
     ap.add_argument("--weights-std", type=float, default=0.02)
     args = ap.parse_args(argv)
 
-    if not args.model_path:
+    if not args.model_path and not args.random_config:
         ap.print_usage(sys.stderr)
-        print("Error: --model-path is required", file=sys.stderr)
+        print("Error: --model-path (or --random-config) is required", file=sys.stderr)
+        return 1
+    if args.write_random_model and not args.model_path:
+        print("Error: --write-random-model writes to --model-path", file=sys.stderr)
         return 1
     from .errors import CcinferError
     try:
@@ -80,13 +99,24 @@ def main(argv=None) -> int:
             write_random_model(args.model_path, cfg, args.weights_seed, args.weights_std)
             print(f"wrote {args.model_path}", file=sys.stderr)
             return 0
+        if args.dump_config:
+            print(json.dumps(_config(args).to_json(), indent=1, sort_keys=True))
+            return 0
         prompts = _parse_prompts(args)
         if not prompts:
             print("Error: no prompts (--prompt-ids, --prompt-file or --random-prompts)", file=sys.stderr)
             return 1
         from .engine.scheduler import SamplingParams
         from .llm import LLM
-        llm = LLM(args.model_path, dtype=args.dtype, prefill_chunk_size=args.prefill_chunk_size,
+        engine = None
+        if args.random_config:
+            from .engine.engine import Engine, EngineOptions
+            engine = Engine.from_random(_config(args), args.weights_seed, args.weights_std, EngineOptions(
+                dtype=args.dtype, page_size=args.page_size, kv_tokens=args.kv_tokens,
+                kv_memory_fraction=args.kv_memory_fraction, max_requests=args.max_requests,
+                max_tokens_per_step=args.max_tokens_per_step, max_context=args.max_context))
+        llm = LLM(None if engine is not None else args.model_path, engine=engine, dtype=args.dtype,
+                  prefill_chunk_size=args.prefill_chunk_size,
                   page_size=args.page_size, kv_tokens=args.kv_tokens,
                   kv_memory_fraction=args.kv_memory_fraction, max_requests=args.max_requests,
                   max_tokens_per_step=args.max_tokens_per_step, max_context=args.max_context,

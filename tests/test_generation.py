@@ -242,6 +242,35 @@ def test_command_line(model_a):
     assert bad.returncode == 2 and "ModelLoadFailed" in bad.stderr
 
 
+def test_command_line_random_config(tmp_path):
+    """--random-config draws on the device the model that --write-random-model writes for the same seed: the
+    same tokens either way, and those of the plain implementation on the stream's weights; --dump-config."""
+    import tiny_configs
+    cfg = dict(tiny_configs.TINY_B)
+    cj = str(tmp_path / "config.json")
+    with open(cj, "w") as f:
+        json.dump(cfg, f)
+    exe = [sys.executable, os.path.join(ROOT, "bin", "ccinfer")]
+    common = ["--dtype", "float32", "--page-size", "8", "--kv-tokens", "128", "--max-tokens", "6", "--random-prompts", "7,12",
+              "--prompt-seed", "3", "--weights-seed", "11", "--weights-std", "0.05", "--temperature", "0.7"]
+    a = subprocess.run(exe + ["--random-config", cj] + common, capture_output=True, text=True, timeout=300)
+    assert a.returncode == 0, a.stderr
+    d = str(tmp_path / "model")
+    w = subprocess.run(exe + ["--model-path", d, "--write-random-model", cj, "--weights-seed", "11", "--weights-std", "0.05"],
+                       capture_output=True, text=True, timeout=300)
+    assert w.returncode == 0, w.stderr
+    b = subprocess.run(exe + ["--model-path", d] + common, capture_output=True, text=True, timeout=300)
+    assert b.returncode == 0, b.stderr
+    assert a.stdout == b.stdout and len(a.stdout.strip().splitlines()) == 2
+    weights = {k: v.to(torch.bfloat16).float() if cfg["torch_dtype"] == "bfloat16" else v
+               for k, v in plain.stream_weights(cfg, 11, 0.05).items()}
+    prompts = [np.random.RandomState(3).randint(0, cfg["vocab_size"], size=n).tolist() for n in (7,)]
+    first = json.loads(a.stdout.strip().splitlines()[0])
+    assert first["token_ids"] == plain.generate(cfg, weights, prompts[0], 6, 0.7, 42)
+    dump = subprocess.run(exe + ["--random-config", cj, "--dump-config"], capture_output=True, text=True, timeout=300)
+    assert dump.returncode == 0 and json.loads(dump.stdout)["num_hidden_layers"] == cfg["num_hidden_layers"]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(model_b, dtype, tmp_path):
     """bin/trace_run as a user calls it: a mixed trace over a small pool, files compared with the plain logits."""
