@@ -108,19 +108,15 @@ def main(argv=None) -> int:
             return 1
         from .engine.scheduler import SamplingParams
         from .llm import LLM
-        engine = None
+        options = dict(dtype=args.dtype, prefill_chunk_size=args.prefill_chunk_size, page_size=args.page_size,
+                       kv_tokens=args.kv_tokens, kv_memory_fraction=args.kv_memory_fraction,
+                       max_requests=args.max_requests, max_tokens_per_step=args.max_tokens_per_step,
+                       max_context=args.max_context, max_running=args.max_running, eos_token_id=args.eos_token_id,
+                       warm_up=args.warm_up)
         if args.random_config:
-            from .engine.engine import Engine, EngineOptions
-            engine = Engine.from_random(_config(args), args.weights_seed, args.weights_std, EngineOptions(
-                dtype=args.dtype, page_size=args.page_size, kv_tokens=args.kv_tokens,
-                kv_memory_fraction=args.kv_memory_fraction, max_requests=args.max_requests,
-                max_tokens_per_step=args.max_tokens_per_step, max_context=args.max_context))
-        llm = LLM(None if engine is not None else args.model_path, engine=engine, dtype=args.dtype,
-                  prefill_chunk_size=args.prefill_chunk_size,
-                  page_size=args.page_size, kv_tokens=args.kv_tokens,
-                  kv_memory_fraction=args.kv_memory_fraction, max_requests=args.max_requests,
-                  max_tokens_per_step=args.max_tokens_per_step, max_context=args.max_context,
-                  max_running=args.max_running, eos_token_id=args.eos_token_id, warm_up=args.warm_up)
+            llm = LLM.from_random(_config(args), args.weights_seed, args.weights_std, **options)
+        else:
+            llm = LLM(args.model_path, **options)
         sp = SamplingParams(max_tokens=args.max_tokens, top_k=args.top_k, top_p=args.top_p,
                             temperature=args.temperature, seed=args.seed)
         for i, toks in enumerate(llm.generate(prompts, sp)):

@@ -43,6 +43,19 @@ class LLM:
                                    run_ahead=hasattr(engine, "sample_async"))
         self._next_id = 0
 
+    @classmethod
+    def from_random(cls, config, weights_seed: int = 0, weights_std: float = 0.02, **options) -> "LLM":
+        """A model of a typed configuration (or of a config.json dictionary) with the random weights that
+        (weights_seed, weights_std) name, drawn on the device; ``options`` as for the constructor."""
+        if isinstance(config, dict):
+            from .config.registry import architecture_of
+            config = architecture_of(config).parse_config(config)
+        names = ("dtype", "device", "page_size", "kv_tokens", "kv_memory_fraction", "max_requests",
+                 "max_tokens_per_step", "max_context", "use_graphs")
+        engine = Engine.from_random(config, weights_seed, weights_std,
+                                    EngineOptions(**{k: options[k] for k in names if k in options}))
+        return cls(engine=engine, **options)
+
     def generate(self, prompts: Sequence[Sequence[int]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
         """New token ids for each prompt (lists of token ids), in the order given."""
