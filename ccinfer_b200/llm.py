@@ -75,6 +75,39 @@ class LLM:
         self.engine.check()
         return [out.get(rid, []) for rid in ids]
 
+    # -- the same, a step at a time ---------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], sampling_params: Optional[SamplingParams] = None, req_id=None):
+        """Queues a request; returns its id (``req_id`` or a fresh one)."""
+        if req_id is None:
+            req_id = f"gen-{self._next_id}"
+            self._next_id += 1
+        self.scheduler.submit(req_id, [int(t) for t in prompt], sampling_params)
+        return req_id
+
+    def cancel(self, req_id) -> bool:
+        return self.scheduler.cancel(req_id)
+
+    def step(self):
+        """One scheduler step; the events it returns (``TokenEvent(req_id, token, finished, reason)``) are those
+        of the step before it when the scheduler runs one step ahead."""
+        return self.scheduler.step()
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def forward(self, entries):
+        """The raw step, for tests: ``entries`` = [(request id, its next tokens, places whose logits are wanted)];
+        requests are opened at their first entry (close them with ``engine.close_request``).  Returns the float
+        logits [wanted, vocab] on the host."""
+        from .engine.engine import StepEntry
+        batch = []
+        for e in entries:
+            e = e if isinstance(e, StepEntry) else StepEntry(*e)
+            if e.req_id not in self.engine.cache.requests:
+                self.engine.open_request(e.req_id)
+            batch.append(e)
+        return self.engine.step(batch).cpu().numpy()
+
     def stats(self) -> dict:
         s = self.engine.stats()
         s["scheduler_steps"] = self.scheduler.steps

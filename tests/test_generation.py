@@ -227,6 +227,31 @@ def test_long_decoding_and_first_tokens(model_b):
         helpers.compare(first, {"x": ref}, tol, f"first tokens {dtype}")
 
 
+def test_python_entry_point_a_step_at_a_time(model_a):
+    """add_request / step / cancel / forward of the Python entry point: the tokens of generate(), a request
+    cancelled on the way, and the raw step against the plain logits."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, page = model_a
+    llm = LLM(d, dtype="float32", page_size=page, kv_tokens=256, prefill_chunk_size=8, max_requests=4)
+    prompts = _prompts(cfg, [6, 19, 3], 12)
+    ids = [llm.add_request(p, SamplingParams(max_tokens=7)) for p in prompts]
+    out, n = {}, 0
+    while llm.has_work():
+        for ev in llm.step():
+            if ev.token is not None:
+                out.setdefault(ev.req_id, []).append(ev.token)
+        n += 1
+        if n == 3:
+            assert llm.cancel(ids[1])
+    assert out[ids[0]] == plain.generate(cfg, w, prompts[0], 7) and out[ids[2]] == plain.generate(cfg, w, prompts[2], 7)
+    assert len(out.get(ids[1], [])) < 7 and not llm.cancel(ids[1])
+    logits = llm.forward([("raw", prompts[1], [0, len(prompts[1]) - 1])])
+    ref = helpers.plain_logits(cfg, w, prompts[1])
+    assert logits.shape == (2, cfg["vocab_size"]) and np.abs(logits - ref[[0, -1]]).max() <= 2e-5 * np.abs(ref).max()
+    llm.engine.close_request("raw")
+    assert all(p.used_pages == 0 for p in llm.engine.cache.pools)
+
+
 def test_command_line(model_a):
     d, cfg, w, page = model_a
     prompt = _prompts(cfg, [9], 4)[0]
